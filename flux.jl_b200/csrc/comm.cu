@@ -1,0 +1,159 @@
+// DistributedUtils collectives over NCCL (NVLink 5 / NVSwitch): communicator bootstrap, mean all-reduce of
+// gradient buffers, broadcast of parameters / optimiser state, reduce-to-root.
+//
+// libnccl is opened at run time (the copy already loaded into the process is preferred), so the library
+// itself loads on machines without NCCL; the fb_comm_* calls then fail with FB_ERR_NCCL.
+#include <dlfcn.h>
+
+#include "common.cuh"
+
+namespace {
+
+struct NcclUniqueId { char internal[FB_UNIQUE_ID_BYTES]; };
+typedef void* NcclComm;
+constexpr int NCCL_FLOAT32 = 7, NCCL_SUM = 0, NCCL_AVG = 4;
+
+struct NcclApi {
+  void* handle = nullptr;
+  int (*GetUniqueId)(NcclUniqueId*) = nullptr;
+  int (*CommInitRank)(NcclComm*, int, NcclUniqueId, int) = nullptr;
+  int (*CommDestroy)(NcclComm) = nullptr;
+  int (*CommAbort)(NcclComm) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*Broadcast)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*Reduce)(const void*, void*, size_t, int, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*CommGetAsyncError)(NcclComm, int*) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  bool ok = false;
+};
+
+NcclApi& nccl() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api;
+  tried = true;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  for (int pass = 0; pass < 2 && !api.handle; ++pass)
+    for (const char* nm : names) {
+      api.handle = dlopen(nm, RTLD_NOW | RTLD_LOCAL | (pass == 0 ? RTLD_NOLOAD : 0));
+      if (api.handle) break;
+    }
+  if (!api.handle) return api;
+#define FB_SYM(field, name) *(void**)(&api.field) = dlsym(api.handle, name)
+  FB_SYM(GetUniqueId, "ncclGetUniqueId");
+  FB_SYM(CommInitRank, "ncclCommInitRank");
+  FB_SYM(CommDestroy, "ncclCommDestroy");
+  FB_SYM(CommAbort, "ncclCommAbort");
+  FB_SYM(AllReduce, "ncclAllReduce");
+  FB_SYM(Broadcast, "ncclBroadcast");
+  FB_SYM(Reduce, "ncclReduce");
+  FB_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
+  FB_SYM(GetErrorString, "ncclGetErrorString");
+#undef FB_SYM
+  api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.Broadcast && api.Reduce &&
+           api.GetErrorString;
+  return api;
+}
+
+int32_t nccl_fail(const char* what, int rc) {
+  NcclApi& n = nccl();
+  return fb_fail(FB_ERR_NCCL, "%s failed: %s", what, n.GetErrorString ? n.GetErrorString(rc) : "unknown NCCL error");
+}
+
+}  // namespace
+
+struct fb_comm {
+  NcclComm comm;
+  int rank, nranks, device;
+};
+
+#define FB_NCCL_READY()                                                                                   \
+  NcclApi& n = nccl();                                                                                    \
+  if (!n.ok) return fb_fail(FB_ERR_NCCL, "%s: libnccl.so.2 could not be loaded (%s)", __func__, dlerror() ? "dlopen failed" : "missing symbols")
+
+FB_API int32_t fb_comm_get_unique_id(void* id_host) {
+  FB_REQUIRE(id_host, FB_ERR_INVALID_ARG, "fb_comm_get_unique_id: NULL pointer");
+  FB_NCCL_READY();
+  NcclUniqueId id;
+  const int rc = n.GetUniqueId(&id);
+  if (rc != 0) return nccl_fail("ncclGetUniqueId", rc);
+  memcpy(id_host, id.internal, FB_UNIQUE_ID_BYTES);
+  return FB_OK;
+}
+
+FB_API int32_t fb_comm_init_rank(fb_ctx* ctx, const void* id_host, int32_t nranks, int32_t rank, fb_comm** out) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(id_host && out, FB_ERR_INVALID_ARG, "fb_comm_init_rank: NULL pointer");
+  FB_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, FB_ERR_INVALID_ARG, "fb_comm_init_rank: rank %d of %d", rank, nranks);
+  FB_NCCL_READY();
+  FB_CUDA(cudaSetDevice(ctx->device));
+  NcclUniqueId id;
+  memcpy(id.internal, id_host, FB_UNIQUE_ID_BYTES);
+  NcclComm c = nullptr;
+  const int rc = n.CommInitRank(&c, nranks, id, rank);
+  if (rc != 0) return nccl_fail("ncclCommInitRank", rc);
+  fb_comm* fc = new fb_comm();
+  fc->comm = c; fc->rank = rank; fc->nranks = nranks; fc->device = ctx->device;
+  *out = fc;
+  return FB_OK;
+}
+
+FB_API int32_t fb_comm_destroy(fb_comm* comm) {
+  if (!comm) return FB_OK;
+  NcclApi& n = nccl();
+  if (n.ok && comm->comm) n.CommDestroy(comm->comm);
+  delete comm;
+  return FB_OK;
+}
+
+FB_API int32_t fb_comm_rank(const fb_comm* comm) { return comm ? comm->rank : -1; }
+FB_API int32_t fb_comm_size(const fb_comm* comm) { return comm ? comm->nranks : -1; }
+
+FB_API int32_t fb_allreduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op) {
+  FB_REQUIRE(comm, FB_ERR_INVALID_ARG, "fb_allreduce: comm is NULL");
+  FB_REQUIRE(count >= 0 && (op == FB_OP_SUM || op == FB_OP_AVG), FB_ERR_INVALID_ARG, "fb_allreduce: bad count or op");
+  if (count == 0) return FB_OK;
+  FB_REQUIRE(send && recv, FB_ERR_INVALID_ARG, "fb_allreduce: NULL pointer");
+  FB_NCCL_READY();
+  const int rc = n.AllReduce(send, recv, (size_t)count, NCCL_FLOAT32, op == FB_OP_AVG ? NCCL_AVG : NCCL_SUM, comm->comm,
+                             (cudaStream_t)stream);
+  if (rc != 0) return nccl_fail("ncclAllReduce", rc);
+  return FB_OK;
+}
+
+FB_API int32_t fb_bcast(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t root) {
+  FB_REQUIRE(comm, FB_ERR_INVALID_ARG, "fb_bcast: comm is NULL");
+  FB_REQUIRE(count >= 0 && root >= 0 && root < comm->nranks, FB_ERR_INVALID_ARG, "fb_bcast: bad count or root");
+  if (count == 0) return FB_OK;
+  FB_REQUIRE(send && recv, FB_ERR_INVALID_ARG, "fb_bcast: NULL pointer");
+  FB_NCCL_READY();
+  const int rc = n.Broadcast(send, recv, (size_t)count, NCCL_FLOAT32, root, comm->comm, (cudaStream_t)stream);
+  if (rc != 0) return nccl_fail("ncclBroadcast", rc);
+  return FB_OK;
+}
+
+FB_API int32_t fb_reduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op,
+                         int32_t root) {
+  FB_REQUIRE(comm, FB_ERR_INVALID_ARG, "fb_reduce: comm is NULL");
+  FB_REQUIRE(count >= 0 && (op == FB_OP_SUM || op == FB_OP_AVG) && root >= 0 && root < comm->nranks, FB_ERR_INVALID_ARG,
+             "fb_reduce: bad count, op or root");
+  if (count == 0) return FB_OK;
+  FB_REQUIRE(send && recv, FB_ERR_INVALID_ARG, "fb_reduce: NULL pointer");
+  FB_NCCL_READY();
+  const int rc = n.Reduce(send, recv, (size_t)count, NCCL_FLOAT32, op == FB_OP_AVG ? NCCL_AVG : NCCL_SUM, root, comm->comm,
+                          (cudaStream_t)stream);
+  if (rc != 0) return nccl_fail("ncclReduce", rc);
+  return FB_OK;
+}
+
+FB_API int32_t fb_comm_async_error(fb_comm* comm, int32_t* out_host) {
+  FB_REQUIRE(comm && out_host, FB_ERR_INVALID_ARG, "fb_comm_async_error: NULL pointer");
+  FB_NCCL_READY();
+  *out_host = 0;
+  if (!n.CommGetAsyncError) return FB_OK;
+  int err = 0;
+  const int rc = n.CommGetAsyncError(comm->comm, &err);
+  if (rc != 0) return nccl_fail("ncclCommGetAsyncError", rc);
+  *out_host = err;
+  return FB_OK;
+}

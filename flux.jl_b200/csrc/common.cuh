@@ -1,0 +1,185 @@
+// Shared declarations of libfluxb200: context, error reporting, launch helpers, activations.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/fluxb200.h"
+
+#define FB_API extern "C" __attribute__((visibility("default")))
+
+// ---------------------------------------------------------------------------- context ---
+struct fb_ctx {
+  int device;
+  int sm_count;
+  size_t smem_optin;
+  void* scratch;         // device arena, grown on demand, reused by every call on this context
+  size_t scratch_bytes;
+  int32_t* dev_error;    // device error word written by kernels whose bounded waits ran out
+  void* tmap_cache;      // opaque (gemm_tc.cu): encoded TMA descriptors keyed by (ptr, shape)
+};
+
+// thread-local last-error message
+void fb_set_error(const char* fmt, ...);
+int32_t fb_fail(int32_t code, const char* fmt, ...);
+
+// Returns a pointer into the context arena of at least `bytes` (256-byte aligned); grows the arena
+// (stream-ordered free of the old block) when it is too small.  NULL on allocation failure.
+void* fb_scratch(fb_ctx* ctx, cudaStream_t stream, size_t bytes);
+
+#define FB_CHECK_CTX(ctx)                                                   \
+  do {                                                                      \
+    if ((ctx) == nullptr) return fb_fail(FB_ERR_INVALID_ARG, "%s: ctx is NULL", __func__); \
+  } while (0)
+
+#define FB_CUDA(call)                                                                        \
+  do {                                                                                       \
+    cudaError_t e__ = (call);                                                                \
+    if (e__ != cudaSuccess)                                                                  \
+      return fb_fail(FB_ERR_CUDA, "%s: %s failed: %s", __func__, #call, cudaGetErrorString(e__)); \
+  } while (0)
+
+extern unsigned long long g_fb_kernel_launches;   // kernels launched by this library in this process
+
+#define FB_LAUNCH_CHECK()                                                                     \
+  do {                                                                                        \
+    ++g_fb_kernel_launches;                                                                   \
+    cudaError_t e__ = cudaGetLastError();                                                     \
+    if (e__ != cudaSuccess)                                                                   \
+      return fb_fail(FB_ERR_CUDA, "%s: kernel launch failed: %s", __func__, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define FB_REQUIRE(cond, code, ...)                    \
+  do {                                                 \
+    if (!(cond)) return fb_fail((code), __VA_ARGS__);  \
+  } while (0)
+
+static inline bool fb_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ------------------------------------------------------------------------ activations ---
+// Evaluated in fp32.  *_from_y derivatives use the forward output where that is enough
+// (relu / tanh / sigmoid), the gelu flavours need the pre-activation z.
+__device__ __forceinline__ float fb_sigmoidf(float z) { return 1.0f / (1.0f + __expf(-z)); }
+
+__device__ __forceinline__ float fb_act_apply(int act, float z) {
+  switch (act) {
+    case FB_ACT_RELU: return fmaxf(z, 0.0f);
+    case FB_ACT_TANH: return tanhf(z);
+    case FB_ACT_SIGMOID: return 1.0f / (1.0f + expf(-z));
+    case FB_ACT_GELU_TANH: {
+      const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+      return 0.5f * z * (1.0f + tanhf(u));
+    }
+    case FB_ACT_GELU_ERF: return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+    default: return z;
+  }
+}
+
+// derivative at pre-activation z
+__device__ __forceinline__ float fb_act_grad_z(int act, float z) {
+  switch (act) {
+    case FB_ACT_RELU: return z > 0.0f ? 1.0f : 0.0f;
+    case FB_ACT_TANH: { const float t = tanhf(z); return 1.0f - t * t; }
+    case FB_ACT_SIGMOID: { const float s = 1.0f / (1.0f + expf(-z)); return s * (1.0f - s); }
+    case FB_ACT_GELU_TANH: {
+      const float z2 = z * z;
+      const float u = 0.7978845608028654f * (z + 0.044715f * z * z2);
+      const float t = tanhf(u);
+      const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * z2);
+      return 0.5f * (1.0f + t) + 0.5f * z * (1.0f - t * t) * du;
+    }
+    case FB_ACT_GELU_ERF: {
+      const float pdf = 0.3989422804014327f * expf(-0.5f * z * z);
+      return 0.5f * (1.0f + erff(z * 0.7071067811865476f)) + z * pdf;
+    }
+    default: return 1.0f;
+  }
+}
+
+// derivative from the forward output y (valid for identity / relu / tanh / sigmoid)
+__device__ __forceinline__ float fb_act_grad_y(int act, float y) {
+  switch (act) {
+    case FB_ACT_RELU: return y > 0.0f ? 1.0f : 0.0f;
+    case FB_ACT_TANH: return 1.0f - y * y;
+    case FB_ACT_SIGMOID: return y * (1.0f - y);
+    default: return 1.0f;
+  }
+}
+
+static inline bool fb_act_valid(int act) { return act >= FB_ACT_IDENTITY && act <= FB_ACT_GELU_ERF; }
+static inline bool fb_act_needs_z(int act) { return act == FB_ACT_GELU_TANH || act == FB_ACT_GELU_ERF; }
+
+// -------------------------------------------------------------------------- reductions ---
+__device__ __forceinline__ float fb_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float fb_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; `sh` must hold at least 32 floats.  All threads get the result.
+__device__ __forceinline__ float fb_block_sum(float v, float* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = fb_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? sh[lane] : 0.0f;
+  r = fb_warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float fb_block_max(float v, float* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = fb_warp_max(v);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? sh[lane] : -INFINITY;
+  r = fb_warp_max(r);
+  return r;
+}
+
+// Welford / Chan merge of (count, mean, M2) partials
+__device__ __forceinline__ void fb_welford_merge(float& n_a, float& mean_a, float& m2_a, float n_b,
+                                                 float mean_b, float m2_b) {
+  if (n_b == 0.0f) return;
+  const float n = n_a + n_b;
+  const float delta = mean_b - mean_a;
+  const float f = n_b / n;
+  mean_a += delta * f;
+  m2_a += m2_b + delta * delta * n_a * f;
+  n_a = n;
+}
+
+// ---------------------------------------------------------- internal cross-file entry points ---
+// Row-major core GEMM: C[M][N] (ldc) = A*B with A given either K-major (A[m*lda + k]) or MN-major
+// (A[k*lda + m]), same for B (K-major: B[n*ldb + k]; MN-major: B[k*ldb + n]).  Epilogue: optional bias
+// along n, activation, optional pre-activation store, optional accumulate into C.
+struct fb_gemm_args {
+  const float* A; int64_t lda; int a_mn_major;
+  const float* B; int64_t ldb; int b_mn_major;
+  float* C; int64_t ldc;
+  float* Z;              // optional pre-activation (same layout as C), or NULL
+  const float* bias_n;   // optional bias indexed by n, or NULL
+  const float* bias_m;   // optional bias indexed by m, or NULL
+  int64_t M, N, K;
+  int act;
+  int accumulate;
+};
+int32_t fb_gemm_simt_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a);
+// tensor-core path; returns FB_ERR_UNSUPPORTED (without raising an error message) when the shape or
+// alignment is outside what the kernel handles, so the dispatcher can pick the FMA kernel.
+int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a, int passes);
+bool fb_gemm_tc_supported(const fb_gemm_args& a);
+int32_t fb_gemm_dispatch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a, int precision);
+void fb_tmap_cache_destroy(fb_ctx* ctx);
+
+// delta = dy .* act'(.) and db[j] = sum_rows delta[row][j]   (rows x cols row-major; cols = out_dim)
+int32_t fb_act_bwd_colsum(fb_ctx* ctx, cudaStream_t stream, int act, const float* dy, const float* y,
+                          const float* z, float* delta, float* db, int64_t rows, int64_t cols);

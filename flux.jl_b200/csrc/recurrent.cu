@@ -1,0 +1,581 @@
+// Recurrence over LSTMCell / GRUCell: fused scan forward and BPTT backward.
+//
+// Layout: Julia x[in, T, B] is read as [B][T][in]; row (b, t) = b*T + t.  out[H, T, B] likewise.
+// Forward:  (1) one GEMM over all T*B columns for the input projection Gx = x*Wi' + b,
+//           (2) T step kernels; a block owns HU hidden units (NG*HU rows of Wh, staged in shared memory),
+//               streams h_{t-1} through shared memory, and finishes the gate math for its units in place.
+// Backward: T step kernels in reverse (gate derivatives, then dh_{t-1} = Wh' * dgates), followed by three
+//           GEMMs over all T*B columns for dWi, dWh and dx.
+// Steps are ordered by the stream (one launch per step), so no kernel ever waits on another block.
+#include "common.cuh"
+
+namespace {
+
+constexpr int RT = 256;      // threads per block
+constexpr int BC = 64;       // batch columns per pass
+constexpr int KC = 128;      // k values staged per pass
+constexpr int HS = KC + 4;   // padded row stride of the staged h tile (float4-aligned, conflict-free)
+
+// acc[r] += sum_k Ws[r][k] * v[b][k] for this thread's b and its quarter of every k-chunk.
+//   Ws: shared [NR][kp] (kp = K rounded up to KC, zero padded); v: global rows of length K at stride ldv
+//   (NULL = all zeros); vs: shared [BC][HS] staging tile.
+template <int NR>
+__device__ __forceinline__ void rows_times_vec(const float* __restrict__ Ws, int kp, const float* __restrict__ v,
+                                               int64_t ldv, int K, int b0, int B, float* __restrict__ vs,
+                                               float* acc) {
+  const int b = threadIdx.x & (BC - 1), kq = threadIdx.x >> 6;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
+  if (v == nullptr) return;
+  for (int kc = 0; kc < kp; kc += KC) {
+    __syncthreads();
+    // stage v[b0 .. b0+BC)[kc .. kc+KC): 32 consecutive threads read 128 consecutive floats
+    for (int e = threadIdx.x; e < BC * KC; e += RT) {
+      const int bb = e / KC, kk = e % KC;
+      const int gb = b0 + bb, gk = kc + kk;
+      vs[bb * HS + kk] = (gb < B && gk < K) ? __ldg(v + (int64_t)gb * ldv + gk) : 0.0f;
+    }
+    __syncthreads();
+    const float4* vrow = (const float4*)(vs + b * HS + kq * (KC / 4));
+#pragma unroll 2
+    for (int k4 = 0; k4 < KC / 16; ++k4) {
+      const float4 hv = vrow[k4];
+      const int kbase = kc + kq * (KC / 4) + k4 * 4;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const float4 w = *(const float4*)(Ws + r * kp + kbase);
+        acc[r] = fmaf(w.x, hv.x, acc[r]);
+        acc[r] = fmaf(w.y, hv.y, acc[r]);
+        acc[r] = fmaf(w.z, hv.z, acc[r]);
+        acc[r] = fmaf(w.w, hv.w, acc[r]);
+      }
+    }
+  }
+}
+
+// Sum the four k-quarter partials through shared memory: red[kq][b][r]; result for (b, r) in red[0][b][r].
+template <int NR>
+__device__ __forceinline__ void reduce_quarters(float* __restrict__ red, const float* acc) {
+  const int b = threadIdx.x & (BC - 1), kq = threadIdx.x >> 6;
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < NR; ++r) red[(kq * BC + b) * (NR + 1) + r] = acc[r];
+  __syncthreads();
+  for (int e = threadIdx.x; e < BC * NR; e += RT) {
+    const int bb = e / NR, r = e % NR;
+    float s = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) s += red[(q * BC + bb) * (NR + 1) + r];
+    red[bb * (NR + 1) + r] = s;   // (0, bb, r) is only read by this thread in this pass
+  }
+  __syncthreads();
+}
+
+// Stage the NG*HU rows of Wh that belong to units [u0, u0+HU) into shared memory, zero padded to kp.
+// Wh memory is [H (k)][NG*H (row)] (Julia Wh[NG*H, H]); row r = g*H + u.
+template <int NG, int HU>
+__device__ __forceinline__ void stage_w_rows(float* __restrict__ Ws, int kp, const float* __restrict__ Wh, int H, int u0) {
+  for (int e = threadIdx.x; e < NG * HU * kp; e += RT) {
+    const int k = e / (NG * HU), rr = e % (NG * HU);   // rr fastest: consecutive threads read neighbouring units
+    const int g = rr / HU, u = rr % HU;
+    float w = 0.0f;
+    if (k < H && u0 + u < H) w = __ldg(Wh + (int64_t)k * (NG * H) + g * H + u0 + u);
+    Ws[rr * kp + k] = w;
+  }
+}
+
+// ------------------------------------------------------------------------------- LSTM forward step ---
+template <int HU>
+__global__ void __launch_bounds__(RT)
+lstm_fwd_step_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, const float* __restrict__ hprev,
+                     int64_t ldh, const float* __restrict__ cprev, int64_t ldc, float* __restrict__ out_t,
+                     int64_t ldo, float* __restrict__ gates_t, float* __restrict__ c_t, int64_t ldcache_g,
+                     int64_t ldcache_c, float* __restrict__ hT, float* __restrict__ cT, int H, int B, int64_t ldgx) {
+  extern __shared__ float sm[];
+  const int kp = (H + KC - 1) / KC * KC;
+  constexpr int NR = 4 * HU;
+  float* Ws = sm;                         // [NR][kp]
+  float* vs = Ws + NR * kp;               // [BC][HS]
+  float* red = vs + BC * HS;              // [4][BC][NR+1]
+  const int u0 = blockIdx.x * HU;
+  stage_w_rows<4, HU>(Ws, kp, Wh, H, u0);
+  for (int b0 = 0; b0 < B; b0 += BC) {
+    float acc[NR];
+    rows_times_vec<NR>(Ws, kp, hprev, ldh, H, b0, B, vs, acc);
+    reduce_quarters<NR>(red, acc);
+    for (int e = threadIdx.x; e < BC * HU; e += RT) {
+      const int bb = e / HU, u = e % HU;
+      const int gb = b0 + bb, gu = u0 + u;
+      if (gb < B && gu < H) {
+        const float* pre = red + bb * (NR + 1);
+        const float* gxr = gx + (int64_t)gb * ldgx;
+        const float zi = pre[0 * HU + u] + gxr[gu];
+        const float zf = pre[1 * HU + u] + gxr[H + gu];
+        const float zg = pre[2 * HU + u] + gxr[2 * H + gu];
+        const float zo = pre[3 * HU + u] + gxr[3 * H + gu];
+        const float ig = 1.0f / (1.0f + expf(-zi)), fg = 1.0f / (1.0f + expf(-zf));
+        const float gg = tanhf(zg), og = 1.0f / (1.0f + expf(-zo));
+        const float cp = cprev ? cprev[(int64_t)gb * ldc + gu] : 0.0f;
+        const float cn = fg * cp + ig * gg;
+        const float hn = og * tanhf(cn);
+        out_t[(int64_t)gb * ldo + gu] = hn;
+        if (gates_t) {
+          float* gr = gates_t + (int64_t)gb * ldcache_g;
+          gr[gu] = ig; gr[H + gu] = fg; gr[2 * H + gu] = gg; gr[3 * H + gu] = og;
+        }
+        c_t[(int64_t)gb * ldcache_c + gu] = cn;
+        if (hT) { hT[(int64_t)gb * H + gu] = hn; cT[(int64_t)gb * H + gu] = cn; }
+      }
+    }
+  }
+}
+
+// gate derivatives for step t, in place over the cached gates:
+//   dh = dout_t + dh_rec; do = dh*tanh(c); dc += dh*o*(1-tanh(c)^2); di = dc*g; dg = dc*i; df = dc*c_prev
+//   gates <- (di*i*(1-i), df*f*(1-f), dg*(1-g^2), do*o*(1-o)); dc_prev = dc*f
+__global__ void __launch_bounds__(RT)
+lstm_bwd_gates_kernel(float* __restrict__ gates_t, int64_t ldg, const float* __restrict__ c_t,
+                      const float* __restrict__ c_prev, int64_t ldc, int64_t ldcp,
+                      const float* __restrict__ dout_t, int64_t ldo, const float* __restrict__ dh_rec,
+                      float* __restrict__ dc, int H, int B) {
+  const int64_t total = (int64_t)B * H;
+  for (int64_t e = (int64_t)blockIdx.x * RT + threadIdx.x; e < total; e += (int64_t)gridDim.x * RT) {
+    const int b = (int)(e / H), u = (int)(e % H);
+    float* gr = gates_t + (int64_t)b * ldg;
+    const float ig = gr[u], fg = gr[H + u], gg = gr[2 * H + u], og = gr[3 * H + u];
+    const float tc = tanhf(c_t[(int64_t)b * ldc + u]);
+    const float cp = c_prev ? c_prev[(int64_t)b * ldcp + u] : 0.0f;
+    const float dh = dout_t[(int64_t)b * ldo + u] + (dh_rec ? dh_rec[e] : 0.0f);
+    const float d_o = dh * tc;
+    const float dcc = dc[e] + dh * og * (1.0f - tc * tc);
+    gr[u] = dcc * gg * ig * (1.0f - ig);
+    gr[H + u] = dcc * cp * fg * (1.0f - fg);
+    gr[2 * H + u] = dcc * ig * (1.0f - gg * gg);
+    gr[3 * H + u] = d_o * og * (1.0f - og);
+    dc[e] = dcc * fg;
+  }
+}
+
+// dh_rec[b][u] = (add ? add[b][u] : 0) + sum_r Wm[u][r] * dg[b][r], r over R = NG*H.  Wm is Wh memory [H][R],
+// so the HU rows of a block are contiguous.  A block owns HU units.
+template <int HU>
+__global__ void __launch_bounds__(RT)
+rnn_bwd_dh_kernel(const float* __restrict__ Wh, const float* __restrict__ dg, int64_t ldg, const float* __restrict__ add,
+                  float* __restrict__ dh_rec, int H, int R, int B) {
+  extern __shared__ float sm[];
+  const int kp = (R + KC - 1) / KC * KC;
+  float* Ws = sm;                 // [HU][kp]
+  float* vs = Ws + HU * kp;       // [BC][HS]
+  float* red = vs + BC * HS;      // [4][BC][HU+1]
+  const int u0 = blockIdx.x * HU;
+  for (int e = threadIdx.x; e < HU * kp; e += RT) {
+    const int u = e / kp, k = e % kp;
+    Ws[e] = (u0 + u < H && k < R) ? __ldg(Wh + (int64_t)(u0 + u) * R + k) : 0.0f;
+  }
+  for (int b0 = 0; b0 < B; b0 += BC) {
+    float acc[HU];
+    rows_times_vec<HU>(Ws, kp, dg, ldg, R, b0, B, vs, acc);
+    reduce_quarters<HU>(red, acc);
+    for (int e = threadIdx.x; e < BC * HU; e += RT) {
+      const int bb = e / HU, u = e % HU;
+      const int gb = b0 + bb, gu = u0 + u;
+      if (gb < B && gu < H) {
+        const int64_t o = (int64_t)gb * H + gu;
+        dh_rec[o] = red[bb * (HU + 1) + u] + (add ? add[o] : 0.0f);
+      }
+    }
+  }
+}
+
+// -------------------------------------------------------------------------------- GRU forward step ---
+// cache row layout per (b, t): [r (H)][z (H)][hc (H)][gh3 (H)]
+template <int HU>
+__global__ void __launch_bounds__(RT)
+gru_fwd_step_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, int64_t ldgx,
+                    const float* __restrict__ hprev, int64_t ldh, float* __restrict__ out_t, int64_t ldo,
+                    float* __restrict__ cache_t, int64_t ldcache, float* __restrict__ hT, int H, int B) {
+  extern __shared__ float sm[];
+  const int kp = (H + KC - 1) / KC * KC;
+  constexpr int NR = 3 * HU;
+  float* Ws = sm;
+  float* vs = Ws + NR * kp;
+  float* red = vs + BC * HS;
+  const int u0 = blockIdx.x * HU;
+  stage_w_rows<3, HU>(Ws, kp, Wh, H, u0);
+  for (int b0 = 0; b0 < B; b0 += BC) {
+    float acc[NR];
+    rows_times_vec<NR>(Ws, kp, hprev, ldh, H, b0, B, vs, acc);
+    reduce_quarters<NR>(red, acc);
+    for (int e = threadIdx.x; e < BC * HU; e += RT) {
+      const int bb = e / HU, u = e % HU;
+      const int gb = b0 + bb, gu = u0 + u;
+      if (gb < B && gu < H) {
+        const float* pre = red + bb * (NR + 1);
+        const float* gxr = gx + (int64_t)gb * ldgx;   // includes the bias
+        const float gh3 = pre[2 * HU + u];
+        const float r = 1.0f / (1.0f + expf(-(gxr[gu] + pre[u])));
+        const float z = 1.0f / (1.0f + expf(-(gxr[H + gu] + pre[HU + u])));
+        const float hc = tanhf(gxr[2 * H + gu] + r * gh3);
+        const float hp = hprev ? hprev[(int64_t)gb * ldh + gu] : 0.0f;
+        const float hn = (1.0f - z) * hc + z * hp;
+        out_t[(int64_t)gb * ldo + gu] = hn;
+        if (cache_t) {
+          float* cr = cache_t + (int64_t)gb * ldcache;
+          cr[gu] = r; cr[H + gu] = z; cr[2 * H + gu] = hc; cr[3 * H + gu] = gh3;
+        }
+        if (hT) hT[(int64_t)gb * H + gu] = hn;
+      }
+    }
+  }
+}
+
+// GRU gate derivatives for step t.  Writes dgx_t = (da1, da2, da3) and dgh_t = (da1, da2, da3*r), and
+// dh_direct = dh*z (the part of dh_{t-1} that does not go through Wh).
+__global__ void __launch_bounds__(RT)
+gru_bwd_gates_kernel(const float* __restrict__ cache_t, int64_t ldcache, const float* __restrict__ hprev, int64_t ldh,
+                     const float* __restrict__ dout_t, int64_t ldo, const float* __restrict__ dh_rec,
+                     float* __restrict__ dgx_t, float* __restrict__ dgh_t, int64_t ldd, float* __restrict__ dh_direct,
+                     int H, int B) {
+  const int64_t total = (int64_t)B * H;
+  for (int64_t e = (int64_t)blockIdx.x * RT + threadIdx.x; e < total; e += (int64_t)gridDim.x * RT) {
+    const int b = (int)(e / H), u = (int)(e % H);
+    const float* cr = cache_t + (int64_t)b * ldcache;
+    const float r = cr[u], z = cr[H + u], hc = cr[2 * H + u], gh3 = cr[3 * H + u];
+    const float hp = hprev ? hprev[(int64_t)b * ldh + u] : 0.0f;
+    const float dh = dout_t[(int64_t)b * ldo + u] + (dh_rec ? dh_rec[e] : 0.0f);
+    const float da3 = dh * (1.0f - z) * (1.0f - hc * hc);
+    const float da2 = dh * (hp - hc) * z * (1.0f - z);
+    const float da1 = da3 * gh3 * r * (1.0f - r);
+    float* x_ = dgx_t + (int64_t)b * ldd;
+    float* h_ = dgh_t + (int64_t)b * ldd;
+    x_[u] = da1; x_[H + u] = da2; x_[2 * H + u] = da3;
+    h_[u] = da1; h_[H + u] = da2; h_[2 * H + u] = da3 * r;
+    dh_direct[e] = dh * z;
+  }
+}
+
+// hprev_all[(b, t)] = t == 0 ? h0[b] (or 0) : out[(b, t-1)]
+__global__ void __launch_bounds__(RT)
+shift_prev_kernel(const float* __restrict__ out, const float* __restrict__ h0, float* __restrict__ hprev_all, int H,
+                  int64_t T, int64_t B) {
+  const int64_t total = B * T * H;
+  for (int64_t e = (int64_t)blockIdx.x * RT + threadIdx.x; e < total; e += (int64_t)gridDim.x * RT) {
+    const int64_t row = e / H;
+    const int u = (int)(e % H);
+    const int64_t t = row % T, b = row / T;
+    hprev_all[e] = t == 0 ? (h0 ? h0[b * H + u] : 0.0f) : out[e - H];
+  }
+}
+
+// db[j] = sum over rows of dg[row][j]
+int32_t colsum_rows(fb_ctx* ctx, cudaStream_t stream, const float* dg, float* db, int64_t rows, int64_t cols) {
+  return fb_act_bwd_colsum(ctx, stream, FB_ACT_IDENTITY, dg, nullptr, nullptr, nullptr, db, rows, cols);
+}
+
+int pick_hu(int ng, int H, size_t smem_optin, size_t extra) {
+  const int kp = (H + KC - 1) / KC * KC;
+  const int cand[3] = {4, 2, 1};
+  for (int i = 0; i < 3; ++i) {
+    const size_t need = (size_t)(ng * cand[i]) * kp * 4 + extra + (size_t)4 * BC * (ng * cand[i] + 1) * 4;
+    if (need <= smem_optin) return cand[i];
+  }
+  return 0;
+}
+
+size_t fwd_smem(int ng, int hu, int H) {
+  const int kp = (H + KC - 1) / KC * KC;
+  return (size_t)(ng * hu) * kp * 4 + (size_t)BC * HS * 4 + (size_t)4 * BC * (ng * hu + 1) * 4;
+}
+
+size_t dh_smem(int hu, int R) {
+  const int kp = (R + KC - 1) / KC * KC;
+  return (size_t)hu * kp * 4 + (size_t)BC * HS * 4 + (size_t)4 * BC * (hu + 1) * 4;
+}
+
+int32_t check_dims(const char* fn, int64_t in_dim, int64_t H, int64_t T, int64_t B) {
+  FB_REQUIRE(in_dim >= 1 && H >= 1 && T >= 0 && B >= 0, FB_ERR_SHAPE, "%s: bad shape in=%lld H=%lld T=%lld B=%lld", fn,
+             (long long)in_dim, (long long)H, (long long)T, (long long)B);
+  FB_REQUIRE(H <= 16384 && B <= (1 << 24) && T <= (1 << 24), FB_ERR_SHAPE, "%s: dimension too large", fn);
+  return FB_OK;
+}
+
+}  // namespace
+
+FB_API int64_t fb_lstm_cache_bytes(int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch) {
+  (void)in_dim;
+  // gates [B*T][4H] + cell states [B*T][H] + input projection [B*T][4H] (reused as scratch by the backward pass)
+  return (int64_t)sizeof(float) * seq_len * batch * hidden * 9;
+}
+
+FB_API int64_t fb_gru_cache_bytes(int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch) {
+  (void)in_dim;
+  // (r, z, hc, gh3) [B*T][4H] + input projection [B*T][3H] + recurrent-side gate derivatives [B*T][3H]
+  // + shifted hidden states [B*T][H]
+  return (int64_t)sizeof(float) * seq_len * batch * hidden * 11;
+}
+
+FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const float* Wh, const float* b, const float* x,
+                           const float* h0, const float* c0, float* out, float* hT, float* cT, void* cache,
+                           int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch) {
+  FB_CHECK_CTX(ctx);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int32_t st = check_dims("fb_lstm_fwd", in_dim, hidden, seq_len, batch);
+  if (st != FB_OK) return st;
+  if (seq_len == 0 || batch == 0) return FB_OK;
+  FB_REQUIRE(Wi && Wh && x && out, FB_ERR_INVALID_ARG, "fb_lstm_fwd: NULL pointer");
+  FB_REQUIRE((hT == nullptr) == (cT == nullptr), FB_ERR_INVALID_ARG, "fb_lstm_fwd: hT and cT must both be given or both NULL");
+  const int H = (int)hidden, B = (int)batch;
+  const int64_t T = seq_len, rows = T * batch;
+  float *gates, *cst, *gx;
+  if (cache) {
+    gates = (float*)cache;
+    cst = gates + rows * 4 * H;
+    gx = cst + rows * H;
+  } else {
+    float* ws = (float*)fb_scratch(ctx, stream, (size_t)(rows * 4 * H + 2 * (int64_t)B * H) * sizeof(float));
+    if (!ws) return FB_ERR_ALLOC;
+    gates = nullptr;
+    gx = ws;
+    cst = ws + rows * 4 * H;   // two [B][H] ping-pong cell buffers
+  }
+  // (1) input projection for every (b, t): gx[rows][4H] = x[rows][in] * Wi' + b
+  fb_gemm_args a;
+  a.A = x; a.lda = in_dim; a.a_mn_major = 0;
+  a.B = Wi; a.ldb = 4 * hidden; a.b_mn_major = 1;
+  a.C = gx; a.ldc = 4 * hidden; a.Z = nullptr; a.bias_n = b; a.bias_m = nullptr;
+  a.M = rows; a.N = 4 * hidden; a.K = in_dim; a.act = FB_ACT_IDENTITY; a.accumulate = 0;
+  st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+  if (st != FB_OK) return st;
+  // (2) time loop
+  const int hu = pick_hu(4, H, ctx->smem_optin, (size_t)BC * HS * 4);
+  FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_lstm_fwd: hidden size %d does not fit the step kernel's shared memory", H);
+  const size_t smem = fwd_smem(4, hu, H);
+  auto kern = hu == 4 ? lstm_fwd_step_kernel<4> : hu == 2 ? lstm_fwd_step_kernel<2> : lstm_fwd_step_kernel<1>;
+  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const unsigned grid = (unsigned)((H + hu - 1) / hu);
+  const int64_t ldrow = T * H;       // stride between batch rows of out / cached c at a fixed t
+  for (int64_t t = 0; t < T; ++t) {
+    const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
+    const int64_t ldh = t == 0 ? H : ldrow;
+    const float* cprev;
+    int64_t ldcp;
+    float* c_t;
+    int64_t ldct;
+    if (cache) {
+      cprev = t == 0 ? c0 : cst + (t - 1) * H;
+      ldcp = t == 0 ? H : ldrow;
+      c_t = cst + t * H;
+      ldct = ldrow;
+    } else {
+      cprev = t == 0 ? c0 : cst + ((t - 1) & 1) * (int64_t)B * H;
+      ldcp = H;
+      c_t = cst + (t & 1) * (int64_t)B * H;
+      ldct = H;
+    }
+    // the kernel reads cprev at stride ldc and writes c_t at stride ldcache_c; both are passed
+    kern<<<grid, RT, smem, stream>>>(Wh, gx + t * 4 * H, hprev, ldh, cprev, ldcp, out + t * H, ldrow,
+                                     gates ? gates + t * 4 * H : nullptr, c_t, T * 4 * H, ldct,
+                                     (t == T - 1) ? hT : nullptr, (t == T - 1) ? cT : nullptr, H, B, T * 4 * H);
+    FB_LAUNCH_CHECK();
+  }
+  return FB_OK;
+}
+
+FB_API int32_t fb_lstm_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const float* Wh, const float* x,
+                           const float* h0, const float* c0, const float* out, const void* cache, const float* dout,
+                           const float* dhT, const float* dcT,
+                           float* dWi, float* dWh, float* db, float* dx, int64_t in_dim, int64_t hidden,
+                           int64_t seq_len, int64_t batch) {
+  FB_CHECK_CTX(ctx);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int32_t st = check_dims("fb_lstm_bwd", in_dim, hidden, seq_len, batch);
+  if (st != FB_OK) return st;
+  FB_REQUIRE(seq_len >= 1 && batch >= 1, FB_ERR_SHAPE, "fb_lstm_bwd: empty sequence or batch");
+  FB_REQUIRE(Wi && Wh && x && out && cache && dout && dWi && dWh, FB_ERR_INVALID_ARG, "fb_lstm_bwd: NULL pointer");
+  const int H = (int)hidden, B = (int)batch;
+  const int64_t T = seq_len, rows = T * batch, ldrow = T * H;
+  float* gates = (float*)cache;              // overwritten in place by the gate derivatives
+  const float* cst = gates + rows * 4 * H;
+  float* ws = (float*)fb_scratch(ctx, stream, (size_t)(3 * (int64_t)B * H) * sizeof(float));
+  if (!ws) return FB_ERR_ALLOC;
+  float* dc = ws;                            // [B][H]
+  float* dh_a = ws + (int64_t)B * H;         // ping-pong recurrent dh
+  float* dh_b = dh_a + (int64_t)B * H;
+  if (dcT) FB_CUDA(cudaMemcpyAsync(dc, dcT, (size_t)B * H * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  else FB_CUDA(cudaMemsetAsync(dc, 0, (size_t)B * H * sizeof(float), stream));
+  const int hu = pick_hu(1, 4 * H, ctx->smem_optin, (size_t)BC * HS * 4);
+  FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_lstm_bwd: hidden size %d does not fit the step kernel's shared memory", H);
+  const size_t smem = dh_smem(hu, 4 * H);
+  auto kern = hu == 4 ? rnn_bwd_dh_kernel<4> : hu == 2 ? rnn_bwd_dh_kernel<2> : rnn_bwd_dh_kernel<1>;
+  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const unsigned grid_dh = (unsigned)((H + hu - 1) / hu);
+  int64_t eb = ((int64_t)B * H + RT - 1) / RT;
+  if (eb > ctx->sm_count * 8) eb = ctx->sm_count * 8;
+  const float* dh_rec = dhT;                 // recurrent dh entering step t (dhT at the last step)
+  for (int64_t t = T - 1; t >= 0; --t) {
+    float* g_t = gates + t * 4 * H;
+    const float* c_prev = t == 0 ? c0 : cst + (t - 1) * H;
+    lstm_bwd_gates_kernel<<<(unsigned)eb, RT, 0, stream>>>(g_t, T * 4 * H, cst + t * H, c_prev, ldrow,
+                                                           t == 0 ? (int64_t)H : ldrow, dout + t * H, ldrow, dh_rec,
+                                                           dc, H, B);
+    FB_LAUNCH_CHECK();
+    if (t > 0) {
+      float* dh_next = (dh_rec == dh_a) ? dh_b : dh_a;
+      kern<<<grid_dh, RT, smem, stream>>>(Wh, g_t, T * 4 * H, nullptr, dh_next, H, 4 * H, B);
+      FB_LAUNCH_CHECK();
+      dh_rec = dh_next;
+    }
+  }
+  // bulk GEMMs over all T*B columns (dg = gates buffer, [rows][4H])
+  fb_gemm_args a;
+  a.Z = nullptr; a.bias_n = nullptr; a.bias_m = nullptr; a.act = FB_ACT_IDENTITY; a.accumulate = 0;
+  // dWi memory [in][4H] = x^T dg
+  a.A = x; a.lda = in_dim; a.a_mn_major = 1;
+  a.B = gates; a.ldb = 4 * hidden; a.b_mn_major = 1;
+  a.C = dWi; a.ldc = 4 * hidden; a.M = in_dim; a.N = 4 * hidden; a.K = rows;
+  st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+  if (st != FB_OK) return st;
+  // dWh memory [H][4H] = hprev^T dg with hprev(b, t) = out(b, t-1) (h0 at t = 0); the shifted copy lives in
+  // the cache's input-projection region, which the backward pass no longer needs.
+  {
+    float* hprev_all = gates + rows * 5 * H;
+    int64_t sb = (rows * H + RT - 1) / RT;
+    if (sb > (int64_t)ctx->sm_count * 16) sb = (int64_t)ctx->sm_count * 16;
+    shift_prev_kernel<<<(unsigned)sb, RT, 0, stream>>>(out, h0, hprev_all, H, T, batch);
+    FB_LAUNCH_CHECK();
+    a.A = hprev_all; a.lda = hidden; a.a_mn_major = 1;
+    a.B = gates; a.ldb = 4 * hidden; a.b_mn_major = 1;
+    a.C = dWh; a.ldc = 4 * hidden; a.M = hidden; a.N = 4 * hidden; a.K = rows;
+    st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+    if (st != FB_OK) return st;
+  }
+  a.accumulate = 0;
+  if (db) {
+    st = colsum_rows(ctx, stream, gates, db, rows, 4 * hidden);
+    if (st != FB_OK) return st;
+  }
+  if (dx) {
+    // dx[rows][in] = dg[rows][4H] * Wi (memory [in][4H]) ^T
+    a.A = gates; a.lda = 4 * hidden; a.a_mn_major = 0;
+    a.B = Wi; a.ldb = 4 * hidden; a.b_mn_major = 0;
+    a.C = dx; a.ldc = in_dim; a.M = rows; a.N = in_dim; a.K = 4 * hidden;
+    st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+  }
+  return st;
+}
+
+FB_API int32_t fb_gru_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const float* Wh, const float* b, const float* x,
+                          const float* h0, float* out, float* hT, void* cache, int64_t in_dim, int64_t hidden,
+                          int64_t seq_len, int64_t batch) {
+  FB_CHECK_CTX(ctx);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int32_t st = check_dims("fb_gru_fwd", in_dim, hidden, seq_len, batch);
+  if (st != FB_OK) return st;
+  if (seq_len == 0 || batch == 0) return FB_OK;
+  FB_REQUIRE(Wi && Wh && x && out, FB_ERR_INVALID_ARG, "fb_gru_fwd: NULL pointer");
+  const int H = (int)hidden, B = (int)batch;
+  const int64_t T = seq_len, rows = T * batch, ldrow = T * H;
+  float *cch = nullptr, *gx;
+  if (cache) {
+    cch = (float*)cache;
+    gx = cch + rows * 4 * H;
+  } else {
+    gx = (float*)fb_scratch(ctx, stream, (size_t)(rows * 3 * H) * sizeof(float));
+    if (!gx) return FB_ERR_ALLOC;
+  }
+  fb_gemm_args a;
+  a.A = x; a.lda = in_dim; a.a_mn_major = 0;
+  a.B = Wi; a.ldb = 3 * hidden; a.b_mn_major = 1;
+  a.C = gx; a.ldc = 3 * hidden; a.Z = nullptr; a.bias_n = b; a.bias_m = nullptr;
+  a.M = rows; a.N = 3 * hidden; a.K = in_dim; a.act = FB_ACT_IDENTITY; a.accumulate = 0;
+  st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+  if (st != FB_OK) return st;
+  const int hu = pick_hu(3, H, ctx->smem_optin, (size_t)BC * HS * 4);
+  FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_gru_fwd: hidden size %d does not fit the step kernel's shared memory", H);
+  const size_t smem = fwd_smem(3, hu, H);
+  auto kern = hu == 4 ? gru_fwd_step_kernel<4> : hu == 2 ? gru_fwd_step_kernel<2> : gru_fwd_step_kernel<1>;
+  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const unsigned grid = (unsigned)((H + hu - 1) / hu);
+  for (int64_t t = 0; t < T; ++t) {
+    const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
+    const int64_t ldh = t == 0 ? H : ldrow;
+    kern<<<grid, RT, smem, stream>>>(Wh, gx + t * 3 * H, T * 3 * H, hprev, ldh, out + t * H, ldrow,
+                                     cch ? cch + t * 4 * H : nullptr, T * 4 * H, (t == T - 1) ? hT : nullptr, H, B);
+    FB_LAUNCH_CHECK();
+  }
+  return FB_OK;
+}
+
+FB_API int32_t fb_gru_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const float* Wh, const float* x,
+                          const float* h0, const float* out, const void* cache, const float* dout, const float* dhT, float* dWi, float* dWh, float* db,
+                          float* dx, int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch) {
+  FB_CHECK_CTX(ctx);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int32_t st = check_dims("fb_gru_bwd", in_dim, hidden, seq_len, batch);
+  if (st != FB_OK) return st;
+  FB_REQUIRE(seq_len >= 1 && batch >= 1, FB_ERR_SHAPE, "fb_gru_bwd: empty sequence or batch");
+  FB_REQUIRE(Wi && Wh && x && out && cache && dout && dWi && dWh, FB_ERR_INVALID_ARG, "fb_gru_bwd: NULL pointer");
+  const int H = (int)hidden, B = (int)batch;
+  const int64_t T = seq_len, rows = T * batch, ldrow = T * H;
+  const float* cch = (const float*)cache;          // [rows][4H]
+  float* dgx = (float*)cache + rows * 4 * H;       // [rows][3H], over the input projection
+  float* dgh = dgx + rows * 3 * H;                 // [rows][3H]
+  float* ws = (float*)fb_scratch(ctx, stream, (size_t)(3 * (int64_t)B * H) * sizeof(float));
+  if (!ws) return FB_ERR_ALLOC;
+  float* dh_direct = ws;
+  float* dh_a = ws + (int64_t)B * H;
+  float* dh_b = dh_a + (int64_t)B * H;
+  const int hu = pick_hu(1, 3 * H, ctx->smem_optin, (size_t)BC * HS * 4);
+  FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_gru_bwd: hidden size %d does not fit the step kernel's shared memory", H);
+  const size_t smem = dh_smem(hu, 3 * H);
+  auto kern = hu == 4 ? rnn_bwd_dh_kernel<4> : hu == 2 ? rnn_bwd_dh_kernel<2> : rnn_bwd_dh_kernel<1>;
+  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const unsigned grid_dh = (unsigned)((H + hu - 1) / hu);
+  int64_t eb = ((int64_t)B * H + RT - 1) / RT;
+  if (eb > ctx->sm_count * 8) eb = ctx->sm_count * 8;
+  const float* dh_rec = dhT;
+  for (int64_t t = T - 1; t >= 0; --t) {
+    const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
+    gru_bwd_gates_kernel<<<(unsigned)eb, RT, 0, stream>>>(cch + t * 4 * H, T * 4 * H, hprev, t == 0 ? (int64_t)H : ldrow, dout + t * H, ldrow,
+                                                          dh_rec, dgx + t * 3 * H, dgh + t * 3 * H, T * 3 * H,
+                                                          dh_direct, H, B);
+    FB_LAUNCH_CHECK();
+    if (t > 0) {
+      float* dh_next = (dh_rec == dh_a) ? dh_b : dh_a;
+      kern<<<grid_dh, RT, smem, stream>>>(Wh, dgh + t * 3 * H, T * 3 * H, dh_direct, dh_next, H, 3 * H, B);
+      FB_LAUNCH_CHECK();
+      dh_rec = dh_next;
+    }
+  }
+  fb_gemm_args a;
+  a.Z = nullptr; a.bias_n = nullptr; a.bias_m = nullptr; a.act = FB_ACT_IDENTITY; a.accumulate = 0;
+  a.A = x; a.lda = in_dim; a.a_mn_major = 1;
+  a.B = dgx; a.ldb = 3 * hidden; a.b_mn_major = 1;
+  a.C = dWi; a.ldc = 3 * hidden; a.M = in_dim; a.N = 3 * hidden; a.K = rows;
+  st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+  if (st != FB_OK) return st;
+  {
+    float* hprev_all = dgh + rows * 3 * H;
+    int64_t sb = (rows * H + RT - 1) / RT;
+    if (sb > (int64_t)ctx->sm_count * 16) sb = (int64_t)ctx->sm_count * 16;
+    shift_prev_kernel<<<(unsigned)sb, RT, 0, stream>>>(out, h0, hprev_all, H, T, batch);
+    FB_LAUNCH_CHECK();
+    a.A = hprev_all; a.lda = hidden; a.a_mn_major = 1;
+    a.B = dgh; a.ldb = 3 * hidden; a.b_mn_major = 1;
+    a.C = dWh; a.ldc = 3 * hidden; a.M = hidden; a.N = 3 * hidden; a.K = rows;
+    st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+    if (st != FB_OK) return st;
+  }
+  a.accumulate = 0;
+  if (db) {
+    st = colsum_rows(ctx, stream, dgx, db, rows, 3 * hidden);
+    if (st != FB_OK) return st;
+  }
+  if (dx) {
+    a.A = dgx; a.lda = 3 * hidden; a.a_mn_major = 0;
+    a.B = Wi; a.ldb = 3 * hidden; a.b_mn_major = 0;
+    a.C = dx; a.ldc = in_dim; a.M = rows; a.N = in_dim; a.K = 3 * hidden;
+    st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
+  }
+  return st;
+}

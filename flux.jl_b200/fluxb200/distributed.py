@@ -1,0 +1,294 @@
+"""DistributedUtils for B200 arrays: NCCL backend, broadcast / allreduce / reduce, `synchronize`,
+`DistributedDataContainer`, `DistributedOptimizer` with bucketed, overlapped gradient averaging.
+
+Mirrors src/distributed/public_api.jl (initialize :45-49, get_distributed_backend :67-71,
+local_rank / total_workers :82-93, bcast! :102-116, allreduce! :134-150, reduce! :166-183,
+synchronize!! :203-231, DistributedDataContainer :245-272, DistributedOptimizer :286-300) and
+ext/FluxMPINCCLExt (NCCL collectives on device buffers).  The reference bootstraps the NCCL unique
+id over MPI; here the launcher's rendezvous (torch.distributed store, env:// as torchrun sets it)
+carries the 128 id bytes, and every data-path collective runs through fb_allreduce / fb_bcast /
+fb_reduce of libfluxb200.so on a dedicated communication stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+
+import numpy as np
+import torch
+
+from . import lib
+from .core import B200Array, context
+from .layers import Layer, trainables
+from .train import DistributedOptimizerBase, OptState
+
+avg = "avg"
+_BACKEND = None
+
+
+class NCCLBackend:
+    """NCCLBackend(comm): one rank of a single-node NCCL communicator."""
+
+    def __init__(self, comm_handle, rank: int, size: int):
+        self.comm = comm_handle
+        self.rank, self.size = rank, size
+        self.stream = torch.cuda.Stream(priority=-1)   # communication stream (high priority)
+
+    def __repr__(self):
+        return f"NCCLBackend(rank={self.rank}, size={self.size})"
+
+
+def shard_indices(total_size: int, total_workers: int, local_rank: int) -> np.ndarray:
+    """public_api.jl:262-272: contiguous ceil(n/N) index ranges (0-based here), shorter last shard."""
+    per = int(math.ceil(total_size / total_workers))
+    starts = list(range(0, total_size, per))
+    if local_rank >= len(starts):
+        raise IndexError("BoundsError: attempt to access partition of a rank without data")
+    s = starts[local_rank]
+    return np.arange(s, min(s + per, total_size))
+
+
+def initialize(backend=NCCLBackend, device: int | None = None):
+    """DistributedUtils.initialize(NCCLBackend): joins the process group named by the launcher's
+    environment (RANK, WORLD_SIZE, LOCAL_RANK, MASTER_ADDR, MASTER_PORT) and creates the communicator."""
+    global _BACKEND
+    if _BACKEND is not None:
+        return _BACKEND
+    rank = int(os.environ.get("RANK", "0"))
+    size = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    dev = local if device is None else device
+    ctx = context(dev)
+    idbuf = (C.c_uint8 * lib.UNIQUE_ID_BYTES)()
+    if size > 1:
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            dist.init_process_group(backend="gloo", rank=rank, world_size=size)
+        if rank == 0:
+            lib.call("fb_comm_get_unique_id", idbuf)
+        t = torch.tensor(list(bytes(idbuf)), dtype=torch.uint8)
+        dist.broadcast(t, src=0)
+        idbuf = (C.c_uint8 * lib.UNIQUE_ID_BYTES)(*t.tolist())
+        h = C.c_void_p()
+        lib.call("fb_comm_init_rank", ctx.handle, idbuf, size, rank, C.byref(h))
+    else:
+        # a single worker needs no communicator; one is still created when NCCL is present so that the
+        # collectives run the same code path
+        h = C.c_void_p()
+        try:
+            lib.call("fb_comm_get_unique_id", idbuf)
+            lib.call("fb_comm_init_rank", ctx.handle, idbuf, 1, 0, C.byref(h))
+        except lib.FluxB200Error:
+            h = None
+    _BACKEND = NCCLBackend(h, rank, size)
+    return _BACKEND
+
+
+def get_distributed_backend(backend=NCCLBackend):
+    if _BACKEND is None:
+        raise RuntimeError("backend `NCCLBackend` is not initialized; call DistributedUtils.initialize first")
+    return _BACKEND
+
+
+def local_rank(backend) -> int:
+    return backend.rank
+
+
+def total_workers(backend) -> int:
+    return backend.size
+
+
+def _stream_ptr(backend, on_comm_stream: bool):
+    s = backend.stream if on_comm_stream else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _local_copy(src: B200Array, dst: B200Array):
+    """A one-worker collective is a copy (or nothing when the buffers coincide)."""
+    if dst.t.data_ptr() != src.t.data_ptr():
+        ctx = context()
+        lib.call("fb_memcpy_d2d", ctx.handle, ctx.stream, dst.ptr, src.ptr, 4 * dst.numel())
+    return dst
+
+
+def bcast(backend, sendrecvbuf: B200Array, recvbuf: B200Array | None = None, root: int = 0):
+    """bcast!(backend, sendrecvbuf; root) / bcast!(backend, sendbuf, recvbuf; root)."""
+    dst = sendrecvbuf if recvbuf is None else recvbuf
+    if backend.comm is None:
+        return _local_copy(sendrecvbuf, dst)
+    lib.call("fb_bcast", backend.comm, _stream_ptr(backend, False), sendrecvbuf.ptr, dst.ptr, dst.numel(), root)
+    return dst
+
+
+def allreduce(backend, sendrecvbuf: B200Array, op_or_recv="+", op=None):
+    """allreduce!(backend, sendrecvbuf, op) / allreduce!(backend, sendbuf, recvbuf, op); op is "+" or avg."""
+    if isinstance(op_or_recv, B200Array):
+        dst, o = op_or_recv, op
+    else:
+        dst, o = sendrecvbuf, op_or_recv
+    if backend.comm is None:
+        return _local_copy(sendrecvbuf, dst)
+    lib.call("fb_allreduce", backend.comm, _stream_ptr(backend, False), sendrecvbuf.ptr, dst.ptr, dst.numel(), lib.OP[o])
+    return dst
+
+
+def reduce(backend, sendrecvbuf: B200Array, op_or_recv="+", op=None, root: int = 0):
+    if isinstance(op_or_recv, B200Array):
+        dst, o = op_or_recv, op
+    else:
+        dst, o = sendrecvbuf, op_or_recv
+    if backend.comm is None:
+        return _local_copy(sendrecvbuf, dst)
+    lib.call("fb_reduce", backend.comm, _stream_ptr(backend, False), sendrecvbuf.ptr, dst.ptr, dst.numel(), lib.OP[o], root)
+    return dst
+
+
+class FluxDistributedModel:
+    def __init__(self, model):
+        self.model = model
+
+
+def synchronize(backend, ps, root: int = 0):
+    """synchronize!!(backend, ps; root): broadcasts every array leaf (model parameters, optimiser
+    moments) from `root`; scalar state (β powers) is broadcast through a one-element buffer."""
+    if isinstance(ps, FluxDistributedModel):
+        synchronize(backend, ps.model, root)
+        return ps.model
+    if isinstance(ps, B200Array):
+        bcast(backend, ps, root=root)
+        return ps
+    if isinstance(ps, OptState):
+        for leaf in ps.leaves.values():
+            if leaf.state is not None:
+                bcast(backend, leaf.state[0], root=root)
+                bcast(backend, leaf.state[1], root=root)
+                t = torch.tensor(leaf.state[2], dtype=torch.float32, device="cuda")
+                bcast(backend, B200Array(t, (2,)), root=root)
+                v = t.cpu().tolist()
+                leaf.state[2] = (float(np.float32(v[0])), float(np.float32(v[1])))
+        return ps
+    if isinstance(ps, (tuple, list)):
+        return type(ps)(synchronize(backend, p, root) for p in ps)
+    if isinstance(ps, dict):
+        return {k: synchronize(backend, v, root) for k, v in ps.items()}
+    if isinstance(ps, Layer):
+        for name in ps._fields:
+            v = getattr(ps, name, None)
+            if isinstance(v, (B200Array, Layer, tuple, list)):
+                synchronize(backend, v, root)
+        return ps
+    return ps
+
+
+class DistributedDataContainer:
+    """DistributedDataContainer(backend, data): this rank's contiguous shard of the observations
+    (last array dimension)."""
+
+    def __init__(self, backend, data: np.ndarray):
+        self.data = data
+        n = data.shape[-1]
+        self.idxs = shard_indices(n, backend.size, backend.rank)
+
+    def __len__(self):
+        return len(self.idxs)
+
+    def __getitem__(self, i):
+        return self.data[..., self.idxs[i]]
+
+
+class GradBuckets:
+    """Flat gradient buffer split into buckets of ~bucket_mb MiB in reverse parameter order (the order
+    the backward pass produces gradients).  Layer pullbacks write gradients straight into their slice;
+    when a bucket's last gradient has landed, its mean all-reduce starts on the communication stream
+    while the backward pass continues."""
+
+    def __init__(self, backend, params, bucket_mb: float = 64.0):
+        self.backend = backend
+        self.params = list(params)
+        pad = lambda n: (n + 63) // 64 * 64          # every slice starts on a 256-byte boundary
+        total = sum(pad(p.numel()) for p in self.params)
+        dev = self.params[0].t.device
+        self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.views, self.bucket_of = {}, {}
+        self.buckets = []   # [start, end, pending ids, all ids]
+        limit = int(bucket_mb * (1 << 20) / 4)
+        off = 0
+        cur_start, cur_ids = 0, []
+        for p in reversed(self.params):
+            n = p.numel()
+            self.views[id(p)] = B200Array(self.flat[off:off + n], p.size)
+            cur_ids.append(id(p))
+            off += pad(n)
+            if off - cur_start >= limit:
+                self.buckets.append([cur_start, off, set(), list(cur_ids)])
+                cur_start, cur_ids = off, []
+        if cur_ids:
+            self.buckets.append([cur_start, off, set(), list(cur_ids)])
+        for bi, b in enumerate(self.buckets):
+            for k in b[3]:
+                self.bucket_of[k] = bi
+        self.events = [torch.cuda.Event() for _ in self.buckets]
+        self.launched = [False] * len(self.buckets)
+        self.begin_step()
+
+    def begin_step(self):
+        for b in self.buckets:
+            b[2] = set(b[3])
+        self.launched = [False] * len(self.buckets)
+
+    def buffer_for(self, param):
+        return self.views.get(id(param)) if param is not None else None
+
+    def ready(self, param):
+        k = id(param)
+        bi = self.bucket_of.get(k)
+        if bi is None:
+            return
+        b = self.buckets[bi]
+        b[2].discard(k)
+        if not b[2] and not self.launched[bi]:
+            self._launch(bi)
+
+    def _launch(self, bi):
+        self.launched[bi] = True
+        be = self.backend
+        if be.size == 1:
+            return
+        start, end = self.buckets[bi][0], self.buckets[bi][1]
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        be.stream.wait_event(ev)
+        ptr = C.c_void_p(self.flat.data_ptr() + 4 * start)
+        lib.call("fb_allreduce", be.comm, C.c_void_p(be.stream.cuda_stream), ptr, ptr, end - start, lib.OP["avg"])
+        self.events[bi].record(be.stream)
+
+    def finish(self):
+        """Launches whatever is still pending and makes the compute stream wait for every bucket."""
+        for bi in range(len(self.buckets)):
+            if not self.launched[bi]:
+                self._launch(bi)
+        if self.backend.size > 1:
+            for ev in self.events:
+                torch.cuda.current_stream().wait_event(ev)
+
+
+class DistributedOptimizer(DistributedOptimizerBase):
+    """DistributedOptimizer(backend, opt): averages gradients over the workers, then applies `opt`
+    (public_api.jl:286-294).  Gradients that a GradBuckets sink already averaged are not reduced twice."""
+
+    def __init__(self, backend, opt, buckets: GradBuckets | None = None):
+        self.backend, self.opt, self.buckets = backend, opt, buckets
+
+    def average_gradients(self, opt_state, gmap: dict):
+        if self.buckets is not None:
+            self.buckets.finish()
+            done = set(self.buckets.views.keys())
+        else:
+            done = set()
+        if self.backend.size == 1:
+            return
+        for k, g in gmap.items():
+            if k in done and g.t.data_ptr() == self.buckets.views[k].t.data_ptr():
+                continue
+            allreduce(self.backend, g, avg)

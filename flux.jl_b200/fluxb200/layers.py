@@ -1,0 +1,560 @@
+"""Host-side mirror of Flux's layers for B200 arrays: same names, fields, argument meaning and errors.
+
+Each call operator does what the Julia extension's method does: size checks on the host, one call
+into libfluxb200.so, and (under `withgradient`) a recorded pullback that calls the matching
+backward entry point.  Reference: src/layers/basic.jl (Chain :49-81, Dense :179-205),
+normalise.jl (LayerNorm :186-210, BatchNorm :259-307), recurrent.jl (scan :1-8, Recurrence :61-81,
+LSTMCell :383-419, GRUCell :586-628, LSTM :491-524, GRU :685-718), attention.jl (:68-133).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import lib
+from .core import B200Array, Tape, context, empty, gpu, zeros
+
+
+class DimensionMismatch(ValueError):
+    pass
+
+
+class ArgumentError(ValueError):
+    pass
+
+
+def _act_name(sigma) -> str:
+    if sigma is None:
+        return "identity"
+    if callable(sigma) and hasattr(sigma, "__name__"):
+        sigma = sigma.__name__
+    if sigma not in lib.ACT:
+        raise lib.FluxB200Error(-7, f"activation {sigma!r} has no B200 kernel (known: {sorted(lib.ACT)})")
+    return sigma
+
+
+def _ptr(a):
+    return a.ptr if a is not None else None
+
+
+def _size_check(layer, x: B200Array, d: int, n: int):
+    """basic.jl:217-223 (d is 1-based)."""
+    if not (0 < d <= x.ndim):
+        raise DimensionMismatch(f"layer {layer} expects ndims(input) >= {d}, but got {x}")
+    if x.size[d - 1] != n:
+        raise DimensionMismatch(f"layer {layer} expects size(input, {d}) == {n}, but got {x}")
+
+
+class Layer:
+    """Base: `_fields` names the child fields (arrays, layers, scalars) in Flux's order;
+    `_trainable` the trainable subset (Flux's `@layer ... trainable=`)."""
+
+    _fields: tuple = ()
+    _trainable = None
+
+    def _fmap(self, f):
+        import copy
+        new = copy.copy(self)
+        for name in self._fields:
+            v = getattr(self, name)
+            if isinstance(v, (B200Array, np.ndarray, tuple, list, dict)) or hasattr(v, "_fmap"):
+                setattr(new, name, f(v))
+        return new
+
+    def trainable_fields(self):
+        return self._fields if self._trainable is None else self._trainable
+
+
+def trainables(obj) -> list:
+    """Flux.trainables: the trainable arrays in traversal order."""
+    out = []
+    if isinstance(obj, B200Array):
+        out.append(obj)
+    elif isinstance(obj, (tuple, list)):
+        for v in obj:
+            out.extend(trainables(v))
+    elif isinstance(obj, Layer):
+        for name in obj.trainable_fields():
+            out.extend(trainables(getattr(obj, name)))
+    return out
+
+
+# ------------------------------------------------------------------------------------ Chain ---
+class Chain(Layer):
+    _fields = ("layers",)
+
+    def __init__(self, *layers):
+        self.layers = tuple(layers)
+
+    def __call__(self, x):
+        for l in self.layers:
+            x = l(x)
+        return x
+
+    def __getitem__(self, i):
+        return self.layers[i]
+
+    def __repr__(self):
+        return "Chain(" + ", ".join(map(repr, self.layers)) + ")"
+
+
+# ------------------------------------------------------------------------------------ Dense ---
+class Dense(Layer):
+    """Dense(W, bias, sigma): y = sigma.(W*x .+ b) (basic.jl:179-205). `bias=False` means no bias."""
+
+    _fields = ("weight", "bias", "σ")
+    _trainable = ("weight", "bias")
+
+    def __init__(self, weight, bias=True, sigma="identity", precision="default"):
+        self.weight = gpu(weight) if isinstance(weight, np.ndarray) else weight
+        if self.weight.ndim != 2:
+            raise TypeError("MethodError: Dense weight must be a matrix")
+        out = self.weight.size[0]
+        if bias is True:
+            bias = zeros((out,))
+        elif bias is False or bias is None:
+            bias = False
+        else:
+            bias = gpu(bias) if isinstance(bias, np.ndarray) else bias
+            if bias.size != (out,):
+                raise DimensionMismatch(f"expected bias of size ({out},), got size {bias.size}")
+        self.bias = bias
+        self.σ = _act_name(sigma)
+        self.precision = precision
+
+    def __repr__(self):
+        return f"Dense({self.weight.size[1]} => {self.weight.size[0]}, {self.σ})"
+
+    def __call__(self, x: B200Array) -> B200Array:
+        if not isinstance(x, B200Array):
+            raise TypeError("MethodError: Dense expects an array")
+        out_dim, in_dim = self.weight.size
+        _size_check(self, x, 1, in_dim)
+        n = x.numel() // in_dim
+        ctx = context()
+        act, prec = lib.ACT[self.σ], lib.PREC[self.precision]
+        b = self.bias if self.bias is not False else None
+        recording = Tape.active
+        y = empty((out_dim,) + x.size[1:])
+        z = empty(y.size) if (recording and self.σ in ("gelu", "gelu_tanh", "gelu_erf")) else None
+        lib.call("fb_dense_fwd", ctx.handle, ctx.stream, act, prec, self.weight.ptr, _ptr(b), x.ptr, y.ptr, _ptr(z),
+                 out_dim, in_dim, n)
+        if recording:
+            W = self.weight
+
+            def pullback(gs, x=x, y=y, z=z):
+                dy = gs[0]
+                need_dx = Tape.needs(x)
+                sink = Tape.grad_sink
+                dW = (sink.buffer_for(W) if sink else None) or empty(W.size)
+                db = ((sink.buffer_for(b) if sink else None) or empty(b.size)) if b is not None else None
+                dx = empty(x.size) if need_dx else None
+                delta = empty(y.size) if act != 0 else None
+                lib.call("fb_dense_bwd", ctx.handle, ctx.stream, act, prec, W.ptr, x.ptr, y.ptr, _ptr(z), dy.ptr,
+                         _ptr(delta), dW.ptr, _ptr(db), _ptr(dx), out_dim, in_dim, n)
+                res = [(W, dW)]
+                if b is not None:
+                    res.append((b, db))
+                if need_dx:
+                    res.append((x, dx))
+                return res
+
+            Tape.record(y, [x, W, b], pullback)
+        return y
+
+
+# -------------------------------------------------------------------------------- LayerNorm ---
+class LayerNorm(Layer):
+    """LayerNorm(size..., λ; affine=true, eps=1f-5) (normalise.jl:186-210); `diag` is the Scale."""
+
+    _fields = ("λ", "diag", "ϵ", "size", "affine")
+    _trainable = ("diag",)
+
+    class _Scale(Layer):
+        _fields = ("scale", "bias", "σ")
+        _trainable = ("scale", "bias")
+
+        def __init__(self, size, sigma):
+            self.scale = gpu(np.ones(size, np.float32))
+            self.bias = gpu(np.zeros(size, np.float32))
+            self.σ = sigma
+
+    def __init__(self, *size, sigma="identity", affine=True, eps=1e-5):
+        if len(size) == 1 and isinstance(size[0], (tuple, list)):
+            size = tuple(size[0])
+        self.size = tuple(int(s) for s in size)
+        self.λ = _act_name(sigma)
+        self.affine = bool(affine)
+        self.ϵ = float(eps)
+        self.diag = LayerNorm._Scale(self.size, self.λ) if affine else None
+
+    def __repr__(self):
+        return f"LayerNorm({', '.join(map(str, self.size))})"
+
+    def __call__(self, x: B200Array) -> B200Array:
+        if self.affine:
+            for d, s in enumerate(self.size):
+                _size_check(self, x, d + 1, s)
+        d = int(np.prod(self.size))
+        if x.numel() % d != 0 or x.size[:len(self.size)] != self.size:
+            raise DimensionMismatch(f"layer {self} expects leading dims {self.size}, got {x}")
+        n = x.numel() // d
+        ctx = context()
+        act = lib.ACT[self.λ]
+        g = self.diag.scale if self.affine else None
+        b = self.diag.bias if self.affine else None
+        y, mean, rstd = empty(x.size), empty((n,)), empty((n,))
+        lib.call("fb_layernorm_fwd", ctx.handle, ctx.stream, x.ptr, _ptr(g), _ptr(b), y.ptr, mean.ptr, rstd.ptr, d, n,
+                 self.ϵ, act)
+        if Tape.active:
+            def pullback(gs, x=x):
+                dy = gs[0]
+                sink = Tape.grad_sink
+                dx = empty(x.size)
+                dg = ((sink.buffer_for(g) if sink else None) or empty(g.size)) if g is not None else None
+                dbeta = ((sink.buffer_for(b) if sink else None) or empty(b.size)) if b is not None else None
+                lib.call("fb_layernorm_bwd", ctx.handle, ctx.stream, x.ptr, _ptr(g), _ptr(b), mean.ptr, rstd.ptr, dy.ptr,
+                         dx.ptr, _ptr(dg), _ptr(dbeta), d, n, act)
+                res = [(x, dx)] if Tape.needs(x) else []
+                if g is not None:
+                    res += [(g, dg), (b, dbeta)]
+                return res
+
+            Tape.record(y, [x, g, b], pullback)
+        return y
+
+
+# -------------------------------------------------------------------------------- BatchNorm ---
+class BatchNorm(Layer):
+    """BatchNorm(chs, λ; affine, track_stats, eps=1f-5, momentum=0.1f0) (normalise.jl:259-307).
+
+    `active=None` means automatic: training under `withgradient`, inference otherwise (`_isactive`)."""
+
+    _fields = ("λ", "β", "γ", "μ", "σ2", "ϵ", "momentum", "affine", "track_stats", "active", "chs")
+    _trainable = ("β", "γ")
+
+    def __init__(self, chs: int, sigma="identity", affine=True, track_stats=True, active=None, eps=1e-5, momentum=0.1):
+        self.chs = int(chs)
+        self.λ = _act_name(sigma)
+        self.affine, self.track_stats, self.active = bool(affine), bool(track_stats), active
+        self.ϵ, self.momentum = float(eps), float(momentum)
+        self.β = gpu(np.zeros(chs, np.float32)) if affine else None
+        self.γ = gpu(np.ones(chs, np.float32)) if affine else None
+        self.μ = gpu(np.zeros(chs, np.float32)) if track_stats else None
+        self.σ2 = gpu(np.ones(chs, np.float32)) if track_stats else None
+
+    def __repr__(self):
+        return f"BatchNorm({self.chs}, {self.λ})"
+
+    def _isactive(self):
+        return Tape.active if self.active is None else bool(self.active)
+
+    def __call__(self, x: B200Array) -> B200Array:
+        N = x.ndim
+        if N < 2:
+            raise DimensionMismatch(f"layer {self} expects ndims(input) >= 2, but got {x}")
+        _size_check(self, x, N - 1, self.chs)
+        training = self._isactive()
+        s = int(np.prod(x.size[:N - 2], dtype=np.int64)) if N > 2 else 1
+        c, n = self.chs, x.size[-1]
+        if training and s * n == 1:
+            raise ArgumentError(
+                f"BatchNorm expected more than 1 value per channel when training, got input of size {x.size}. "
+                "The batch variance of a single value is undefined; use a larger batch or call `testmode!` for inference.")
+        ctx = context()
+        act = lib.ACT[self.λ]
+        y = empty(x.size)
+        if not training and self.track_stats:
+            lib.call("fb_batchnorm_fwd_infer", ctx.handle, ctx.stream, x.ptr, _ptr(self.γ), _ptr(self.β), self.μ.ptr,
+                     self.σ2.ptr, y.ptr, s, c, n, self.ϵ, act)
+            return y
+        mean, rstd = empty((c,)), empty((c,))
+        lib.call("fb_batchnorm_fwd_train", ctx.handle, ctx.stream, x.ptr, _ptr(self.γ), _ptr(self.β), _ptr(self.μ),
+                 _ptr(self.σ2), y.ptr, mean.ptr, rstd.ptr, s, c, n, self.ϵ, self.momentum, act,
+                 1 if (training and self.track_stats) else 0)
+        if Tape.active:
+            g, b = self.γ, self.β
+
+            def pullback(gs, x=x):
+                dy = gs[0]
+                dx = empty(x.size)
+                dg = empty((c,)) if g is not None else None
+                dbeta = empty((c,)) if b is not None else None
+                lib.call("fb_batchnorm_bwd", ctx.handle, ctx.stream, x.ptr, _ptr(g), _ptr(b), mean.ptr, rstd.ptr, dy.ptr,
+                         dx.ptr, _ptr(dg), _ptr(dbeta), s, c, n, act)
+                res = [(x, dx)] if Tape.needs(x) else []
+                if g is not None:
+                    res += [(g, dg), (b, dbeta)]
+                return res
+
+            Tape.record(y, [x, g, b], pullback)
+        return y
+
+
+def testmode(m, mode=True):
+    """Flux.testmode! (functor.jl:30-54): walks the model and sets `.active`."""
+    for layer in _walk(m):
+        if hasattr(layer, "active"):
+            layer.active = None if mode is None else (not mode)
+    return m
+
+
+def trainmode(m):
+    return testmode(m, False)
+
+
+def _walk(m):
+    if isinstance(m, Layer):
+        yield m
+        for name in m._fields:
+            yield from _walk(getattr(m, name, None))
+    elif isinstance(m, (tuple, list)):
+        for v in m:
+            yield from _walk(v)
+
+
+# ---------------------------------------------------------------------------------- recurrent ---
+class LSTMCell(Layer):
+    """LSTMCell(Wi, Wh, bias): Wi (4H, in), Wh (4H, H), b (4H) with gate rows i, f, g, o (recurrent.jl:383-419)."""
+
+    _fields = ("Wi", "Wh", "bias")
+    NG = 4
+
+    def __init__(self, Wi, Wh, bias=True):
+        self.Wi, self.Wh = gpu(Wi), gpu(Wh)
+        rows = self.Wi.size[0]
+        if bias is True:
+            bias = zeros((rows,))
+        elif bias is False or bias is None:
+            bias = False
+        else:
+            bias = gpu(bias)
+        self.bias = bias
+
+    @property
+    def hidden(self):
+        return self.Wh.size[1]
+
+    def initialstates(self):
+        H = self.hidden
+        return zeros((H,)), zeros((H,))
+
+
+class GRUCell(Layer):
+    """GRUCell(Wi, Wh, b): rows r, z, h~ (recurrent.jl:586-628)."""
+
+    _fields = ("Wi", "Wh", "b")
+    NG = 3
+
+    def __init__(self, Wi, Wh, b=True):
+        self.Wi, self.Wh = gpu(Wi), gpu(Wh)
+        rows = self.Wi.size[0]
+        if b is True:
+            b = zeros((rows,))
+        elif b is False or b is None:
+            b = False
+        else:
+            b = gpu(b)
+        self.b = b
+
+    @property
+    def hidden(self):
+        return self.Wh.size[1]
+
+    def initialstates(self):
+        return zeros((self.hidden,))
+
+
+def _broadcast_state(s: B200Array | None, H: int, B: int):
+    """A length-H state vector is broadcast over the batch (recurrent.jl:391-393); None = zeros."""
+    if s is None:
+        return None
+    if s.size == (H, B):
+        return s
+    if s.size == (H,):
+        return B200Array(s.t.repeat(B).contiguous(), (H, B))   # memory [B][H]
+    raise DimensionMismatch(f"state of size {s.size} does not match hidden size {H} and batch {B}")
+
+
+class Recurrence(Layer):
+    """Recurrence(cell; return_state=false): applies `scan(cell, x, state)` over x[in, T, B] (recurrent.jl:1-8, 61-81)."""
+
+    _fields = ("cell",)
+
+    def __init__(self, cell, return_state=False):
+        self.cell = cell
+        self.return_state = bool(return_state)
+
+    def __call__(self, x: B200Array, state=None):
+        cell = self.cell
+        in_dim = cell.Wi.size[1]
+        _size_check(cell, x, 1, in_dim)
+        if x.ndim == 2:
+            x3 = x.reshape(x.size[0], x.size[1], 1)
+        elif x.ndim == 3:
+            x3 = x
+        else:
+            raise DimensionMismatch(f"Recurrence expects a 2-d or 3-d input, got {x}")
+        _, T, B = x3.size
+        H = cell.hidden
+        ctx = context()
+        recording = Tape.active
+        is_lstm = isinstance(cell, LSTMCell)
+        bias = (cell.bias if is_lstm else cell.b)
+        bias = bias if bias is not False else None
+        out = empty((H, T, B))
+        hT = empty((H, B))
+        if is_lstm:
+            h0, c0 = (None, None) if state is None else state
+            h0, c0 = _broadcast_state(h0, H, B), _broadcast_state(c0, H, B)
+            cT = empty((H, B))
+            cache = None
+            if recording:
+                nbytes = lib.raw().fb_lstm_cache_bytes(in_dim, H, T, B)
+                cache = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=x.t.device)
+            lib.call("fb_lstm_fwd", ctx.handle, ctx.stream, cell.Wi.ptr, cell.Wh.ptr, _ptr(bias), x3.ptr, _ptr(h0), _ptr(c0),
+                     out.ptr, hT.ptr, cT.ptr, cache.data_ptr() if cache is not None else None, in_dim, H, T, B)
+            final = (hT, cT)
+        else:
+            h0 = _broadcast_state(state, H, B)
+            cache = None
+            if recording:
+                nbytes = lib.raw().fb_gru_cache_bytes(in_dim, H, T, B)
+                cache = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=x.t.device)
+            lib.call("fb_gru_fwd", ctx.handle, ctx.stream, cell.Wi.ptr, cell.Wh.ptr, _ptr(bias), x3.ptr, _ptr(h0), out.ptr,
+                     hT.ptr, cache.data_ptr() if cache is not None else None, in_dim, H, T, B)
+            final = hT
+        if recording:
+            def pullback(gs, x3=x3):
+                dout = gs[0] if gs[0] is not None else zeros(out.size)
+                dWi, dWh = empty(cell.Wi.size), empty(cell.Wh.size)
+                db = empty(bias.size) if bias is not None else None
+                dx = empty(x3.size) if Tape.needs(x3) else None
+                if is_lstm:
+                    dhT, dcT = gs[1], gs[2]
+                    lib.call("fb_lstm_bwd", ctx.handle, ctx.stream, cell.Wi.ptr, cell.Wh.ptr, x3.ptr, _ptr(h0), _ptr(c0),
+                             out.ptr, cache.data_ptr(), dout.ptr, _ptr(dhT), _ptr(dcT), dWi.ptr, dWh.ptr, _ptr(db),
+                             _ptr(dx), in_dim, H, T, B)
+                else:
+                    dhT = gs[1]
+                    lib.call("fb_gru_bwd", ctx.handle, ctx.stream, cell.Wi.ptr, cell.Wh.ptr, x3.ptr, _ptr(h0), out.ptr,
+                             cache.data_ptr(), dout.ptr, _ptr(dhT), dWi.ptr, dWh.ptr, _ptr(db), _ptr(dx), in_dim, H, T, B)
+                res = [(cell.Wi, dWi), (cell.Wh, dWh)]
+                if bias is not None:
+                    res.append((bias, db))
+                if dx is not None:
+                    res.append((x3, dx))
+                return res
+
+            outs = [out, hT, cT] if is_lstm else [out, hT]
+            Tape.record(outs, [x3, cell.Wi, cell.Wh, bias], pullback)
+        y = out if x.ndim == 3 else out.reshape(H, T)
+        if self.return_state:
+            return y, final
+        return y
+
+
+def LSTM(Wi, Wh, bias=True, return_state=False):
+    """LSTM(in => out) == Recurrence(LSTMCell(in => out)) (recurrent.jl:491-524)."""
+    return Recurrence(LSTMCell(Wi, Wh, bias), return_state=return_state)
+
+
+def GRU(Wi, Wh, b=True, return_state=False):
+    """GRU(in => out) == Recurrence(GRUCell(in => out)) (recurrent.jl:685-718)."""
+    return Recurrence(GRUCell(Wi, Wh, b), return_state=return_state)
+
+
+# ---------------------------------------------------------------------------------- attention ---
+class CausalMask:
+    """What NNlib.make_causal_mask(x) stands for: key j visible to query i iff j <= i.  Passed as `mask=`."""
+
+
+def make_causal_mask(x=None):
+    return CausalMask()
+
+
+class AttnScores:
+    """The second return value of MultiHeadAttention: alpha[kv, q, heads, batch], materialised on first use
+    (attention.jl:128-132 returns it eagerly; here it costs nothing unless it is read)."""
+
+    def __init__(self, q, k, lse, mask, causal, nheads, dims):
+        self._args = (q, k, lse, mask, causal, nheads, dims)
+        self._val = None
+        self.size = dims
+
+    def materialize(self) -> B200Array:
+        if self._val is None:
+            q, k, lse, mask, causal, nheads, (Lk, Lq, H, B) = self._args
+            ctx = context()
+            a = empty((Lk, Lq, H, B))
+            lib.call("fb_attn_scores", ctx.handle, ctx.stream, q.ptr, k.ptr, _ptr(mask), lse.ptr, a.ptr, q.size[0], Lq, Lk, B,
+                     nheads, 1 if causal else 0)
+            self._val = a
+        return self._val
+
+
+def dot_product_attention(q: B200Array, k: B200Array, v: B200Array, bias=None, nheads=1, mask=None):
+    """NNlib.dot_product_attention(q, k, v, bias; nheads, mask) -> (x, alpha) for 3-d B200 arrays."""
+    if bias is not None:
+        raise lib.FluxB200Error(-7, "additive attention bias has no B200 kernel; pass a boolean mask instead")
+    E, Lq, B = q.size
+    Ev, Lk, _ = v.size
+    if k.size != (E, Lk, B):
+        raise DimensionMismatch(f"key of size {k.size} does not match query {q.size} / value {v.size}")
+    if E % nheads or Ev % nheads:
+        raise ArgumentError(f"qk_dim = {E} and v_dim = {Ev} should be divisible by nheads = {nheads}")
+    causal = isinstance(mask, CausalMask)
+    m = None
+    if mask is not None and not causal:
+        m = gpu(np.asarray(mask, dtype=np.uint8)) if isinstance(mask, np.ndarray) else mask
+        if m.size != (Lk, Lq):
+            raise DimensionMismatch(f"mask of size {m.size} must be (kv_len, q_len) = ({Lk}, {Lq})")
+    ctx = context()
+    o, lse = empty((Ev, Lq, B)), empty((Lq, nheads, B))
+    lib.call("fb_attn_fwd", ctx.handle, ctx.stream, q.ptr, k.ptr, v.ptr, _ptr(m), o.ptr, lse.ptr, E, Ev, Lq, Lk, B, nheads,
+             1 if causal else 0)
+    if Tape.active:
+        def pullback(gs):
+            do = gs[0]
+            dq, dk, dv = empty(q.size), empty(k.size), empty(v.size)
+            lib.call("fb_attn_bwd", ctx.handle, ctx.stream, q.ptr, k.ptr, v.ptr, _ptr(m), o.ptr, lse.ptr, do.ptr, dq.ptr,
+                     dk.ptr, dv.ptr, E, Ev, Lq, Lk, B, nheads, 1 if causal else 0)
+            return [(q, dq), (k, dk), (v, dv)]
+
+        Tape.record(o, [q, k, v], pullback)
+    return o, AttnScores(q, k, lse, m, causal, nheads, (Lk, Lq, nheads, B))
+
+
+class MultiHeadAttention(Layer):
+    """MultiHeadAttention(dims; nheads, bias=false) = 3 input Dense + attention + output Dense (attention.jl:68-133)."""
+
+    _fields = ("nheads", "q_proj", "k_proj", "v_proj", "attn_drop", "out_proj")
+    _trainable = ("q_proj", "k_proj", "v_proj", "out_proj")
+
+    def __init__(self, Wq, Wk, Wv, Wo, nheads=8, biases=None, precision="default"):
+        bq = bk = bv = bo = False
+        if biases is not None:
+            bq, bk, bv, bo = biases
+        self.nheads = int(nheads)
+        self.q_proj = Dense(Wq, bq, precision=precision)
+        self.k_proj = Dense(Wk, bk, precision=precision)
+        self.v_proj = Dense(Wv, bv, precision=precision)
+        self.out_proj = Dense(Wo, bo, precision=precision)
+        self.attn_drop = None   # Dropout(0.0)
+        qk, vd = self.q_proj.weight.size[0], self.v_proj.weight.size[0]
+        if qk % nheads:
+            raise ArgumentError(f"qk_dim = {qk} should be divisible by nheads = {nheads}")
+        if vd % nheads:
+            raise ArgumentError(f"v_dim = {vd} should be divisible by nheads = {nheads}")
+
+    def __call__(self, q_in, k_in=None, v_in=None, bias=None, mask=None):
+        k_in = q_in if k_in is None else k_in
+        v_in = k_in if v_in is None else v_in
+        for a in (q_in, k_in, v_in):
+            if a.ndim != 3:
+                raise TypeError("MethodError: MultiHeadAttention expects 3-d arrays (features, len, batch)")
+        q = self.q_proj(q_in)
+        k = self.k_proj(k_in)
+        v = self.v_proj(v_in)
+        x, alpha = dot_product_attention(q, k, v, bias, nheads=self.nheads, mask=mask)
+        return self.out_proj(x), alpha

@@ -1,0 +1,327 @@
+"""Losses, `withgradient`, the Adam rule and the training step for B200 arrays.
+
+Mirrors src/losses/functions.jl:270-273 (logitcrossentropy), src/gradient.jl:214-233
+(withgradient), src/train.jl (`setup` :142-150, `trainstep!` :323-339 / `_eager_step!` :375-379,
+`train!` :198-253) and the Adam rule whose arithmetic the reference states in
+src/optimise/optimisers.jl:171-184.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from . import lib
+from .core import B200Array, Tape, accumulate, context, empty, gpu, zeros
+from .layers import DimensionMismatch, Layer, trainables
+
+
+class DomainError(ArithmeticError):
+    pass
+
+
+# ------------------------------------------------------------------------------------- losses ---
+def logitcrossentropy(yhat: B200Array, y, dims=1, agg="mean") -> B200Array:
+    """Flux.logitcrossentropy(ŷ, y): mean over the batch of -sum(y .* logsoftmax(ŷ; dims=1); dims=1).
+
+    `y` is either a dense target array of the same size as ŷ or a `OneHotLabels` (1-based integer labels,
+    what `onehotbatch(labels, 1:C)` stands for)."""
+    if dims != 1 or agg != "mean":
+        raise lib.FluxB200Error(-7, "logitcrossentropy on B200 arrays supports dims=1, agg=mean")
+    c = yhat.size[0]
+    n = yhat.numel() // c
+    ctx = context()
+    loss = empty(())
+    recording = Tape.needs(yhat)
+    dyhat = empty(yhat.size) if recording else None
+    if isinstance(y, OneHotLabels):
+        if y.nclasses != c or y.labels.numel() != n:
+            raise DimensionMismatch(f"loss function expects size(ŷ) = {yhat.size} to match size(y) = {(y.nclasses, y.labels.numel())}")
+        lib.call("fb_logitcrossentropy_labels", ctx.handle, ctx.stream, yhat.ptr, y.labels.ptr, loss.ptr,
+                 dyhat.ptr if dyhat else None, c, n, 1.0)
+    else:
+        if y.size != yhat.size:
+            raise DimensionMismatch(f"loss function expects size(ŷ) = {yhat.size} to match size(y) = {y.size}")
+        lib.call("fb_logitcrossentropy_dense", ctx.handle, ctx.stream, yhat.ptr, y.ptr, loss.ptr,
+                 dyhat.ptr if dyhat else None, c, n, 1.0)
+    if recording:
+        def pullback(gs):
+            g = gs[0]   # cotangent of the scalar loss (device scalar); 1 for a top-level loss
+            if g is not None and not getattr(g, "_is_one", False):
+                s = float(g.t.item())
+                lib.call("fb_scale", ctx.handle, ctx.stream, dyhat.ptr, s, dyhat.ptr, dyhat.numel())
+            return [(yhat, dyhat)]
+
+        Tape.record(loss, [yhat], pullback)
+    return loss
+
+
+class OneHotLabels:
+    """onehotbatch(labels, 1:nclasses) kept as the integer labels (1-based) on the device."""
+
+    def __init__(self, labels, nclasses: int):
+        if isinstance(labels, np.ndarray):
+            labels = gpu(labels.astype(np.int32))
+        self.labels = labels
+        self.nclasses = int(nclasses)
+
+
+def onehotbatch(labels, nclasses):
+    return OneHotLabels(np.asarray(labels), nclasses)
+
+
+def sum_abs2(y: B200Array) -> B200Array:
+    """sum(abs2, y); its pullback is the cotangent 2y."""
+    ctx = context()
+    out = empty(())
+    lib.call("fb_sumsq", ctx.handle, ctx.stream, y.ptr, y.numel(), out.ptr)
+    if Tape.needs(y):
+        def pullback(gs):
+            g = gs[0]
+            s = 2.0 if (g is None or getattr(g, "_is_one", False)) else 2.0 * float(g.t.item())
+            dy = empty(y.size)
+            lib.call("fb_scale", ctx.handle, ctx.stream, y.ptr, s, dy.ptr, y.numel())
+            return [(y, dy)]
+
+        Tape.record(out, [y], pullback)
+    return out
+
+
+def sum_all(y: B200Array) -> B200Array:
+    """sum(y); its pullback fills the cotangent."""
+    ctx = context()
+    out = empty(())
+    lib.call("fb_sum", ctx.handle, ctx.stream, y.ptr, y.numel(), out.ptr)
+    if Tape.needs(y):
+        def pullback(gs):
+            g = gs[0]
+            s = 1.0 if (g is None or getattr(g, "_is_one", False)) else float(g.t.item())
+            dy = empty(y.size)
+            lib.call("fb_fill", ctx.handle, ctx.stream, dy.ptr, s, y.numel())
+            return [(y, dy)]
+
+        Tape.record(out, [y], pullback)
+    return out
+
+
+def scale(c: float, a: B200Array) -> B200Array:
+    """c * a for a Python scalar c."""
+    ctx = context()
+    out = empty(a.size)
+    lib.call("fb_scale", ctx.handle, ctx.stream, a.ptr, float(c), out.ptr, a.numel())
+    if Tape.needs(a):
+        def pullback(gs):
+            g = gs[0]
+            da = empty(a.size)
+            if getattr(g, "_is_one", False):
+                lib.call("fb_fill", ctx.handle, ctx.stream, da.ptr, float(c), a.numel())
+            else:
+                lib.call("fb_scale", ctx.handle, ctx.stream, g.ptr, float(c), da.ptr, a.numel())
+            return [(a, da)]
+
+        Tape.record(out, [a], pullback)
+    return out
+
+
+# ----------------------------------------------------------------------------------- gradient ---
+def _grad_tree(obj, grads: dict):
+    """Gradient with the model's structure: dict of field name -> subtree / array / None
+    (src/gradient.jl:112: `(layers = ((weight = ..., bias = ..., σ = nothing), ...),)`)."""
+    if isinstance(obj, B200Array):
+        return grads.get(id(obj))
+    if isinstance(obj, (tuple, list)):
+        return tuple(_grad_tree(v, grads) for v in obj)
+    if isinstance(obj, Layer):
+        return {name: _grad_tree(getattr(obj, name), grads) for name in obj._fields}
+    return None
+
+
+def withgradient(f, model, grad_sink=None):
+    """Flux.withgradient(m -> loss, model): returns (loss_value, (grad_tree,)).
+
+    `f(model)` must return a scalar B200Array (or a tuple whose first element is one, like Zygote's
+    auxiliary-output form).  The loss value comes back as a Python float (one device -> host read,
+    the same sync `_eager_step!` pays at src/train.jl:377).
+    """
+    assert not Tape.active, "nested withgradient is not supported"
+    Tape.reset()
+    Tape.active = True
+    Tape.grad_sink = grad_sink
+    params = trainables(model)
+    for p in params:
+        Tape.track(p)
+    try:
+        out = f(model)
+        aux = None
+        loss = out
+        if isinstance(out, tuple):
+            loss, aux = out[0], out[1:]
+        if not isinstance(loss, B200Array) or loss.numel() != 1:
+            raise TypeError("withgradient: the function must return a scalar B200Array")
+        grads: dict = {}
+        keep: dict = {}
+        grads[id(loss)] = _One(B200Array(torch.ones(1, device=loss.t.device), ()))
+        keep[id(loss)] = loss
+        for outs, inputs, pullback in reversed(Tape.entries):
+            gs = [grads.get(id(o)) for o in outs]
+            if all(g is None for g in gs):
+                continue
+            for arr, g in pullback(gs):
+                if arr is None or g is None:
+                    continue
+                accumulate(grads, keep, arr, g)
+                if grad_sink is not None:
+                    grad_sink.ready(arr)
+        tree = _grad_tree(model, grads)
+    finally:
+        Tape.active = False
+        Tape.grad_sink = None
+        Tape.reset()
+    val = float(loss.t.item())
+    if aux is not None:
+        return (val,) + tuple(aux), (tree,)
+    return val, (tree,)
+
+
+class _One(B200Array):
+    """Cotangent 1 of the top-level loss."""
+
+    __slots__ = ("_is_one",)
+
+    def __init__(self, a: B200Array):
+        super().__init__(a.t, a.size)
+        self._is_one = True
+
+
+def gradient(f, model):
+    return withgradient(f, model)[1]
+
+
+# --------------------------------------------------------------------------------------- Adam ---
+class Adam:
+    """Optimisers.Adam(η = 0.001, β = (0.9, 0.999), ϵ = 1e-8)."""
+
+    def __init__(self, eta=1e-3, beta=(0.9, 0.999), epsilon=1e-8):
+        self.eta, self.beta, self.epsilon = float(eta), (float(beta[0]), float(beta[1])), float(epsilon)
+
+
+class Descent:
+    """Optimisers.Descent(η): x .-= η .* dx (used by the reference's train tests)."""
+
+    def __init__(self, eta=0.1):
+        self.eta = float(eta)
+
+
+class Leaf:
+    """Optimisers.Leaf(rule, state): state = (m, v, (β1ᵗ, β2ᵗ)) for Adam."""
+
+    def __init__(self, rule, param: B200Array):
+        self.rule = rule
+        if isinstance(rule, Adam):
+            self.state = [zeros(param.size), zeros(param.size), (rule.beta[0], rule.beta[1])]
+        else:
+            self.state = None
+
+
+class OptState:
+    def __init__(self, rule, model):
+        self.rule = rule
+        self.params = trainables(model)
+        if len({id(p) for p in self.params}) != len(self.params):
+            pass  # tied weights share one leaf
+        self.leaves = {}
+        for p in self.params:
+            if id(p) not in self.leaves:
+                self.leaves[id(p)] = Leaf(rule, p)
+
+
+def setup(rule, model) -> OptState:
+    """Flux.setup(rule, model) (src/train.jl:142-150): one Leaf per trainable array."""
+    inner = rule.opt if isinstance(rule, DistributedOptimizerBase) else rule
+    if not isinstance(inner, (Adam, Descent)):
+        raise lib.FluxB200Error(-7, f"optimiser rule {type(inner).__name__} has no B200 kernel")
+    st = OptState(inner, model)
+    st.outer = rule
+    return st
+
+
+class DistributedOptimizerBase:
+    """Marker base so `setup` can unwrap DistributedUtils.DistributedOptimizer without a circular import."""
+    opt = None
+
+
+def _flat_grads(model, tree, out: dict):
+    if isinstance(model, B200Array):
+        if tree is not None:
+            out[id(model)] = tree
+    elif isinstance(model, (tuple, list)):
+        for m, t in zip(model, tree):
+            _flat_grads(m, t, out)
+    elif isinstance(model, Layer) and tree is not None:
+        for name in model.trainable_fields():
+            _flat_grads(getattr(model, name), tree.get(name), out)
+
+
+def update(opt_state: OptState, model, grad_tree):
+    """Optimisers.update!(opt_state, model, grads) (src/train.jl:425): in-place, multi-tensor."""
+    gmap: dict = {}
+    _flat_grads(model, grad_tree, gmap)
+    outer = getattr(opt_state, "outer", None)
+    if isinstance(outer, DistributedOptimizerBase):
+        outer.average_gradients(opt_state, gmap)
+    ctx = context()
+    rule = opt_state.rule
+    ps = [p for p in opt_state.params if id(p) in gmap]
+    seen = set()
+    ps = [p for p in ps if not (id(p) in seen or seen.add(id(p)))]
+    if not ps:
+        return opt_state, model
+    if isinstance(rule, Descent):
+        for p in ps:
+            lib.call("fb_axpy", ctx.handle, ctx.stream, -rule.eta, gmap[id(p)].ptr, p.ptr, p.numel())
+        return opt_state, model
+    # leaves share (β1ᵗ, β2ᵗ) when they have seen the same number of steps: group by that pair
+    groups: dict = {}
+    for p in ps:
+        groups.setdefault(opt_state.leaves[id(p)].state[2], []).append(p)
+    for (b1t, b2t), plist in groups.items():
+        k = len(plist)
+        arr_t = C.c_void_p * k
+        w = arr_t(*[p.t.data_ptr() for p in plist])
+        g = arr_t(*[gmap[id(p)].t.data_ptr() for p in plist])
+        m = arr_t(*[opt_state.leaves[id(p)].state[0].t.data_ptr() for p in plist])
+        v = arr_t(*[opt_state.leaves[id(p)].state[1].t.data_ptr() for p in plist])
+        cnt = (C.c_int64 * k)(*[p.numel() for p in plist])
+        lib.call("fb_adam_step", ctx.handle, ctx.stream, k, w, g, m, v, cnt, rule.eta, rule.beta[0], rule.beta[1],
+                 rule.epsilon, b1t, b2t, 1.0)
+        f32 = np.float32
+        nb = (float(f32(b1t) * f32(rule.beta[0])), float(f32(b2t) * f32(rule.beta[1])))
+        for p in plist:
+            opt_state.leaves[id(p)].state[2] = nb
+    return opt_state, model
+
+
+def trainstep(loss, model, batch, opt_state):
+    """Flux.trainstep!(loss, model, batch, opt_state) (src/train.jl:323-339, 375-379): returns the
+    pre-update loss; a non-finite loss skips the update."""
+    if not isinstance(batch, tuple):
+        batch = (batch,)
+    l, gs = withgradient(lambda m: loss(m, *batch), model)
+    lv = l[0] if isinstance(l, tuple) else l
+    if math.isfinite(lv):
+        update(opt_state, model, gs[0])
+    return l
+
+
+def train(loss, model, data, opt_state):
+    """Flux.train!(loss, model, data, opt_state) (src/train.jl:198-253): stops with DomainError on a
+    non-finite loss, as the reference does."""
+    from .layers import trainmode
+    trainmode(model)
+    for i, batch in enumerate(data):
+        l = trainstep(loss, model, batch, opt_state)
+        lv = l[0] if isinstance(l, tuple) else l
+        if not math.isfinite(lv):
+            raise DomainError(f"Loss is {lv} on data item {i + 1}, stopping training")

@@ -1,0 +1,289 @@
+/*
+ * fluxb200.h — C ABI of libfluxb200.so: the forward + backward hot path of Flux.jl's own layers
+ * as hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * Flux has no FFI of its own: its layers call NNlib / BLAS / Optimisers / NCCL.jl through Julia
+ * dispatch on the array type.  Each entry point below names the reference call site it replaces
+ * (file:line inside the Flux.jl source tree); a Julia package extension binds them with `ccall`
+ * for arrays of a new device type.
+ *
+ * Conventions
+ *  - every function returns an int32 status (FB_OK == 0, negative on error), never aborts, throws
+ *    or exits; fb_last_error() returns the message of the calling thread's last failure;
+ *  - pointers are raw device pointers unless the name ends in `_host`; sizes are int64; enums are
+ *    int32; scalars are passed by value;
+ *  - arrays are dense and column-major exactly as Julia stores them: a Julia `W[out,in]` is read by
+ *    the kernels as row-major `[in][out]`, `x[in,N]` as `[N][in]`, WHCN images as `[N][C][H*W]`;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Calls enqueue work
+ *    and return; only fb_sync, fb_memcpy_d2h and the fb_comm_* bootstrap calls block;
+ *  - the caller owns all tensors, including the saved-for-backward buffers (statistics, gates,
+ *    log-sum-exp); the library owns only a per-context scratch arena that grows on demand.
+ */
+#ifndef FLUXB200_H
+#define FLUXB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FB_VERSION 100
+
+/* status codes */
+#define FB_OK 0
+#define FB_ERR_INVALID_ARG (-1)
+#define FB_ERR_SHAPE (-2)
+#define FB_ERR_ALLOC (-3)
+#define FB_ERR_CUDA (-4)
+#define FB_ERR_NCCL (-5)
+#define FB_ERR_TIMEOUT (-6)
+#define FB_ERR_UNSUPPORTED (-7)
+
+/* activation enum (NNlib activations that Flux layers are constructed with) */
+#define FB_ACT_IDENTITY 0
+#define FB_ACT_RELU 1
+#define FB_ACT_TANH 2
+#define FB_ACT_SIGMOID 3
+#define FB_ACT_GELU_TANH 4
+#define FB_ACT_GELU_ERF 5
+
+/* matmul precision for Float32 data */
+#define FB_PREC_DEFAULT 0 /* 3xTF32 on the tensor cores when the shape allows, else fp32 FMA */
+#define FB_PREC_FP32_SIMT 1 /* always the fp32 FMA kernel */
+#define FB_PREC_3XTF32 2  /* tcgen05 tensor cores, error-compensated TF32 (fp32-level accuracy) */
+#define FB_PREC_TF32 3    /* tcgen05 tensor cores, single TF32 pass */
+
+/* reduction op for collectives (DistributedUtils.avg is FB_OP_AVG) */
+#define FB_OP_SUM 0
+#define FB_OP_AVG 1
+
+typedef struct fb_ctx fb_ctx;
+typedef struct fb_comm fb_comm;
+
+/* ---------------------------------------------------------------- context, memory, errors -- */
+
+/* Library version (FB_VERSION of the build). No reference counterpart. */
+int32_t fb_version(void);
+
+/* Number of kernels this library has launched in the calling process (diagnostic counter). No reference
+ * counterpart. */
+int64_t fb_kernel_launches(void);
+
+/* Creates the per-(thread, device) context: selects `device`, creates the scratch arena.
+ * Replaces what CUDA.jl's task-local state gives FluxCUDAExt (ext/FluxCUDAExt.jl:1-13). */
+int32_t fb_ctx_create(int32_t device, fb_ctx** out);
+int32_t fb_ctx_destroy(fb_ctx* ctx);
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char* fb_last_error(void);
+
+/* Device memory for the B200 array type: allocation, release, copies and fill.
+ * Replaces Adapt.adapt_storage / `gpu` / `cpu` movement (src/functor.jl:85, 116). */
+int32_t fb_malloc(fb_ctx* ctx, int64_t bytes, void** out);
+int32_t fb_free(fb_ctx* ctx, void* ptr);
+int32_t fb_memcpy_h2d(fb_ctx* ctx, void* stream, void* dst, const void* src_host, int64_t bytes);
+int32_t fb_memcpy_d2h(fb_ctx* ctx, void* stream, void* dst_host, const void* src, int64_t bytes);
+int32_t fb_memcpy_d2d(fb_ctx* ctx, void* stream, void* dst, const void* src, int64_t bytes);
+int32_t fb_memset(fb_ctx* ctx, void* stream, void* dst, int32_t byte_value, int64_t bytes);
+int32_t fb_sync(fb_ctx* ctx, void* stream);
+
+/* Device-side error word set by kernels whose bounded waits ran out (0 = none).  While it is set the
+ * tensor-core kernels return without computing.  Reading it synchronises the stream and clears it. */
+int32_t fb_device_error(fb_ctx* ctx, void* stream, int32_t* out_host);
+
+/* ------------------------------------------------------------------------------- matmul -- */
+
+/* C = op(A) * op(B) (+ C when accumulate != 0), column-major BLAS convention, Float32.
+ * transa/transb: 0 = 'N', 1 = 'T'.  Replaces `a.weight * xT` (src/layers/basic.jl:199) and the
+ * `*` calls of the recurrent cells (src/layers/recurrent.jl:414, 616-617) for the new array type. */
+int32_t fb_gemm_f32(fb_ctx* ctx, void* stream, int32_t transa, int32_t transb, int64_t m, int64_t n,
+                    int64_t k, const float* A, int64_t lda, const float* B, int64_t ldb, float* C,
+                    int64_t ldc, int32_t accumulate, int32_t precision);
+
+/* ------------------------------------------------------------------------------- Dense -- */
+
+/* y[out,n] = act.(W[out,in] * x[in,n] .+ b) in one fused kernel.  `b` may be NULL (bias=false).
+ * `z` (optional, may be NULL) receives the pre-activation, needed by fb_dense_bwd for the gelu
+ * activations.  Replaces (a::Dense)(x) = NNlib.bias_act!(sigma, a.weight * xT, a.bias)
+ * (src/layers/basic.jl:196-200). */
+int32_t fb_dense_fwd(fb_ctx* ctx, void* stream, int32_t act, int32_t precision, const float* W,
+                     const float* b, const float* x, float* y, float* z, int64_t out_dim,
+                     int64_t in_dim, int64_t n);
+
+/* Reverse of fb_dense_fwd (the Zygote pullback of basic.jl:199; external rrules of `*` and
+ * NNlib.bias_act!): delta = dy .* act'(.), dW = delta * x', db = sum_n delta, dx = W' * delta.
+ * `y` is the forward output (used by relu/tanh/sigmoid), `z` the saved pre-activation (gelu; may be
+ * NULL otherwise).  `delta` is caller scratch of out*n floats (may be NULL for FB_ACT_IDENTITY).
+ * db and dx may be NULL to skip them. */
+int32_t fb_dense_bwd(fb_ctx* ctx, void* stream, int32_t act, int32_t precision, const float* W,
+                     const float* x, const float* y, const float* z, const float* dy, float* delta,
+                     float* dW, float* db, float* dx, int64_t out_dim, int64_t in_dim, int64_t n);
+
+/* ---------------------------------------------------------------------------- LayerNorm -- */
+
+/* y[d,n] = act.(gamma .* (x - mean) * rstd .+ beta), statistics over the first (flattened) d
+ * elements of every column, biased variance, eps added to the variance.  gamma/beta may be NULL
+ * (affine=false).  mean/rstd (n floats each) are saved for the backward pass.
+ * Replaces (a::LayerNorm)(x) = a.diag(NNlib.normalise(x; dims, eps)) (src/layers/normalise.jl:203-210,
+ * Scale: src/layers/basic.jl:284-287). */
+int32_t fb_layernorm_fwd(fb_ctx* ctx, void* stream, const float* x, const float* gamma,
+                         const float* beta, float* y, float* mean, float* rstd, int64_t d, int64_t n,
+                         float eps, int32_t act);
+
+/* Reverse of fb_layernorm_fwd (external NNlib rrules): dx, dgamma[d], dbeta[d] (the last two may be
+ * NULL when gamma is NULL). */
+int32_t fb_layernorm_bwd(fb_ctx* ctx, void* stream, const float* x, const float* gamma,
+                         const float* beta, const float* mean, const float* rstd, const float* dy,
+                         float* dx, float* dgamma, float* dbeta, int64_t d, int64_t n, int32_t act);
+
+/* ---------------------------------------------------------------------------- BatchNorm -- */
+
+/* Training-mode BatchNorm on x viewed as [n][c][s] (s = product of the dims before the channel dim):
+ * per-channel batch mean and biased variance, y = act.(gamma*(x-mu)*rstd+beta); running statistics are
+ * updated in place (mu <- (1-m) mu + m mu_B, var <- (1-m) var + m var_B * cnt/(cnt-1)) when
+ * track_stats != 0.  save_mean/save_rstd (c floats) are saved for the backward pass.  cnt == 1 is
+ * rejected with FB_ERR_SHAPE.  Replaces (BN::BatchNorm)(x) in training
+ * (src/layers/normalise.jl:292-304 -> NNlib.batchnorm, then BN.lambda.(y)). */
+int32_t fb_batchnorm_fwd_train(fb_ctx* ctx, void* stream, const float* x, const float* gamma,
+                               const float* beta, float* running_mean, float* running_var, float* y,
+                               float* save_mean, float* save_rstd, int64_t s, int64_t c, int64_t n,
+                               float eps, float momentum, int32_t act, int32_t track_stats);
+
+/* Inference-mode BatchNorm: normalises with the running statistics (normalise.jl:292-304 with
+ * training == false).  running_mean/running_var NULL means track_stats=false: batch statistics are
+ * used as in training, without an update. */
+int32_t fb_batchnorm_fwd_infer(fb_ctx* ctx, void* stream, const float* x, const float* gamma,
+                               const float* beta, const float* running_mean, const float* running_var,
+                               float* y, int64_t s, int64_t c, int64_t n, float eps, int32_t act);
+
+/* Reverse of fb_batchnorm_fwd_train (external NNlib rrule): dx, dgamma[c], dbeta[c]. */
+int32_t fb_batchnorm_bwd(fb_ctx* ctx, void* stream, const float* x, const float* gamma,
+                         const float* beta, const float* save_mean, const float* save_rstd,
+                         const float* dy, float* dx, float* dgamma, float* dbeta, int64_t s, int64_t c,
+                         int64_t n, int32_t act);
+
+/* ----------------------------------------------------------------------- losses / helpers -- */
+
+/* loss = mean_n( -sum_c y[c,n] * logsoftmax(yhat)[c,n] ) with one-hot y given as 1-based int32 labels;
+ * dyhat (optional) = dloss * (softmax - onehot)/n in the same pass.  `loss` is one device float.
+ * Replaces Flux.logitcrossentropy (src/losses/functions.jl:270-273) for one-hot targets. */
+int32_t fb_logitcrossentropy_labels(fb_ctx* ctx, void* stream, const float* yhat,
+                                    const int32_t* labels, float* loss, float* dyhat, int64_t c,
+                                    int64_t n, float dloss);
+
+/* Same for a dense target y[c,n] (label smoothing, soft targets). */
+int32_t fb_logitcrossentropy_dense(fb_ctx* ctx, void* stream, const float* yhat, const float* y,
+                                   float* loss, float* dyhat, int64_t c, int64_t n, float dloss);
+
+/* out[0] = sum(abs2, x) (Base.sum(abs2, y) in the benchmark losses). */
+int32_t fb_sumsq(fb_ctx* ctx, void* stream, const float* x, int64_t count, float* out);
+/* out[0] = sum(x) (Base.sum on the new array type; its cotangent is a fill, done with fb_fill). */
+int32_t fb_sum(fb_ctx* ctx, void* stream, const float* x, int64_t count, float* out);
+/* x[i] = value for all i (Base.fill!, the cotangent of sum). */
+int32_t fb_fill(fb_ctx* ctx, void* stream, float* x, float value, int64_t count);
+/* y = alpha * x (the cotangent 2y of sum(abs2, y); Optimisers' eta scaling). */
+int32_t fb_scale(fb_ctx* ctx, void* stream, const float* x, float alpha, float* y, int64_t count);
+/* y += alpha * x (tangent accumulation `+` of Zygote; `x .-= dx` of Optimisers.update!). */
+int32_t fb_axpy(fb_ctx* ctx, void* stream, float alpha, const float* x, float* y, int64_t count);
+/* Float32 -> BFloat16 bits, round-to-nearest-even in the integer domain, NaN -> 0x7fc0; bit-exact
+ * with Flux._to_bf16 (src/functor.jl:161-166). */
+int32_t fb_cast_f32_bf16(fb_ctx* ctx, void* stream, const float* x, uint16_t* y, int64_t count);
+int32_t fb_cast_bf16_f32(fb_ctx* ctx, void* stream, const uint16_t* x, float* y, int64_t count);
+
+/* ------------------------------------------------------------------------------- Adam -- */
+
+/* One Adam update of `ntensors` parameter leaves in one launch per 32 leaves:
+ * m = b1 m + (1-b1) g; v = b2 v + (1-b2) g^2; w -= m/(1-b1t) / (sqrt(v/(1-b2t)) + eps) * eta.
+ * b1t/b2t are the running powers beta^t *before* this step (the caller multiplies them afterwards,
+ * as the rule's state does).  The pointer tables are host arrays of device pointers.
+ * Replaces Optimisers.update! with the Adam rule (src/train.jl:425; arithmetic as in
+ * src/optimise/optimisers.jl:171-184). grad_scale multiplies g first (1.0 normally). */
+int32_t fb_adam_step(fb_ctx* ctx, void* stream, int32_t ntensors, float* const* w_host,
+                     const float* const* g_host, float* const* m_host, float* const* v_host,
+                     const int64_t* counts_host, float eta, float beta1, float beta2, float eps,
+                     float b1t, float b2t, float grad_scale);
+
+/* ------------------------------------------------------------------------- Recurrence -- */
+
+/* Bytes of the saved-for-backward buffer of fb_lstm_fwd / fb_gru_fwd. */
+int64_t fb_lstm_cache_bytes(int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch);
+int64_t fb_gru_cache_bytes(int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch);
+
+/* Recurrence(LSTMCell)(x): x[in,T,B] -> out[H,T,B], final h[H,B], c[H,B]; zero initial state when
+ * h0/c0 are NULL, else h0/c0 are [H,B].  Gate rows of Wi[4H,in], Wh[4H,H], b[4H] are i,f,g,o.
+ * The input projection runs as one GEMM over all T*B columns; the time loop is one persistent kernel.
+ * `cache` (fb_lstm_cache_bytes) may be NULL when no backward pass follows.
+ * Replaces scan(cell, x, state) (src/layers/recurrent.jl:1-8) over LSTMCell (:411-419). */
+int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream, const float* Wi, const float* Wh, const float* b,
+                    const float* x, const float* h0, const float* c0, float* out, float* hT, float* cT,
+                    void* cache, int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch);
+
+/* Reverse of fb_lstm_fwd (Zygote's BPTT over recurrent.jl:1-8): dout[H,T,B] (+ optional dhT, dcT)
+ * -> dWi, dWh, db (may be NULL), dx (may be NULL).  h0/c0 are the initial
+ * state given to the forward call (NULL = zeros).  The cache is consumed (overwritten). */
+int32_t fb_lstm_bwd(fb_ctx* ctx, void* stream, const float* Wi, const float* Wh, const float* x,
+                    const float* h0, const float* c0, const float* out, const void* cache,
+                    const float* dout, const float* dhT, const float* dcT, float* dWi, float* dWh, float* db, float* dx, int64_t in_dim,
+                    int64_t hidden, int64_t seq_len, int64_t batch);
+
+/* Recurrence(GRUCell)(x) (src/layers/recurrent.jl:614-628; rows r,z,h~; r multiplies Wh3*h). */
+int32_t fb_gru_fwd(fb_ctx* ctx, void* stream, const float* Wi, const float* Wh, const float* b,
+                   const float* x, const float* h0, float* out, float* hT, void* cache, int64_t in_dim,
+                   int64_t hidden, int64_t seq_len, int64_t batch);
+int32_t fb_gru_bwd(fb_ctx* ctx, void* stream, const float* Wi, const float* Wh, const float* x,
+                   const float* h0, const float* out, const void* cache, const float* dout, const float* dhT, float* dWi,
+                   float* dWh, float* db, float* dx, int64_t in_dim, int64_t hidden, int64_t seq_len,
+                   int64_t batch);
+
+/* -------------------------------------------------------------------------- Attention -- */
+
+/* NNlib.dot_product_attention(q, k, v; nheads, mask) without materialising the score tensor:
+ * q[E,Lq,B], k[E,Lk,B], v[Ev,Lk,B] -> o[Ev,Lq,B]; head h is the contiguous feature block
+ * h*d..(h+1)*d-1; scores k'q/sqrt(d); softmax over the kv axis; causal != 0 keeps key j for query i
+ * iff j <= i.  `mask` (optional uint8 [Lk,Lq], nonzero = keep) is applied as well.  lse[Lq,h,B]
+ * (log-sum-exp per query, caller buffer) is saved for the backward pass.
+ * Replaces the call at src/layers/attention.jl:128. */
+int32_t fb_attn_fwd(fb_ctx* ctx, void* stream, const float* q, const float* k, const float* v,
+                    const uint8_t* mask, float* o, float* lse, int64_t e_dim, int64_t ev_dim,
+                    int64_t lq, int64_t lk, int64_t batch, int32_t nheads, int32_t causal);
+
+/* Reverse of fb_attn_fwd (external NNlib rrule): probabilities are recomputed from lse. */
+int32_t fb_attn_bwd(fb_ctx* ctx, void* stream, const float* q, const float* k, const float* v,
+                    const uint8_t* mask, const float* o, const float* lse, const float* dout, float* dq,
+                    float* dk, float* dv, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk,
+                    int64_t batch, int32_t nheads, int32_t causal);
+
+/* The attention weights alpha[Lk,Lq,h,B], the second return value of dot_product_attention
+ * (src/layers/attention.jl:128-132), materialised on demand from q, k and lse. */
+int32_t fb_attn_scores(fb_ctx* ctx, void* stream, const float* q, const float* k, const uint8_t* mask,
+                       const float* lse, float* alpha, int64_t e_dim, int64_t lq, int64_t lk,
+                       int64_t batch, int32_t nheads, int32_t causal);
+
+/* ------------------------------------------------------------------- DistributedUtils -- */
+
+/* NCCL unique id (128 bytes) created on one rank and handed to the others by the caller's bootstrap
+ * (MPI broadcast in ext/FluxMPINCCLExt/FluxMPINCCLExt.jl:19-30; a store or file elsewhere). */
+#define FB_UNIQUE_ID_BYTES 128
+int32_t fb_comm_get_unique_id(void* id_host);
+/* Joins the communicator (NCCL.Communicator, FluxMPINCCLExt.jl:26-29). Blocks until all ranks join. */
+int32_t fb_comm_init_rank(fb_ctx* ctx, const void* id_host, int32_t nranks, int32_t rank, fb_comm** out);
+int32_t fb_comm_destroy(fb_comm* comm);
+/* DistributedUtils.local_rank / total_workers (src/distributed/public_api.jl:82-93). */
+int32_t fb_comm_rank(const fb_comm* comm);
+int32_t fb_comm_size(const fb_comm* comm);
+/* DistributedUtils.allreduce! on a Float32 device buffer, in place when send == recv
+ * (NCCL.Allreduce!, FluxMPINCCLExt.jl:61-78); FB_OP_AVG is DistributedUtils.avg. */
+int32_t fb_allreduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op);
+/* DistributedUtils.bcast! (NCCL.Broadcast!, FluxMPINCCLExt.jl:38-53). */
+int32_t fb_bcast(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t root);
+/* DistributedUtils.reduce! (NCCL.Reduce!, FluxMPINCCLExt.jl:86-102). */
+int32_t fb_reduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op, int32_t root);
+/* Non-zero when NCCL reported an asynchronous error on this communicator (polled by the host between
+ * steps; a dead rank otherwise hangs the next collective, as it does in the reference). */
+int32_t fb_comm_async_error(fb_comm* comm, int32_t* out_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLUXB200_H */

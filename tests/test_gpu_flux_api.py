@@ -1,0 +1,245 @@
+"""GPU tests of the host-side mirror of Flux's API (Chain / Dense / norms / Recurrence / MultiHeadAttention /
+withgradient / setup / trainstep! / train!) against the oracle, written the way the reference's own layer
+and training tests read (test/layers/*.jl, test/train.jl, test/ext_cuda/layers.jl)."""
+import numpy as np
+import pytest
+
+import flux_oracle as O
+from util import close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def F():
+    import fluxb200
+    yield fluxb200
+    assert fluxb200.context().device_error() == 0
+
+
+def test_dense_layer_shapes_errors_and_gradient_tree(F):
+    """test/layers/basic.jl:70-108; gradient field names as src/gradient.jl:112."""
+    rng = np.random.default_rng(0)
+    W = O.glorot_uniform(rng, 5, 10)
+    d = F.Dense(W)
+    for shp in [(10,), (10, 2), (10, 2, 3), (10, 2, 3, 4)]:
+        assert d(F.gpu(rng.normal(size=shp).astype(np.float32))).size == (5,) + shp[1:]
+    with pytest.raises(F.DimensionMismatch):
+        d(F.gpu(np.zeros((11, 2, 3), np.float32)))
+    with pytest.raises(F.DimensionMismatch):
+        d(F.gpu(np.zeros((1,), np.float32)))
+    x = rng.normal(size=(10, 4))
+    close(F.cpu(d(F.gpu(x))), W.astype(np.float64) @ x)          # Float64 input is converted (_match_eltype)
+    d2 = F.Dense(W, False)
+    x32 = F.gpu(x.astype(np.float32))
+    val, (g,) = F.withgradient(lambda m: F.sum_abs2(m(x32)), d2)
+    assert set(g) == {"weight", "bias", "σ"} and g["bias"] is None and g["σ"] is None   # test/ext_cuda/layers.jl:120-127
+    y = W.astype(np.float64) @ x
+    close(val, (y * y).sum())
+    close(F.cpu(g["weight"]), 2 * y @ x.T)
+
+
+def test_mlp_config1_ten_adam_steps_match_oracle(F):
+    """Chain(Dense(784=>512,relu), Dense(512=>512,relu), Dense(512=>10)), batch 1024, logitcrossentropy, Adam(1e-3)."""
+    rng = np.random.default_rng(0)
+    dims = [(512, 784, "relu"), (512, 512, "relu"), (10, 512, "identity")]
+    Ws = [O.glorot_uniform(rng, o, i) for o, i, _ in dims]
+    bs = [np.zeros(o, np.float32) for o, _, _ in dims]
+    x = rng.random((784, 1024), dtype=np.float32)
+    labels = rng.integers(1, 11, size=1024)
+    model = F.Chain(*[F.Dense(W.copy(), b.copy(), s) for W, b, (_, _, s) in zip(Ws, bs, dims)])
+    opt = F.setup(F.Adam(1e-3), model)
+    xg, yg = F.gpu(x), F.onehotbatch(labels, 10)
+    loss = lambda m, x_, y_: F.logitcrossentropy(m(x_), y_)
+    # oracle in float64 with float32-rounded Adam scalars
+    W64 = [w.astype(np.float64) for w in Ws]
+    b64 = [b.astype(np.float64) for b in bs]
+    st = [(O.adam_init(w), O.adam_init(b)) for w, b in zip(W64, b64)]
+    y1h = O.onehotbatch(labels, 10, np.float64)
+    for step in range(10):
+        l = F.trainstep(loss, model, (xg, yg), opt)
+        lref, grads, _ = O.mlp_chain_fwd_bwd([(w, b, s) for w, b, (_, _, s) in zip(W64, b64, dims)], x.astype(np.float64), y1h)
+        close(l, lref, name=f"loss step {step}")
+        for i, (dW, db) in enumerate(grads):
+            W64[i] = O.adam_apply(st[i][0], W64[i], dW)
+            b64[i] = O.adam_apply(st[i][1], b64[i], db)
+    for i, layer in enumerate(model.layers):
+        close(F.cpu(layer.weight), W64[i], rtol=2e-4, atol_scale=2e-4, name=f"W{i}")
+        close(F.cpu(layer.bias), b64[i], rtol=2e-4, atol_scale=2e-3, name=f"b{i}")
+
+
+def test_mlp_gradients_match_oracle(F):
+    rng = np.random.default_rng(1)
+    dims = [(64, 48, "tanh"), (32, 64, "gelu"), (7, 32, "identity")]
+    layers = [(O.glorot_uniform(rng, o, i), (rng.normal(size=o) * 0.1).astype(np.float32), s) for o, i, s in dims]
+    x = rng.normal(size=(48, 33)).astype(np.float32)
+    labels = rng.integers(1, 8, size=33)
+    model = F.Chain(*[F.Dense(W, b, s) for W, b, s in layers])
+    xg, yg = F.gpu(x), F.onehotbatch(labels, 7)
+    val, (g,) = F.withgradient(lambda m: F.logitcrossentropy(m(xg), yg), model)
+    ref_layers = [(W.astype(np.float64), b.astype(np.float64), "gelu_tanh" if s == "gelu" else s) for W, b, s in layers]
+    lref, grads, _ = O.mlp_chain_fwd_bwd(ref_layers, x.astype(np.float64), O.onehotbatch(labels, 7, np.float64))
+    close(val, lref)
+    for gi, (dW, db) in zip(g["layers"], grads):
+        close(F.cpu(gi["weight"]), dW)
+        close(F.cpu(gi["bias"]), db)
+
+
+def test_trainstep_semantics(F):
+    """test/train.jl:37-47 (stop on NaN after 50 Descent(0.1) steps, weight == -5), :130-141 (update skipped),
+    :89-94 (returned loss is pre-update)."""
+    m1 = F.Dense(np.zeros((1, 1), np.float32))
+    opt = F.setup(F.Descent(0.1), m1)
+    one = F.gpu(np.ones((1,), np.float32))
+    cnt = [0]
+
+    def loss(m, i):
+        cnt[0] += 1
+        return F.scale(float("nan") if i == 51 else 1.0, F.sum_all(m(one)))
+
+    with pytest.raises(F.DomainError):
+        F.train(loss, m1, [(i,) for i in range(1, 101)], opt)
+    assert cnt[0] == 51
+    assert abs(F.cpu(m1.weight)[0, 0] + 5) < 1e-5
+    m2 = F.Dense(np.zeros((1, 1), np.float32))
+    opt2 = F.setup(F.Descent(0.1), m2)
+    l = F.trainstep(lambda m, i: F.scale(float("nan"), F.sum_all(m(one))), m2, (1,), opt2)
+    assert not np.isfinite(l)
+    assert F.cpu(m2.weight)[0, 0] == 0 and F.cpu(m2.bias)[0] == 0
+    m3 = F.Dense(np.ones((1, 1), np.float32))
+    opt3 = F.setup(F.Descent(0.1), m3)
+    l3 = F.trainstep(lambda m: F.sum_all(m(one)), m3, (), opt3)
+    assert abs(l3 - 1.0) < 1e-6 and abs(F.cpu(m3.weight)[0, 0] - 0.9) < 1e-6
+
+
+def test_batchnorm_layer_modes(F):
+    """test/layers/normalisation.jl:125-159 and test/ext_cuda/layers.jl:129-181: statistics are tracked only
+    in gradient / train mode; test mode uses them."""
+    x = np.array([[1.0, 3.0, 5.0], [2.0, 4.0, 6.0]], np.float32)
+    m = F.BatchNorm(2)
+    assert len(F.trainables(m)) == 2
+    xg = F.gpu(x)
+    y = F.cpu(m(xg))                                   # outside a gradient call: inference with mu = 0, var = 1
+    np.testing.assert_allclose(y, x / np.sqrt(1 + 1e-5), rtol=1e-6)
+    np.testing.assert_allclose(F.cpu(m.μ), [0, 0])
+    val, (g,) = F.withgradient(lambda mm: F.sum_abs2(mm(xg)), m)
+    np.testing.assert_allclose(F.cpu(m.μ), [0.3, 0.4], rtol=1e-6)
+    np.testing.assert_allclose(F.cpu(m.σ2), [1.3, 1.3], rtol=1e-6)
+    assert g["μ"] is None and g["γ"] is not None
+    F.trainmode(m)
+    np.testing.assert_allclose(F.cpu(m(xg)), [[-1.22474, 0, 1.22474]] * 2, atol=1e-5)
+    F.testmode(m)
+    assert abs(F.cpu(m(xg))[0, 0] - (1 - F.cpu(m.μ)[0]) / np.sqrt(F.cpu(m.σ2)[0] + 1e-5)) < 1e-5
+    m1 = F.trainmode(F.BatchNorm(1))
+    with pytest.raises(F.ArgumentError):
+        m1(F.gpu(np.zeros((1, 1), np.float32)))
+    m1(F.gpu(np.arange(4, dtype=np.float32).reshape(4, 1, 1)))
+    with pytest.raises(F.DimensionMismatch):
+        F.BatchNorm(3)(xg)
+
+
+def test_layernorm_layer(F):
+    rng = np.random.default_rng(2)
+    x = rng.random((2, 3, 4, 5)).astype(np.float32)
+    y = F.cpu(F.LayerNorm(2)(F.gpu(x)))
+    x64 = x.astype(np.float64)
+    close(y, (x64 - x64.mean(0, keepdims=True)) / np.sqrt(x64.var(0, keepdims=True) + 1e-5))
+    y2 = F.cpu(F.LayerNorm(2, 3)(F.gpu(x)))
+    close(y2, (x64 - x64.mean((0, 1), keepdims=True)) / np.sqrt(x64.var((0, 1), keepdims=True) + 1e-5))
+    m = F.LayerNorm((2, 3, 4))
+    assert len(F.trainables(m)) == 2 and len(F.trainables(F.LayerNorm((2, 3, 4), affine=False))) == 0
+    with pytest.raises(F.DimensionMismatch):
+        F.LayerNorm(3)(F.gpu(x))
+
+
+def test_recurrence_lstm_gru(F):
+    """test/layers/recurrent.jl:113-197, 336-356: zero initial state, state shapes, Recurrence(cell) == LSTM(...)."""
+    rng = np.random.default_rng(3)
+    I, H, T, B = 5, 8, 6, 4
+    x = rng.normal(size=(I, T, B)).astype(np.float32)
+    xg = F.gpu(x)
+    for ng, Cell, Wrap, fwd, bwd in [(4, F.LSTMCell, F.LSTM, O.lstm_scan_fwd, O.lstm_scan_bwd),
+                                     (3, F.GRUCell, F.GRU, O.gru_scan_fwd, O.gru_scan_bwd)]:
+        Wi, Wh = O.glorot_uniform(rng, ng * H, I), O.glorot_uniform(rng, ng * H, H)
+        b = (rng.normal(size=ng * H) * 0.1).astype(np.float32)
+        rnn = F.Recurrence(Cell(Wi, Wh, b))
+        y = rnn(xg)
+        assert y.size == (H, T, B)
+        ref = fwd(*[a.astype(np.float64) for a in (Wi, Wh, b, x)])[0]
+        close(F.cpu(y), ref)
+        close(F.cpu(Wrap(Wi, Wh, b)(xg)), ref)
+        y0 = rnn(xg, rnn.cell.initialstates())            # explicit zero state vectors broadcast over the batch
+        np.testing.assert_array_equal(F.cpu(y0), F.cpu(y))
+        out, state = F.Recurrence(Cell(Wi, Wh, b), return_state=True)(xg)
+        hT = state[0] if ng == 4 else state
+        assert hT.size == (H, B)
+        np.testing.assert_array_equal(F.cpu(hT), F.cpu(out)[:, -1, :])
+        val, (g,) = F.withgradient(lambda m: F.sum_abs2(m(xg)), rnn)
+        dWi, dWh, db, _ = bwd(*[a.astype(np.float64) for a in (Wi, Wh, b, x)], O.sum_abs2_bwd(ref))
+        close(val, (ref * ref).sum())
+        close(F.cpu(g["cell"]["Wi"]), dWi, rtol=2e-4, atol_scale=2e-4)
+        close(F.cpu(g["cell"]["Wh"]), dWh, rtol=2e-4, atol_scale=2e-4)
+        close(F.cpu(g["cell"]["bias" if ng == 4 else "b"]), db, rtol=2e-4, atol_scale=2e-4)
+        y2 = rnn(F.gpu(x[:, :, 0]))                        # 2-d input: (features, len)
+        assert y2.size == (H, T)
+
+
+def test_multiheadattention_layer(F):
+    """test/layers/attention.jl:3-63 and test/ext_cuda/layers.jl:343-363 (y and alpha, atol 1e-4)."""
+    rng = np.random.default_rng(4)
+    dim, nheads, L, B = 16, 4, 10, 3
+    Ws = [O.glorot_uniform(rng, dim, dim) for _ in range(4)]
+    mha = F.MultiHeadAttention(*Ws, nheads=nheads)
+    q = rng.normal(size=(dim, L, B)).astype(np.float32)
+    qg = F.gpu(q)
+    W64 = [w.astype(np.float64) for w in Ws]
+    y, a = mha(qg)
+    assert y.size == (dim, L, B) and a.size == (L, L, nheads, B)
+    yref, aref = O.mha_fwd(*W64, q.astype(np.float64), nheads=nheads)
+    np.testing.assert_allclose(F.cpu(y), yref, atol=1e-4)
+    np.testing.assert_allclose(F.cpu(a.materialize()), aref, atol=1e-4)
+    y, a = mha(qg, mask=F.make_causal_mask(qg))
+    al = F.cpu(a.materialize())
+    assert (al[1, 0, :, :] == 0).all()
+    np.testing.assert_allclose(al[:, :, 0, 0], np.triu(al[:, :, 0, 0]))
+    yref, aref = O.mha_fwd(*W64, q.astype(np.float64), nheads=nheads, mask=O.make_causal_mask(L))
+    np.testing.assert_allclose(F.cpu(y), yref, atol=1e-4)
+    kv = rng.normal(size=(dim, 7, B)).astype(np.float32)
+    y, a = mha(qg, F.gpu(kv))
+    assert y.size == (dim, L, B) and a.size == (7, L, nheads, B)
+    val, (g,) = F.withgradient(lambda m: F.sum_abs2(m(qg, mask=F.make_causal_mask(qg))[0]), mha)
+    dWq, dWk, dWv, dWo, _ = O.mha_bwd(*W64, q.astype(np.float64), O.sum_abs2_bwd(yref), nheads=nheads, mask=O.make_causal_mask(L))
+    for name, ref in [("q_proj", dWq), ("k_proj", dWk), ("v_proj", dWv), ("out_proj", dWo)]:
+        close(F.cpu(g[name]["weight"]), ref, rtol=2e-4, atol_scale=2e-4, name=name)
+        assert g[name]["bias"] is None
+    with pytest.raises(F.ArgumentError):
+        F.MultiHeadAttention(*Ws, nheads=3)
+
+
+def test_dp_block_model_gradients_match_oracle(F):
+    """The data-parallel benchmark model at reduced width: LayerNorm -> Dense(gelu) blocks + classifier."""
+    rng = np.random.default_rng(5)
+    D, Cc, N, nb = 256, 40, 96, 3
+    blocks = [{"gamma": (rng.normal(size=D) * 0.1 + 1).astype(np.float32), "beta": (rng.normal(size=D) * 0.1).astype(np.float32),
+               "W": O.glorot_uniform(rng, D, D), "b": np.zeros(D, np.float32)} for _ in range(nb)]
+    head = {"W": O.glorot_uniform(rng, Cc, D), "b": np.zeros(Cc, np.float32)}
+    x = rng.normal(size=(D, N)).astype(np.float32)
+    labels = rng.integers(1, Cc + 1, size=N)
+    layers = []
+    for blk in blocks:
+        ln = F.LayerNorm(D)
+        ln.diag.scale, ln.diag.bias = F.gpu(blk["gamma"]), F.gpu(blk["beta"])
+        layers += [ln, F.Dense(blk["W"], blk["b"], "gelu")]
+    layers.append(F.Dense(head["W"], head["b"]))
+    model = F.Chain(*layers)
+    xg, yg = F.gpu(x), F.onehotbatch(labels, Cc)
+    val, (g,) = F.withgradient(lambda m: F.logitcrossentropy(m(xg), yg), model)
+    to64 = lambda d: {k: v.astype(np.float64) for k, v in d.items()}
+    lref, gb, gh = O.dp_mlp_fwd_bwd([to64(b) for b in blocks], to64(head), x.astype(np.float64), O.onehotbatch(labels, Cc, np.float64))
+    close(val, lref)
+    for i, ref in enumerate(gb):
+        close(F.cpu(g["layers"][2 * i]["diag"]["scale"]), ref["gamma"], rtol=2e-4, atol_scale=2e-4)
+        close(F.cpu(g["layers"][2 * i]["diag"]["bias"]), ref["beta"], rtol=2e-4, atol_scale=2e-4)
+        close(F.cpu(g["layers"][2 * i + 1]["weight"]), ref["W"], rtol=2e-4, atol_scale=2e-4)
+        close(F.cpu(g["layers"][2 * i + 1]["bias"]), ref["b"], rtol=2e-4, atol_scale=2e-4)
+    close(F.cpu(g["layers"][-1]["weight"]), gh["W"], rtol=2e-4, atol_scale=2e-4)
