@@ -10,7 +10,13 @@
 // 4-stage ring.  Warp roles: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs,
 // warps 2-5 split the landed tiles into hi / lo and afterwards run the epilogue (one TMEM lane quadrant
 // each).  Operands may be K-major (k contiguous) or MN-major (m / n contiguous) in global memory; the
-// shared-memory layouts are the canonical 64-byte- and 128-byte-swizzled ones the MMA descriptors name.
+// shared-memory layouts are the canonical ones the MMA descriptors name: 64-byte swizzle for K-major tiles
+// (8 rows x 64 B atoms) and, for MN-major tiles, the 128-byte swizzle with 32-byte atoms (128 B x 4 k-rows
+// per atom), which is the only MN-major layout the tensor core accepts for 32-bit operands.
+//
+// The tensor core adds into its fp32 accumulator with truncation, so a long K chain drifts (about 3e-5 of
+// max|C| at K = 4096).  K is therefore cut into segments of 2048: after each segment the epilogue warps drain
+// tensor memory into C with round-to-nearest adds and the next segment starts from a zeroed accumulator.
 //
 // Every mbarrier wait is bounded; when a wait runs out the kernel records a code in the context's
 // device error word, every role leaves its loop, tensor memory is released and the kernel returns.
@@ -25,6 +31,7 @@ constexpr int BK = 16;               // floats per k-block (64 bytes)
 constexpr int STAGES = 4;
 constexpr int NUM_THREADS = 192;     // 6 warps
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
+constexpr int SEG_KB = 128;          // k-blocks per accumulation segment (2048 k-values)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -105,7 +112,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= (uint64_t)(layout_type & 7u) << 61;
   return d;
 }
-constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_SW64 = 4;
+constexpr uint32_t LAYOUT_SW128_32B = 1, LAYOUT_SW64 = 4;   // MN-major 32-bit operands only exist in the 32-byte-atom 128B swizzle
 
 template <int BN, int PASSES>
 struct Cfg {
@@ -127,13 +134,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t smem_base = smem_u32(smem);
   uint64_t* bars = (uint64_t*)(smem + cfg::BAR_OFFSET);
   const uint32_t bar_base = smem_base + cfg::BAR_OFFSET;
-  // barrier slots: full[0..S), ready[S..2S), empty[2S..3S), tmem_full[3S]
+  // barrier slots: full[0..S), ready[S..2S), empty[2S..3S), tmem_full[3S], tmem_empty[3S+1]
   auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
   auto ready_bar = [&](int s) { return bar_base + 8u * (uint32_t)(STAGES + s); };
   auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * STAGES + s); };
   const uint32_t tmem_full_bar = bar_base + 8u * (uint32_t)(3 * STAGES);
-  volatile uint32_t* s_tmem = (volatile uint32_t*)(bars + 3 * STAGES + 1);
-  volatile int* s_abort = (volatile int*)(bars + 3 * STAGES + 2);
+  const uint32_t tmem_empty_bar = bar_base + 8u * (uint32_t)(3 * STAGES + 1);
+  volatile uint32_t* s_tmem = (volatile uint32_t*)(bars + 3 * STAGES + 2);
+  volatile int* s_abort = (volatile int*)(bars + 3 * STAGES + 3);
 
   // a wait that ran out earlier (in this or a previous launch) leaves the error word set: do not start
   __shared__ int s_skip;
@@ -151,6 +159,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
+    mbar_init(tmem_empty_bar, 4);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
@@ -201,6 +210,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        const int seg = kb / SEG_KB, kb_in_seg = kb % SEG_KB;
+        if (kb_in_seg == 0 && seg > 0) {
+          // the epilogue warps must have drained the previous segment out of tensor memory
+          ok = mbar_wait(tmem_empty_bar, (uint32_t)(seg - 1) & 1u, s_abort);
+          if (!ok) break;
+        }
         ok = mbar_wait(PASSES == 3 ? ready_bar(s) : full_bar(s), ph, s_abort);
         if (!ok) break;
         tc_fence_after();
@@ -210,18 +225,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t b_lo = b_hi + (uint32_t)cfg::B_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BK / 8; ++kk) {
-          // one MMA covers 8 k-values: 32 bytes along a K-major row, one 1024-byte atom of an MN-major tile
+          // one MMA covers 8 k-values: 32 bytes along a K-major row, eight 128-byte k-rows of an MN-major tile
           const uint32_t a_off = A_MN ? (uint32_t)(kk * 1024) : (uint32_t)(kk * 32);
           const uint32_t b_off = B_MN ? (uint32_t)(kk * 1024) : (uint32_t)(kk * 32);
-          const uint64_t da_hi = A_MN ? make_smem_desc(a_hi + a_off, BK * 128, 1024, LAYOUT_SW128)
+          const uint64_t da_hi = A_MN ? make_smem_desc(a_hi + a_off, BK * 128, 512, LAYOUT_SW128_32B)
                                       : make_smem_desc(a_hi + a_off, 16, 512, LAYOUT_SW64);
-          const uint64_t db_hi = B_MN ? make_smem_desc(b_hi + b_off, BK * 128, 1024, LAYOUT_SW128)
+          const uint64_t db_hi = B_MN ? make_smem_desc(b_hi + b_off, BK * 128, 512, LAYOUT_SW128_32B)
                                       : make_smem_desc(b_hi + b_off, 16, 512, LAYOUT_SW64);
-          const uint32_t first = (kb > 0 || kk > 0) ? 1u : 0u;
+          const uint32_t first = (kb_in_seg > 0 || kk > 0) ? 1u : 0u;
           if (PASSES == 3) {
-            const uint64_t da_lo = A_MN ? make_smem_desc(a_lo + a_off, BK * 128, 1024, LAYOUT_SW128)
+            const uint64_t da_lo = A_MN ? make_smem_desc(a_lo + a_off, BK * 128, 512, LAYOUT_SW128_32B)
                                         : make_smem_desc(a_lo + a_off, 16, 512, LAYOUT_SW64);
-            const uint64_t db_lo = B_MN ? make_smem_desc(b_lo + b_off, BK * 128, 1024, LAYOUT_SW128)
+            const uint64_t db_lo = B_MN ? make_smem_desc(b_lo + b_off, BK * 128, 512, LAYOUT_SW128_32B)
                                         : make_smem_desc(b_lo + b_off, 16, 512, LAYOUT_SW64);
             tc_mma_tf32(tmem_base, da_lo, db_hi, idesc, first);
             tc_mma_tf32(tmem_base, da_hi, db_lo, idesc, 1u);
@@ -231,13 +246,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         tc_commit(empty_bar(s));   // frees the stage once these MMAs have read it
+        if (kb_in_seg == SEG_KB - 1 || kb == num_kb - 1) tc_commit(tmem_full_bar);   // segment complete
       }
-      if (ok) tc_commit(tmem_full_bar);
     }
   } else {
-    // ------------------------------------------- hi / lo split, then the epilogue ---
+    // ------------------------------------- hi / lo split, and the epilogue per K segment ---
     const int tt = threadIdx.x - 64;  // 0..127
+    const int q = warp & 3;           // TMEM lane quadrant this warp may read
+    const int row = m0 + 32 * q + lane;
+    float* crow = C + (int64_t)row * ldc;
+    float* zrow = Z ? Z + (int64_t)row * ldc : nullptr;
+    const int num_seg = (num_kb + SEG_KB - 1) / SEG_KB;
     bool ok = true;
+
+    // Drains the accumulator of segment `seg`: intermediate segments add into C (round-to-nearest fp32 adds),
+    // the last one also applies bias, pre-activation store and activation.
+    auto drain = [&](int seg) -> bool {
+      if (!mbar_wait(tmem_full_bar, (uint32_t)seg & 1u, s_abort)) return false;
+      tc_fence_after();
+      const bool last = (seg == num_seg - 1);
+      const bool add_c = (seg > 0) || (accumulate != 0);
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        const int nb = n0 + cc * 32;
+        if (nb >= N) break;   // warp-uniform
+        uint32_t r[32];
+        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(cc * 32), r);
+        tc_wait_ld();
+        if (row < M) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int n = nb + 4 * j;
+            float v[4] = {__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                          __uint_as_float(r[4 * j + 3])};
+            if (n + 3 < N) {
+              if (add_c) {
+                const float4 c4 = *(const float4*)(crow + n);
+                v[0] += c4.x; v[1] += c4.y; v[2] += c4.z; v[3] += c4.w;
+              }
+              if (last) {
+                if (bias_n) {
+                  const float4 b4 = __ldg((const float4*)(bias_n + n));
+                  v[0] += b4.x; v[1] += b4.y; v[2] += b4.z; v[3] += b4.w;
+                }
+                if (zrow) *(float4*)(zrow + n) = make_float4(v[0], v[1], v[2], v[3]);
+                if (act != FB_ACT_IDENTITY) {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) v[e] = fb_act_apply(act, v[e]);
+                }
+              }
+              *(float4*)(crow + n) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+              for (int e = 0; e < 4 && n + e < N; ++e) {
+                float u = v[e];
+                if (add_c) u += crow[n + e];
+                if (last) {
+                  if (bias_n) u += __ldg(bias_n + n + e);
+                  if (zrow) zrow[n + e] = u;
+                  u = fb_act_apply(act, u);
+                }
+                crow[n + e] = u;
+              }
+            }
+          }
+        }
+      }
+      if (!last) {
+        // tensor memory may be overwritten by the next segment once every warp has read its quadrant
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tmem_empty_bar);
+      }
+      return true;
+    };
+
     if (PASSES == 3) {
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % STAGES;
@@ -273,55 +355,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         fence_proxy_async();   // generic-proxy writes become visible to the tensor core's async-proxy reads
         __syncwarp();
         if (lane == 0) mbar_arrive(ready_bar(s));
+        if (kb % SEG_KB == SEG_KB - 1 || kb == num_kb - 1) ok = drain(kb / SEG_KB);
       }
-    }
-    if (ok) ok = mbar_wait(tmem_full_bar, 0u, s_abort);
-    if (ok) {
-      tc_fence_after();
-      const int q = warp & 3;                 // TMEM lane quadrant this warp may read
-      const int row = m0 + 32 * q + lane;
-      float* crow = C + (int64_t)row * ldc;
-      float* zrow = Z ? Z + (int64_t)row * ldc : nullptr;
-#pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        const int nb = n0 + cc * 32;
-        if (nb >= N) break;   // warp-uniform
-        uint32_t r[32];
-        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(cc * 32), r);
-        tc_wait_ld();
-        if (row < M) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int n = nb + 4 * j;
-            float v[4] = {__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                          __uint_as_float(r[4 * j + 3])};
-            if (n + 3 < N) {
-              if (accumulate) {
-                const float4 c4 = *(const float4*)(crow + n);
-                v[0] += c4.x; v[1] += c4.y; v[2] += c4.z; v[3] += c4.w;
-              }
-              if (bias_n) {
-                const float4 b4 = __ldg((const float4*)(bias_n + n));
-                v[0] += b4.x; v[1] += b4.y; v[2] += b4.z; v[3] += b4.w;
-              }
-              if (zrow) *(float4*)(zrow + n) = make_float4(v[0], v[1], v[2], v[3]);
-              if (act != FB_ACT_IDENTITY) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) v[e] = fb_act_apply(act, v[e]);
-              }
-              *(float4*)(crow + n) = make_float4(v[0], v[1], v[2], v[3]);
-            } else {
-              for (int e = 0; e < 4 && n + e < N; ++e) {
-                float u = v[e];
-                if (accumulate) u += crow[n + e];
-                if (bias_n) u += __ldg(bias_n + n + e);
-                if (zrow) zrow[n + e] = u;
-                crow[n + e] = fb_act_apply(act, u);
-              }
-            }
-          }
-        }
-      }
+    } else {
+      for (int seg = 0; seg < num_seg && ok; ++seg) ok = drain(seg);
     }
   }
 
@@ -376,10 +413,10 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   using cfg = Cfg<BN, PASSES>;
   CUtensorMap tmA, tmB;
   bool ok;
-  if (A_MN) ok = encode_map(&tmA, a.A, a.K, a.M, a.lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (A_MN) ok = encode_map(&tmA, a.A, a.K, a.M, a.lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   else ok = encode_map(&tmA, a.A, a.M, a.K, a.lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_64B);
   if (ok) {
-    if (B_MN) ok = encode_map(&tmB, a.B, a.K, a.N, a.ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (B_MN) ok = encode_map(&tmB, a.B, a.K, a.N, a.ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     else ok = encode_map(&tmB, a.B, a.N, a.K, a.ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_64B);
   }
   if (!ok) return fb_fail(FB_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed (M=%lld N=%lld K=%lld lda=%lld ldb=%lld)",

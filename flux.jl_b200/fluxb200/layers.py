@@ -167,7 +167,7 @@ class Dense(Layer):
 class LayerNorm(Layer):
     """LayerNorm(size..., λ; affine=true, eps=1f-5) (normalise.jl:186-210); `diag` is the Scale."""
 
-    _fields = ("λ", "diag", "ϵ", "size", "affine")
+    _fields = ("λ", "diag", "ε", "size", "affine")
     _trainable = ("diag",)
 
     class _Scale(Layer):
@@ -185,7 +185,7 @@ class LayerNorm(Layer):
         self.size = tuple(int(s) for s in size)
         self.λ = _act_name(sigma)
         self.affine = bool(affine)
-        self.ϵ = float(eps)
+        self.ε = float(eps)
         self.diag = LayerNorm._Scale(self.size, self.λ) if affine else None
 
     def __repr__(self):
@@ -205,7 +205,7 @@ class LayerNorm(Layer):
         b = self.diag.bias if self.affine else None
         y, mean, rstd = empty(x.size), empty((n,)), empty((n,))
         lib.call("fb_layernorm_fwd", ctx.handle, ctx.stream, x.ptr, _ptr(g), _ptr(b), y.ptr, mean.ptr, rstd.ptr, d, n,
-                 self.ϵ, act)
+                 self.ε, act)
         if Tape.active:
             def pullback(gs, x=x):
                 dy = gs[0]
@@ -230,14 +230,14 @@ class BatchNorm(Layer):
 
     `active=None` means automatic: training under `withgradient`, inference otherwise (`_isactive`)."""
 
-    _fields = ("λ", "β", "γ", "μ", "σ2", "ϵ", "momentum", "affine", "track_stats", "active", "chs")
+    _fields = ("λ", "β", "γ", "μ", "σ2", "ε", "momentum", "affine", "track_stats", "active", "chs")
     _trainable = ("β", "γ")
 
     def __init__(self, chs: int, sigma="identity", affine=True, track_stats=True, active=None, eps=1e-5, momentum=0.1):
         self.chs = int(chs)
         self.λ = _act_name(sigma)
         self.affine, self.track_stats, self.active = bool(affine), bool(track_stats), active
-        self.ϵ, self.momentum = float(eps), float(momentum)
+        self.ε, self.momentum = float(eps), float(momentum)
         self.β = gpu(np.zeros(chs, np.float32)) if affine else None
         self.γ = gpu(np.ones(chs, np.float32)) if affine else None
         self.μ = gpu(np.zeros(chs, np.float32)) if track_stats else None
@@ -266,11 +266,11 @@ class BatchNorm(Layer):
         y = empty(x.size)
         if not training and self.track_stats:
             lib.call("fb_batchnorm_fwd_infer", ctx.handle, ctx.stream, x.ptr, _ptr(self.γ), _ptr(self.β), self.μ.ptr,
-                     self.σ2.ptr, y.ptr, s, c, n, self.ϵ, act)
+                     self.σ2.ptr, y.ptr, s, c, n, self.ε, act)
             return y
         mean, rstd = empty((c,)), empty((c,))
         lib.call("fb_batchnorm_fwd_train", ctx.handle, ctx.stream, x.ptr, _ptr(self.γ), _ptr(self.β), _ptr(self.μ),
-                 _ptr(self.σ2), y.ptr, mean.ptr, rstd.ptr, s, c, n, self.ϵ, self.momentum, act,
+                 _ptr(self.σ2), y.ptr, mean.ptr, rstd.ptr, s, c, n, self.ε, self.momentum, act,
                  1 if (training and self.track_stats) else 0)
         if Tape.active:
             g, b = self.γ, self.β

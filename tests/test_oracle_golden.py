@@ -268,6 +268,8 @@ def test_committed_golden_fixture_roundtrip():
     path = os.path.join(GOLD, "oracle_vectors.npz")
     if not os.path.exists(path):
         pytest.skip("golden fixture not generated yet")
+    import sys
+    sys.path.insert(0, GOLD)
     import make_golden
     fresh = make_golden.generate()
     stored = np.load(path)
