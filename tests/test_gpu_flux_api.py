@@ -40,7 +40,13 @@ def test_dense_layer_shapes_errors_and_gradient_tree(F):
 
 
 def test_mlp_config1_ten_adam_steps_match_oracle(F):
-    """Chain(Dense(784=>512,relu), Dense(512=>512,relu), Dense(512=>10)), batch 1024, logitcrossentropy, Adam(1e-3)."""
+    """Chain(Dense(784=>512,relu), Dense(512=>512,relu), Dense(512=>10)), batch 1024, logitcrossentropy, Adam(1e-3).
+
+    Adam's normalised step amplifies rounding noise wherever a gradient changes sign between steps (a Float32 and
+    a Float64 run of the oracle itself drift apart by several eta within ten steps), so a free-running trajectory
+    is not a well-posed parity target.  Every step therefore starts from the oracle's state (parameters, moments,
+    beta powers): the device runs one full trainstep from it and loss and updated parameters are compared."""
+    import torch
     rng = np.random.default_rng(0)
     dims = [(512, 784, "relu"), (512, 512, "relu"), (10, 512, "identity")]
     Ws = [O.glorot_uniform(rng, o, i) for o, i, _ in dims]
@@ -51,31 +57,36 @@ def test_mlp_config1_ten_adam_steps_match_oracle(F):
     opt = F.setup(F.Adam(1e-3), model)
     xg, yg = F.gpu(x), F.onehotbatch(labels, 10)
     loss = lambda m, x_, y_: F.logitcrossentropy(m(x_), y_)
-    # oracle in float64 with float32-rounded Adam scalars
     W64 = [w.astype(np.float64) for w in Ws]
     b64 = [b.astype(np.float64) for b in bs]
     st = [(O.adam_init(w), O.adam_init(b)) for w, b in zip(W64, b64)]
     y1h = O.onehotbatch(labels, 10, np.float64)
+
+    def put(arr, value):
+        arr.t.copy_(torch.from_numpy(np.ascontiguousarray(value.astype(np.float32).reshape(-1, order="F"))))
+
     for step in range(10):
+        for i, layer in enumerate(model.layers):
+            for p, val, state in ((layer.weight, W64[i], st[i][0]), (layer.bias, b64[i], st[i][1])):
+                leaf = opt.leaves[id(p)]
+                put(p, val)
+                put(leaf.state[0], state[0])
+                put(leaf.state[1], state[1])
+                leaf.state[2] = (float(np.float32(state[2][0])), float(np.float32(state[2][1])))
         l = F.trainstep(loss, model, (xg, yg), opt)
         lref, grads, _ = O.mlp_chain_fwd_bwd([(w, b, s) for w, b, (_, _, s) in zip(W64, b64, dims)], x.astype(np.float64), y1h)
         close(l, lref, name=f"loss step {step}")
         for i, (dW, db) in enumerate(grads):
             W64[i] = O.adam_apply(st[i][0], W64[i], dW)
             b64[i] = O.adam_apply(st[i][1], b64[i], db)
-        if step == 0:
-            # first Adam step: every parameter moves by eta * sign(g); compare where g is above rounding noise
-            for i, layer in enumerate(model.layers):
-                gabs = np.abs(grads[i][0])
-                solid = gabs > 1e-3 * gabs.max()
-                bad = np.abs(F.cpu(layer.weight)[solid] - W64[i][solid]) > 1e-6 + 1e-5 * np.abs(W64[i][solid])
-                assert bad.mean() < 1e-4, f"W{i}: {bad.sum()} of {bad.size} first-step updates differ"   # a relu unit at exactly 0 may flip
-    # Adam's normalised step amplifies rounding noise wherever the gradient changes sign between steps (a Float32
-    # and a Float64 run of the oracle itself differ by several eta after ten steps), so beyond the per-step loss
-    # the trajectories are only required to stay within the ten steps' reach of each other.
-    for i, layer in enumerate(model.layers):
-        assert np.max(np.abs(F.cpu(layer.weight) - W64[i])) < 1e-2
-        assert np.mean(np.abs(F.cpu(layer.weight) - W64[i])) < 2e-4
+        for i, layer in enumerate(model.layers):
+            gabs = np.abs(grads[i][0])
+            solid = gabs > 1e-2 * gabs.max()          # gradient well above rounding noise
+            got, ref = F.cpu(layer.weight), W64[i]
+            # a gradient error of 1e-4 * max|g| (the parity tolerance) moves an update by at most ~1e-2 * eta here
+            bad = np.abs(got[solid] - ref[solid]) > 2e-5
+            assert bad.mean() < 1e-3, f"step {step} W{i}: {bad.sum()} of {bad.size} updates differ"   # relu units at 0 may flip
+            assert np.max(np.abs(got - ref)) < 2.1e-3  # nothing moves further than one Adam step from the oracle
 
 
 def test_mlp_gradients_match_oracle(F):
