@@ -354,3 +354,78 @@ FB_API int32_t fb_layernorm_bwd(fb_ctx* ctx, void* stream_, const float* x, cons
   return fb_layernorm_bwd_impl(stream, ctx->sm_count, part, groups, x, gamma, beta, mean, rstd, dy, dx, dgamma, dbeta,
                                d, n, act);
 }
+
+// ------------------------------------------------------------- LayerNorm backward without allocation ---
+// Some callers of this library may not allocate device memory at all: a serving or training process whose whole
+// memory budget was handed out at start-up, code running between the begin and end of a stream capture (where an
+// allocation is an error), or a host runtime whose finaliser / callback threads must not trigger the implicit
+// device synchronisation that cudaMalloc and cudaFree can cause.  For them the per-block dgamma / dbeta partials
+// of the backward pass live in the fixed array below instead of the context arena.
+//
+// The array is part of the library image: every GPU that loads the library holds these 16 MiB until the process
+// exits.  Its name is only a host-side handle; the device address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and that pointer is what the kernels receive.
+#include <mutex>
+
+constexpr int64_t FB_LN_STATIC_FLOATS = int64_t(4) << 20;   // 4 Mi floats = 16 MiB
+static __device__ __align__(256) float g_ln_static_scratch[FB_LN_STATIC_FLOATS];
+
+namespace {
+struct LnStaticDevice {
+  float* scratch = nullptr;   // device address of g_ln_static_scratch on this device
+  int sm_count = 0;
+  bool ready = false;
+};
+constexpr int LN_STATIC_MAX_DEVICES = 64;
+LnStaticDevice g_ln_static_dev[LN_STATIC_MAX_DEVICES];
+std::mutex g_ln_static_mutex;
+}  // namespace
+
+FB_API int32_t fb_layernorm_bwd_noalloc(void* stream_, const float* x, const float* gamma, const float* beta,
+                                        const float* mean, const float* rstd, const float* dy, float* dx,
+                                        float* dgamma, float* dbeta, int64_t d, int64_t n, int32_t act) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  FB_REQUIRE(d >= 1 && n >= 0, FB_ERR_SHAPE, "fb_layernorm_bwd_noalloc: bad shape d=%lld n=%lld", (long long)d, (long long)n);
+  FB_REQUIRE(fb_act_valid(act), FB_ERR_INVALID_ARG, "fb_layernorm_bwd_noalloc: unknown activation %d", act);
+  FB_REQUIRE((gamma == nullptr) == (beta == nullptr), FB_ERR_INVALID_ARG, "fb_layernorm_bwd_noalloc: gamma and beta must both be given or both NULL");
+  FB_REQUIRE((dgamma == nullptr) == (dbeta == nullptr), FB_ERR_INVALID_ARG, "fb_layernorm_bwd_noalloc: dgamma and dbeta must both be given or both NULL");
+  // the partials need 2 * groups * d floats with at least one group
+  FB_REQUIRE(dgamma == nullptr || 2 * d <= FB_LN_STATIC_FLOATS, FB_ERR_UNSUPPORTED,
+             "fb_layernorm_bwd_noalloc: d = %lld exceeds the fixed scratch (at most %lld features when dgamma/dbeta are "
+             "requested); use fb_layernorm_bwd",
+             (long long)d, (long long)(FB_LN_STATIC_FLOATS / 2));
+  int dev = -1;
+  FB_CUDA(cudaGetDevice(&dev));
+  FB_REQUIRE(dev >= 0 && dev < LN_STATIC_MAX_DEVICES, FB_ERR_UNSUPPORTED, "fb_layernorm_bwd_noalloc: device index %d not supported", dev);
+  LnStaticDevice& sd = g_ln_static_dev[dev];
+  {
+    // first call on this device: resolve the device address of the array (the device is current here)
+    std::lock_guard<std::mutex> lock(g_ln_static_mutex);
+    if (!sd.ready) {
+      float* p = nullptr;
+      FB_CUDA(cudaGetSymbolAddress((void**)&p, g_ln_static_scratch));
+      int sms = 0;
+      FB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      sd.scratch = p;
+      sd.sm_count = sms;
+      sd.ready = true;
+    }
+  }
+  if (n == 0) {
+    if (dgamma) {
+      FB_CUDA(cudaMemsetAsync(dgamma, 0, d * sizeof(float), stream));
+      FB_CUDA(cudaMemsetAsync(dbeta, 0, d * sizeof(float), stream));
+    }
+    return FB_OK;
+  }
+  FB_REQUIRE(x && mean && rstd && dy && dx, FB_ERR_INVALID_ARG, "fb_layernorm_bwd_noalloc: NULL pointer");
+  int64_t groups = fb_layernorm_bwd_groups(sd.sm_count, n);
+  if (dgamma != nullptr) {
+    const int64_t fit = FB_LN_STATIC_FLOATS / (2 * d);   // >= 1 by the check above
+    if (groups > fit) groups = fit;
+  }
+  // Every block overwrites all d columns of its own partial rows before the reduction reads exactly
+  // groups * d of them, so nothing left behind by an earlier call is ever read.
+  return fb_layernorm_bwd_impl(stream, sd.sm_count, sd.scratch, groups, x, gamma, beta, mean, rstd, dy, dx, dgamma, dbeta,
+                               d, n, act);
+}

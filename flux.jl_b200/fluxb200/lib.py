@@ -57,6 +57,7 @@ PROTOTYPES = {
     "fb_dense_bwd": (_i32, [_p, _p, _i32, _i32, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_layernorm_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i32]),
     "fb_layernorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32]),
+    "fb_layernorm_bwd_noalloc": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32]),
     "fb_batchnorm_fwd_train": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _f, _i32, _i32]),
     "fb_batchnorm_fwd_infer": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _i32]),
     "fb_batchnorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i32]),

@@ -137,6 +137,19 @@ int32_t fb_layernorm_bwd(fb_ctx* ctx, void* stream, const float* x, const float*
                          const float* beta, const float* mean, const float* rstd, const float* dy,
                          float* dx, float* dgamma, float* dbeta, int64_t d, int64_t n, int32_t act);
 
+/* fb_layernorm_bwd for callers that may not allocate device memory (a process whose memory budget is fixed at
+ * start-up, code inside a stream capture, runtime threads that must not risk the implicit synchronisation of
+ * cudaMalloc / cudaFree).  No counterpart in the reference; same arguments and results as fb_layernorm_bwd minus the
+ * context.  The dgamma / dbeta partials live in a fixed 16 MiB device array inside the library image (held by every
+ * GPU that loads the library until the process exits), so: d <= 2 Mi features when dgamma / dbeta are requested
+ * (FB_ERR_UNSUPPORTED otherwise); the call allocates and frees nothing; all calls share the array, so two calls
+ * that overlap on the GPU (different streams) race - serialise them.  The first call on each device also resolves
+ * the array's device address (cudaGetSymbolAddress, with that device current); make that first call before any
+ * stream capture begins.  Uses the current device. */
+int32_t fb_layernorm_bwd_noalloc(void* stream, const float* x, const float* gamma, const float* beta,
+                                 const float* mean, const float* rstd, const float* dy, float* dx,
+                                 float* dgamma, float* dbeta, int64_t d, int64_t n, int32_t act);
+
 /* ---------------------------------------------------------------------------- BatchNorm -- */
 
 /* Training-mode BatchNorm on x viewed as [n][c][s] (s = product of the dims before the channel dim):
