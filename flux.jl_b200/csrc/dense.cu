@@ -35,8 +35,9 @@ int32_t fb_gemm_dispatch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a
     case FB_PREC_FP32_SIMT:
       return fb_gemm_simt_launch(ctx, stream, a);
     case FB_PREC_3XTF32:
+    case FB_PREC_3XTF32_PAIR:
     case FB_PREC_TF32: {
-      const int32_t st = fb_gemm_tc_launch(ctx, stream, a, precision == FB_PREC_3XTF32 ? 3 : 1);
+      const int32_t st = fb_gemm_tc_launch(ctx, stream, a, precision == FB_PREC_TF32 ? 1 : precision == FB_PREC_3XTF32 ? 3 : 32);
       if (st == FB_ERR_UNSUPPORTED)
         return fb_fail(FB_ERR_UNSUPPORTED,
                        "gemm: the tensor-core kernel needs 16-byte aligned pointers, leading dimensions that are "

@@ -1,26 +1,35 @@
 // Tensor-core GEMM for Float32 data on sm_100a: TMA -> shared memory -> tcgen05.mma (TF32, accumulators
 // in tensor memory) -> tcgen05.ld epilogue with fused bias / activation / pre-activation store.
 //
-// fp32 accuracy comes from the error-compensated "3xTF32" scheme: every operand tile is split in shared
-// memory into hi = x with the 13 low mantissa bits cleared (exactly representable in TF32) and
-// lo = x - hi; the accumulator receives A_lo*B_hi + A_hi*B_lo + A_hi*B_hi in fp32.  The dropped
-// lo*lo term is ~2^-22 relative.
+// fp32 accuracy comes from the error-compensated "3xTF32" scheme.  Operand tiles land in shared memory as raw
+// fp32; the tensor core ignores the 13 low mantissa bits of a TF32 operand (measured: clearing them first gives
+// bit-identical results), so the raw tile is the "hi" operand and split warps only write lo = x - trunc_tf32(x)
+// beside it.  The accumulator receives A_lo*B_hi + A_hi*B_lo + A_hi*B_hi; the dropped lo*lo term is ~2^-20.
 //
-// One CTA computes one 128 x BN tile of row-major C[M][N]; K is walked in blocks of 16 floats through a
-// 4-stage ring.  Warp roles: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs,
-// warps 2-5 split the landed tiles into hi / lo and afterwards run the epilogue (one TMEM lane quadrant
-// each).  Operands may be K-major (k contiguous) or MN-major (m / n contiguous) in global memory; the
-// shared-memory layouts are the canonical ones the MMA descriptors name: 64-byte swizzle for K-major tiles
-// (8 rows x 64 B atoms) and, for MN-major tiles, the 128-byte swizzle with 32-byte atoms (128 B x 4 k-rows
-// per atom), which is the only MN-major layout the tensor core accepts for 32-bit operands.
+// Tiles.  One CTA computes a 128 x BN tile of row-major C[M][N] (BN = 256 or 128); or, for large problems, a
+// cluster of two CTAs computes a 256 x 256 tile with cta_group::2 MMAs: each CTA loads and splits 128 rows of A
+// and 128 columns of B, the leader CTA issues one M = 256 MMA per k-step that reads both CTAs' shared memory,
+// and each CTA's tensor memory receives its own 128 rows.  K is walked in blocks of 16 floats through a ring of
+// 4-6 stages.  No TMA load is multicast.
+//
+// Warp roles: warp 0 issues TMA loads; warp 1 owns tensor memory and issues the MMAs; warps 2-5 are the
+// epilogue (one TMEM lane quadrant each); warps 6-13 are two groups of split warps that take alternate
+// k-blocks, so that the proxy fence each split ends with overlaps the next block's split.
+//
+// Operands may be K-major (k contiguous) or MN-major (m / n contiguous) in global memory; the shared-memory
+// layouts are the canonical ones the MMA descriptors name: 64-byte swizzle for K-major tiles (8 rows x 64 B
+// atoms) and, for MN-major tiles, the 128-byte swizzle with 32-byte atoms (128 B x 4 k-rows per atom), which
+// is the only MN-major layout the tensor core accepts for 32-bit operands.
 //
 // The tensor core adds into its fp32 accumulator with truncation, so a long K chain drifts (about 3e-5 of
-// max|C| at K = 4096).  K is therefore cut into segments of 2048: after each segment the epilogue warps drain
-// tensor memory into C with round-to-nearest adds and the next segment starts from a zeroed accumulator.
+// max|C| at K = 4096).  K is therefore cut into segments of 2048 that alternate between two accumulator
+// buffers in tensor memory: while the MMAs fill one, the epilogue warps drain the other into C with
+// round-to-nearest adds.
 //
 // Every mbarrier wait is bounded; when a wait runs out the kernel records a code in the context's
 // device error word, every role leaves its loop, tensor memory is released and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -28,8 +37,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;               // floats per k-block (64 bytes)
-constexpr int STAGES = 4;
-constexpr int NUM_THREADS = 192;     // 6 warps
+constexpr int SPLIT_GROUPS = 2;      // groups of four split warps taking alternate k-blocks
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr int SEG_KB = 128;          // k-blocks per accumulation segment (2048 k-values)
 
@@ -67,6 +75,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+
+// Asks the memory system to bring a tile into L2 (no shared memory, no barrier): used a few k-blocks ahead of the
+// real load so that the load itself hits L2.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x),
+               "r"(y)
+               : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -114,61 +130,151 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 }
 constexpr uint32_t LAYOUT_SW128_32B = 1, LAYOUT_SW64 = 4;   // MN-major 32-bit operands only exist in the 32-byte-atom 128B swizzle
 
-template <int BN, int PASSES>
+// lo = x - (x with the 13 low mantissa bits cleared): what the tensor core drops when it reads x as TF32
+__device__ __forceinline__ float tf32_lo(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* s_abort) {
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 255u) == 255u && *s_abort != 0) return false;
+  }
+  *s_abort = 1;
+  return false;
+}
+__device__ __forceinline__ void tc_commit2_mc(uint32_t bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma2_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+      "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+
+
+template <int BN, int PASSES, bool PAIR>
 struct Cfg {
-  static constexpr int A_BYTES = BM * BK * 4;   // 8 KB
-  static constexpr int B_BYTES = BN * BK * 4;   // 16 KB at BN = 256
+  static_assert(!PAIR || PASSES == 3, "the two-CTA tile exists for the 3-pass scheme only");
+  static constexpr int BNC = PAIR ? BN / 2 : BN;            // B columns this CTA loads per stage
+  static constexpr int A_BYTES = BM * BK * 4;               // 8 KB
+  static constexpr int B_BYTES = BNC * BK * 4;              // 16 KB at 256 columns
   static constexpr int STAGE_BYTES = (PASSES == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
+  static constexpr int STAGES = (229376 / STAGE_BYTES) > 8 ? 8 : (229376 / STAGE_BYTES);   // 224 KB of stages at most
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+  static constexpr int SMEM_BYTES = BAR_OFFSET + 512 + 1024;   // barriers + alignment slack
+  static constexpr int TMEM_COLS = 2 * BN;                  // two accumulator buffers
+  static constexpr int NUM_WARPS = 6 + (PASSES == 3 ? 4 * SPLIT_GROUPS : 0);
+  static constexpr int NUM_THREADS = 32 * NUM_WARPS;
+  static constexpr uint32_t ARRIVALS = PAIR ? 8 : 4;        // four warps per CTA arrive on ready / tmem_empty
 };
 
-template <bool A_MN, bool B_MN, int BN, int PASSES>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR>
+__global__ void __launch_bounds__(Cfg<BN, PASSES, PAIR>::NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                float* __restrict__ C, int64_t ldc, float* __restrict__ Z, const float* __restrict__ bias_n, int M,
-               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err) {
-  using cfg = Cfg<BN, PASSES>;
+               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int prefetch_kb) {
+  using cfg = Cfg<BN, PASSES, PAIR>;
+  constexpr int STAGES = cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
   uint64_t* bars = (uint64_t*)(smem + cfg::BAR_OFFSET);
   const uint32_t bar_base = smem_base + cfg::BAR_OFFSET;
-  // barrier slots: full[0..S), ready[S..2S), empty[2S..3S), tmem_full[3S], tmem_empty[3S+1]
+  // barrier slots: full[S], ready[S], empty[S], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
   auto ready_bar = [&](int s) { return bar_base + 8u * (uint32_t)(STAGES + s); };
   auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * STAGES + s); };
-  const uint32_t tmem_full_bar = bar_base + 8u * (uint32_t)(3 * STAGES);
-  const uint32_t tmem_empty_bar = bar_base + 8u * (uint32_t)(3 * STAGES + 1);
-  volatile uint32_t* s_tmem = (volatile uint32_t*)(bars + 3 * STAGES + 2);
-  volatile int* s_abort = (volatile int*)(bars + 3 * STAGES + 3);
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * STAGES + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * STAGES + 2 + b); };
+  volatile uint32_t* s_tmem = (volatile uint32_t*)(bars + 3 * STAGES + 4);
+  volatile int* s_abort = (volatile int*)(bars + 3 * STAGES + 5);
+  volatile int* s_skip = (volatile int*)(bars + 3 * STAGES + 6);   // [0] mine, [1] written by the peer CTA
 
-  // a wait that ran out earlier (in this or a previous launch) leaves the error word set: do not start
-  __shared__ int s_skip;
-  if (threadIdx.x == 0) s_skip = (*(volatile int32_t*)dev_err != 0) ? 1 : 0;
-  __syncthreads();
-  if (s_skip) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = (rank == 0);
+  // rows of A / C this CTA owns, columns of the tile, and the B columns this CTA loads
+  const int m0 = PAIR ? (int)(blockIdx.x >> 1) * 256 + 128 * (int)rank : (int)blockIdx.y * BM;
+  const int n0 = PAIR ? (int)blockIdx.y * BN : (int)blockIdx.x * BN;
+  const int nb0 = PAIR ? n0 + cfg::BNC * (int)rank : n0;
   const int num_kb = (K + BK - 1) / BK;
+  const int num_seg = (num_kb + SEG_KB - 1) / SEG_KB;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(ready_bar(s), 4);
+      mbar_init(ready_bar(s), cfg::ARRIVALS);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(tmem_full_bar, 1);
-    mbar_init(tmem_empty_bar, 4);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), cfg::ARRIVALS);
+    }
     *s_abort = 0;
+    // an error word left set by an earlier launch means: do not start
+    s_skip[0] = (*(volatile int32_t*)dev_err != 0) ? 1 : 0;
+    s_skip[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
+  if (PAIR) {
+    __syncwarp();
+    cluster_sync_all();   // both CTAs run and their barriers exist: remote accesses may start
+    if (threadIdx.x == 0) {
+      // both CTAs of a pair must take the same decision
+      asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(smem_u32((const void*)(s_skip + 1)), rank ^ 1u)),
+                   "r"((int)s_skip[0])
+                   : "memory");
+    }
+    __syncwarp();
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
+  if (s_skip[0] != 0 || s_skip[1] != 0) return;   // uniform over the CTA (pair)
+
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)),
-                 "r"((uint32_t)BN)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)),
+                   "r"((uint32_t)cfg::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)),
+                   "r"((uint32_t)cfg::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -178,10 +284,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer ---
     if (lane == 0) {
+      auto prefetch = [&](int kbp) {
+        const int kp = kbp * BK;
+        if (A_MN) {
+#pragma unroll
+          for (int c = 0; c < BM / 32; ++c) tma_prefetch_2d(&tmA, m0 + 32 * c, kp);
+        } else {
+          tma_prefetch_2d(&tmA, kp, m0);
+        }
+        if (B_MN) {
+#pragma unroll
+          for (int c = 0; c < cfg::BNC / 32; ++c) tma_prefetch_2d(&tmB, nb0 + 32 * c, kp);
+        } else {
+          tma_prefetch_2d(&tmB, kp, nb0);
+        }
+      };
+      for (int kb = 0; kb < prefetch_kb && kb < num_kb; ++kb) prefetch(kb);
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, s_abort)) break;
+        if (prefetch_kb > 0 && kb + prefetch_kb < num_kb) prefetch(kb + prefetch_kb);
+        if (!mbar_wait_cluster(empty_bar(s), ph ^ 1u, s_abort)) break;
         mbar_arrive_expect_tx(full_bar(s), (uint32_t)(cfg::A_BYTES + cfg::B_BYTES));
         const uint32_t a_dst = smem_base + (uint32_t)(s * cfg::STAGE_BYTES);
         const uint32_t b_dst = a_dst + (uint32_t)((PASSES == 3 ? 2 : 1) * cfg::A_BYTES);
@@ -194,31 +317,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (B_MN) {
 #pragma unroll
-          for (int c = 0; c < BN / 32; ++c) tma_load_2d(b_dst + (uint32_t)(c * BK * 128), &tmB, n0 + 32 * c, k0, full_bar(s));
+          for (int c = 0; c < cfg::BNC / 32; ++c) tma_load_2d(b_dst + (uint32_t)(c * BK * 128), &tmB, nb0 + 32 * c, k0, full_bar(s));
         } else {
-          tma_load_2d(b_dst, &tmB, k0, n0, full_bar(s));
+          tma_load_2d(b_dst, &tmB, k0, nb0, full_bar(s));
         }
       }
     }
   } else if (warp == 1) {
-    // -------------------------------------------------------------------- MMA issuer ---
-    if (lane == 0) {
-      // instruction descriptor: D = F32, A = B = TF32, majors, N >> 3, M >> 4
+    // -------------------------------------------------- MMA issuer (the leader CTA of a pair) ---
+    if (lane == 0 && leader) {
+      // instruction descriptor: D = F32, A = B = TF32, operand majors, N >> 3, M >> 4
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((PAIR ? 256 : BM) >> 4) << 24);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
         const int seg = kb / SEG_KB, kb_in_seg = kb % SEG_KB;
-        if (kb_in_seg == 0 && seg > 0) {
-          // the epilogue warps must have drained the previous segment out of tensor memory
-          ok = mbar_wait(tmem_empty_bar, (uint32_t)(seg - 1) & 1u, s_abort);
+        const int buf = seg & 1, use = seg >> 1;
+        if (kb_in_seg == 0 && use > 0) {
+          // the epilogue warps must have drained this accumulator buffer's previous segment
+          ok = mbar_wait_cluster(tmem_empty_bar(buf), (uint32_t)(use - 1) & 1u, s_abort);
           if (!ok) break;
         }
-        ok = mbar_wait(PASSES == 3 ? ready_bar(s) : full_bar(s), ph, s_abort);
+        ok = mbar_wait_cluster(PASSES == 3 ? ready_bar(s) : full_bar(s), ph, s_abort);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         const uint32_t a_hi = smem_base + (uint32_t)(s * cfg::STAGE_BYTES);
         const uint32_t a_lo = a_hi + (uint32_t)cfg::A_BYTES;
         const uint32_t b_hi = a_hi + (uint32_t)((PASSES == 3 ? 2 : 1) * cfg::A_BYTES);
@@ -238,32 +363,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                         : make_smem_desc(a_lo + a_off, 16, 512, LAYOUT_SW64);
             const uint64_t db_lo = B_MN ? make_smem_desc(b_lo + b_off, BK * 128, 512, LAYOUT_SW128_32B)
                                         : make_smem_desc(b_lo + b_off, 16, 512, LAYOUT_SW64);
-            tc_mma_tf32(tmem_base, da_lo, db_hi, idesc, first);
-            tc_mma_tf32(tmem_base, da_hi, db_lo, idesc, 1u);
-            tc_mma_tf32(tmem_base, da_hi, db_hi, idesc, 1u);
+            if (PAIR) {
+              tc_mma2_tf32(d_tmem, da_lo, db_hi, idesc, first);
+              tc_mma2_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+              tc_mma2_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            } else {
+              tc_mma_tf32(d_tmem, da_lo, db_hi, idesc, first);
+              tc_mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+              tc_mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            }
           } else {
-            tc_mma_tf32(tmem_base, da_hi, db_hi, idesc, first);
+            tc_mma_tf32(d_tmem, da_hi, db_hi, idesc, first);
           }
         }
-        tc_commit(empty_bar(s));   // frees the stage once these MMAs have read it
-        if (kb_in_seg == SEG_KB - 1 || kb == num_kb - 1) tc_commit(tmem_full_bar);   // segment complete
+        const bool seg_end = (kb_in_seg == SEG_KB - 1 || kb == num_kb - 1);
+        if (PAIR) {
+          tc_commit2_mc(empty_bar(s), (uint16_t)3);                 // frees the stage in both CTAs
+          if (seg_end) tc_commit2_mc(tmem_full_bar(buf), (uint16_t)3);
+        } else {
+          tc_commit(empty_bar(s));
+          if (seg_end) tc_commit(tmem_full_bar(buf));
+        }
       }
     }
-  } else {
-    // ------------------------------------- hi / lo split, and the epilogue per K segment ---
-    const int tt = threadIdx.x - 64;  // 0..127
-    const int q = warp & 3;           // TMEM lane quadrant this warp may read
+  } else if (warp < 6) {
+    // -------------------------------------------------------------- epilogue warps ---
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
     const int row = m0 + 32 * q + lane;
     float* crow = C + (int64_t)row * ldc;
     float* zrow = Z ? Z + (int64_t)row * ldc : nullptr;
-    const int num_seg = (num_kb + SEG_KB - 1) / SEG_KB;
     bool ok = true;
-
-    // Drains the accumulator of segment `seg`: intermediate segments add into C (round-to-nearest fp32 adds),
-    // the last one also applies bias, pre-activation store and activation.
-    auto drain = [&](int seg) -> bool {
-      if (!mbar_wait(tmem_full_bar, (uint32_t)seg & 1u, s_abort)) return false;
+    for (int seg = 0; seg < num_seg && ok; ++seg) {
+      const int buf = seg & 1, use = seg >> 1;
+      ok = mbar_wait_cluster(tmem_full_bar(buf), (uint32_t)use & 1u, s_abort);
+      if (!ok) break;
       tc_fence_after();
+      // intermediate segments add into C (round-to-nearest fp32 adds); the last one also applies bias,
+      // pre-activation store and activation
       const bool last = (seg == num_seg - 1);
       const bool add_c = (seg > 0) || (accumulate != 0);
 #pragma unroll 1
@@ -271,7 +407,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int nb = n0 + cc * 32;
         if (nb >= N) break;   // warp-uniform
         uint32_t r[32];
-        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(cc * 32), r);
+        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * BN + cc * 32), r);
         tc_wait_ld();
         if (row < M) {
 #pragma unroll
@@ -312,64 +448,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
       if (!last) {
-        // tensor memory may be overwritten by the next segment once every warp has read its quadrant
+        // this buffer may be overwritten once every epilogue warp (of both CTAs) has read its quadrant
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tmem_empty_bar);
-      }
-      return true;
-    };
-
-    if (PASSES == 3) {
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        ok = mbar_wait(full_bar(s), ph, s_abort);
-        if (!ok) break;
-        float4* a_hi = (float4*)(smem + s * cfg::STAGE_BYTES);
-        float4* a_lo = (float4*)(smem + s * cfg::STAGE_BYTES + cfg::A_BYTES);
-        float4* b_hi = (float4*)(smem + s * cfg::STAGE_BYTES + 2 * cfg::A_BYTES);
-        float4* b_lo = (float4*)(smem + s * cfg::STAGE_BYTES + 2 * cfg::A_BYTES + cfg::B_BYTES);
-#pragma unroll
-        for (int i = 0; i < cfg::A_BYTES / 16 / 128; ++i) {
-          const float4 v = a_hi[tt + i * 128];
-          float4 h, l;
-          h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
-          h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
-          h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
-          h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
-          a_hi[tt + i * 128] = h;
-          a_lo[tt + i * 128] = l;
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0u));
+          else mbar_arrive(tmem_empty_bar(buf));
         }
-#pragma unroll
-        for (int i = 0; i < cfg::B_BYTES / 16 / 128; ++i) {
-          const float4 v = b_hi[tt + i * 128];
-          float4 h, l;
-          h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
-          h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
-          h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
-          h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
-          b_hi[tt + i * 128] = h;
-          b_lo[tt + i * 128] = l;
-        }
-        fence_proxy_async();   // generic-proxy writes become visible to the tensor core's async-proxy reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(ready_bar(s));
-        if (kb % SEG_KB == SEG_KB - 1 || kb == num_kb - 1) ok = drain(kb / SEG_KB);
       }
-    } else {
-      for (int seg = 0; seg < num_seg && ok; ++seg) ok = drain(seg);
+    }
+  } else {
+    // ------------------------------------------- split warps: write lo = x - trunc_tf32(x) ---
+    const int group = (warp - 6) >> 2;
+    const int tt = ((warp - 6) & 3) * 32 + lane;   // 0..127 inside the group
+    bool ok = true;
+    for (int kb = group; kb < num_kb && ok; kb += SPLIT_GROUPS) {
+      const int s = kb % STAGES;
+      const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+      ok = mbar_wait(full_bar(s), ph, s_abort);
+      if (!ok) break;
+      const float4* a_hi = (const float4*)(smem + s * cfg::STAGE_BYTES);
+      float4* a_lo = (float4*)(smem + s * cfg::STAGE_BYTES + cfg::A_BYTES);
+      const float4* b_hi = (const float4*)(smem + s * cfg::STAGE_BYTES + 2 * cfg::A_BYTES);
+      float4* b_lo = (float4*)(smem + s * cfg::STAGE_BYTES + 2 * cfg::A_BYTES + cfg::B_BYTES);
+      constexpr int NA = cfg::A_BYTES / 16 / 128, NB = cfg::B_BYTES / 16 / 128;
+      float4 v[NA + NB];
+#pragma unroll
+      for (int i = 0; i < NA; ++i) v[i] = a_hi[tt + i * 128];
+#pragma unroll
+      for (int i = 0; i < NB; ++i) v[NA + i] = b_hi[tt + i * 128];
+#pragma unroll
+      for (int i = 0; i < NA + NB; ++i) {
+        v[i].x = tf32_lo(v[i].x); v[i].y = tf32_lo(v[i].y); v[i].z = tf32_lo(v[i].z); v[i].w = tf32_lo(v[i].w);
+      }
+#pragma unroll
+      for (int i = 0; i < NA; ++i) a_lo[tt + i * 128] = v[i];
+#pragma unroll
+      for (int i = 0; i < NB; ++i) b_lo[tt + i * 128] = v[NA + i];
+      fence_proxy_async();   // generic-proxy writes become visible to the tensor core's async-proxy reads
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(map_to_cta(ready_bar(s), 0u));
+        else mbar_arrive(ready_bar(s));
+      }
     }
   }
 
   // ---------------------------------------------------------------------- teardown ---
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA may release tensor memory while its peer can still touch it
   if (warp == 1) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)cfg::TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)cfg::TMEM_COLS) : "memory");
   }
-  if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 1001);
+  if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, PAIR ? 1002 : 1001);
 }
 
 // --------------------------------------------------------------------------- host side ---
@@ -408,40 +544,73 @@ bool encode_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols,
   return r == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, int BN, int PASSES>
+
+// FLUXB200_PREFETCH = n: the producer prefetches tiles into L2 n k-blocks ahead of its loads (0 = off, default).
+int prefetch_from_env() {
+  static int n = -1;
+  if (n < 0) {
+    const char* e = getenv("FLUXB200_PREFETCH");
+    n = e ? atoi(e) : 0;
+    if (n < 0 || n > 64) n = 0;
+  }
+  return n;
+}
+
+template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR>
 int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
-  using cfg = Cfg<BN, PASSES>;
+  using cfg = Cfg<BN, PASSES, PAIR>;
   CUtensorMap tmA, tmB;
   bool ok;
   if (A_MN) ok = encode_map(&tmA, a.A, a.K, a.M, a.lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   else ok = encode_map(&tmA, a.A, a.M, a.K, a.lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_64B);
   if (ok) {
     if (B_MN) ok = encode_map(&tmB, a.B, a.K, a.N, a.ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    else ok = encode_map(&tmB, a.B, a.N, a.K, a.ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_64B);
+    else ok = encode_map(&tmB, a.B, a.N, a.K, a.ldb, BK, cfg::BNC, CU_TENSOR_MAP_SWIZZLE_64B);
   }
   if (!ok) return fb_fail(FB_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed (M=%lld N=%lld K=%lld lda=%lld ldb=%lld)",
                           (long long)a.M, (long long)a.N, (long long)a.K, (long long)a.lda, (long long)a.ldb);
-  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, PASSES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
-    attr_set = true;
-  }
-  dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)((a.M + BM - 1) / BM));
-  kern<<<grid, NUM_THREADS, cfg::SMEM_BYTES, stream>>>(tmA, tmB, a.C, a.ldc, a.Z, a.bias_n, (int)a.M, (int)a.N, (int)a.K,
-                                                       a.act, a.accumulate, ctx->dev_error);
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, PASSES, PAIR>;
+  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  if (PAIR) lc.gridDim = dim3((unsigned)(2 * ((a.M + 255) / 256)), (unsigned)((a.N + BN - 1) / BN), 1);
+  else lc.gridDim = dim3((unsigned)((a.N + BN - 1) / BN), (unsigned)((a.M + BM - 1) / BM), 1);
+  lc.blockDim = dim3(cfg::NUM_THREADS, 1, 1);
+  lc.dynamicSmemBytes = cfg::SMEM_BYTES;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  FB_CUDA(cudaLaunchKernelEx(&lc, kern, tmA, tmB, a.C, a.ldc, a.Z, a.bias_n, (int)a.M, (int)a.N, (int)a.K, a.act,
+                             a.accumulate, ctx->dev_error, prefetch_from_env()));
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
 
-template <int BN, int PASSES>
+template <int BN, int PASSES, bool PAIR>
 int32_t launch_layout(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
   if (a.a_mn_major) {
-    if (a.b_mn_major) return launch_variant<true, true, BN, PASSES>(ctx, stream, a);
-    return launch_variant<true, false, BN, PASSES>(ctx, stream, a);
+    if (a.b_mn_major) return launch_variant<true, true, BN, PASSES, PAIR>(ctx, stream, a);
+    return launch_variant<true, false, BN, PASSES, PAIR>(ctx, stream, a);
   }
-  if (a.b_mn_major) return launch_variant<false, true, BN, PASSES>(ctx, stream, a);
-  return launch_variant<false, false, BN, PASSES>(ctx, stream, a);
+  if (a.b_mn_major) return launch_variant<false, true, BN, PASSES, PAIR>(ctx, stream, a);
+  return launch_variant<false, false, BN, PASSES, PAIR>(ctx, stream, a);
+}
+
+// FLUXB200_PAIR = 1 selects the two-CTA 256 x 256 tiles for large problems.  Measured on B200 the one-CTA tile is
+// the faster of the two (it is bound by shared-memory bandwidth at ~56 % tensor-pipe activity, the pair by the
+// latency of its cross-CTA barrier chain at ~50 %), so the pair is opt-in.
+bool pair_kernel_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUXB200_PAIR");
+    on = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return on != 0;
 }
 
 }  // namespace
@@ -460,16 +629,23 @@ bool fb_gemm_tc_supported(const fb_gemm_args& a) {
   return true;
 }
 
+// passes: 3 = 3xTF32, 1 = one TF32 pass, 32 = 3xTF32 on two-CTA tiles where the shape allows
 int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a, int passes) {
   if (!fb_gemm_tc_supported(a)) return FB_ERR_UNSUPPORTED;
+  const bool passes_flag_pair = (passes == 32);
+  if (passes_flag_pair) passes = 3;
   const int64_t tiles256 = ((a.M + BM - 1) / BM) * ((a.N + 255) / 256);
   const bool narrow = (a.N <= 128) || (tiles256 < ctx->sm_count);
   if (passes == 3) {
-    if (narrow) return launch_layout<128, 3>(ctx, stream, a);
-    return launch_layout<256, 3>(ctx, stream, a);
+    // two-CTA 256 x 256 tiles when the problem fills the machine with them
+    if ((passes_flag_pair || pair_kernel_enabled()) && a.M >= 256 && a.N >= 256 && (a.N + 255) / 256 <= 65535 &&
+        (passes_flag_pair || 2 * ((a.M + 255) / 256) * ((a.N + 255) / 256) >= ctx->sm_count))
+      return launch_layout<256, 3, true>(ctx, stream, a);
+    if (narrow) return launch_layout<128, 3, false>(ctx, stream, a);
+    return launch_layout<256, 3, false>(ctx, stream, a);
   }
-  if (narrow) return launch_layout<128, 1>(ctx, stream, a);
-  return launch_layout<256, 1>(ctx, stream, a);
+  if (narrow) return launch_layout<128, 1, false>(ctx, stream, a);
+  return launch_layout<256, 1, false>(ctx, stream, a);
 }
 
 void fb_tmap_cache_destroy(fb_ctx* ctx) { (void)ctx; }

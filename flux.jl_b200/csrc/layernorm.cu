@@ -182,6 +182,131 @@ ln_bwd_vec_kernel(const float4* __restrict__ x, const float4* __restrict__ gamma
   }
 }
 
+// ------------------------------------------- backward, rows staged through shared memory ---
+// Same arithmetic as ln_bwd_vec_kernel, but the x and dy rows of the next LN_PIPE - 1 iterations are already in
+// flight (cp.async.bulk into a ring of shared-memory stages) while the current row is reduced, so the kernel does
+// not depend on occupancy for memory-level parallelism.
+constexpr int LN_PIPE_MAX = 3;
+constexpr uint32_t LN_WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t ln_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <int V>
+__global__ void __launch_bounds__(LN_THREADS, 2)
+ln_bwd_pipe_kernel(const float* __restrict__ x, const float4* __restrict__ gamma, const float4* __restrict__ beta,
+                   const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ dy,
+                   float4* __restrict__ dx, float4* __restrict__ part_dg, float4* __restrict__ part_db, int d4,
+                   int64_t n, int act, int nstages, int32_t* __restrict__ dev_err) {
+  extern __shared__ __align__(128) uint8_t ln_smem[];
+  __shared__ float sh[64];
+  __shared__ __align__(8) uint64_t bar[LN_PIPE_MAX];
+  __shared__ int s_fail;
+  const uint32_t row_bytes = (uint32_t)d4 * 16u;
+  float4* stage_base = (float4*)ln_smem;                 // stage s: x row at [s][0], dy row at [s][1]
+  const float inv_d = 1.0f / (4.0f * (float)d4);
+  const int64_t first = blockIdx.x, step = gridDim.x;
+  const int64_t my_rows = first < n ? (n - first + step - 1) / step : 0;
+
+  auto issue = [&](int64_t i) {   // one thread: bring row first + i*step into stage i % nstages
+    const int s = (int)(i % nstages);
+    const int64_t row = first + i * step;
+    const uint32_t b = ln_smem_u32(&bar[s]);
+    const uint32_t dst_x = ln_smem_u32(stage_base + (size_t)(2 * s) * d4);
+    const uint32_t dst_d = ln_smem_u32(stage_base + (size_t)(2 * s + 1) * d4);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(2u * row_bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_x), "l"(x + row * (int64_t)d4 * 4), "r"(row_bytes), "r"(b) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_d), "l"(dy + row * (int64_t)d4 * 4), "r"(row_bytes), "r"(b) : "memory");
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nstages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ln_smem_u32(&bar[s])) : "memory");
+    s_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int64_t i = 0; i < nstages && i < my_rows; ++i) issue(i);
+  }
+  __syncthreads();
+
+  float4 ag[V], ab[V], gam[V], bet[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c = threadIdx.x + i * LN_THREADS;
+    ag[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    gam[i] = (gamma != nullptr && c < d4) ? __ldg(gamma + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+    bet[i] = (beta != nullptr && c < d4) ? __ldg(beta + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int64_t it = 0; it < my_rows; ++it) {
+    const int s = (int)(it % nstages);
+    const uint32_t parity = (uint32_t)(it / nstages) & 1u;
+    const int64_t row = first + it * step;
+    {
+      // bounded wait for this stage's two bulk copies
+      const uint32_t b = ln_smem_u32(&bar[s]);
+      uint32_t ok = 0;
+      for (uint32_t spin = 0; spin < LN_WAIT_LIMIT && !ok; ++spin)
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b), "r"(parity) : "memory");
+      if (!ok) s_fail = 1;
+    }
+    const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
+    const float4* xr = stage_base + (size_t)(2 * s) * d4;
+    const float4* dyr = stage_base + (size_t)(2 * s + 1) * d4;
+    float4 xh[V], g[V];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int c = threadIdx.x + i * LN_THREADS;
+      if (c < d4) {
+        const float4 xv = xr[c];
+        float4 dz = dyr[c];
+        xh[i].x = (xv.x - mu) * rs; xh[i].y = (xv.y - mu) * rs; xh[i].z = (xv.z - mu) * rs; xh[i].w = (xv.w - mu) * rs;
+        if (act != FB_ACT_IDENTITY) {
+          dz.x *= fb_act_grad_z(act, fmaf(xh[i].x, gam[i].x, bet[i].x));
+          dz.y *= fb_act_grad_z(act, fmaf(xh[i].y, gam[i].y, bet[i].y));
+          dz.z *= fb_act_grad_z(act, fmaf(xh[i].z, gam[i].z, bet[i].z));
+          dz.w *= fb_act_grad_z(act, fmaf(xh[i].w, gam[i].w, bet[i].w));
+        }
+        ag[i].x = fmaf(dz.x, xh[i].x, ag[i].x); ag[i].y = fmaf(dz.y, xh[i].y, ag[i].y);
+        ag[i].z = fmaf(dz.z, xh[i].z, ag[i].z); ag[i].w = fmaf(dz.w, xh[i].w, ag[i].w);
+        ab[i].x += dz.x; ab[i].y += dz.y; ab[i].z += dz.z; ab[i].w += dz.w;
+        g[i].x = dz.x * gam[i].x; g[i].y = dz.y * gam[i].y; g[i].z = dz.z * gam[i].z; g[i].w = dz.w * gam[i].w;
+        s1 += (g[i].x + g[i].y) + (g[i].z + g[i].w);
+        s2 += (g[i].x * xh[i].x + g[i].y * xh[i].y) + (g[i].z * xh[i].z + g[i].w * xh[i].w);
+      }
+    }
+    block_sum2(s1, s2, sh);   // its barriers also mean: every thread has finished reading stage s
+    if (s_fail) break;        // block-uniform after the barriers above
+    if (threadIdx.x == 0 && it + nstages < my_rows) issue(it + nstages);
+    const float m1 = s1 * inv_d, m2 = s2 * inv_d;
+    float4* dxr = dx + row * d4;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int c = threadIdx.x + i * LN_THREADS;
+      if (c < d4) {
+        float4 o;
+        o.x = rs * (g[i].x - m1 - xh[i].x * m2); o.y = rs * (g[i].y - m1 - xh[i].y * m2);
+        o.z = rs * (g[i].z - m1 - xh[i].z * m2); o.w = rs * (g[i].w - m1 - xh[i].w * m2);
+        st_stream(dxr + c, o);
+      }
+    }
+  }
+  if (part_dg != nullptr) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int c = threadIdx.x + i * LN_THREADS;
+      if (c < d4) {
+        part_dg[(int64_t)blockIdx.x * d4 + c] = ag[i];
+        part_db[(int64_t)blockIdx.x * d4 + c] = ab[i];
+      }
+    }
+  }
+  if (threadIdx.x == 0 && s_fail && dev_err != nullptr) atomicExch(dev_err, 2001);
+}
+
 // ---------------------------------------------------------------- backward, any d / alignment ---
 __global__ void __launch_bounds__(LN_THREADS)
 ln_bwd_generic_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
@@ -290,7 +415,7 @@ FB_API int32_t fb_layernorm_fwd(fb_ctx* ctx, void* stream_, const float* x, cons
 int32_t fb_layernorm_bwd_impl(cudaStream_t stream, int sm_count, float* part, int64_t groups, const float* x,
                               const float* gamma, const float* beta, const float* mean, const float* rstd,
                               const float* dy, float* dx, float* dgamma, float* dbeta, int64_t d, int64_t n,
-                              int32_t act) {
+                              int32_t act, int32_t* dev_err) {
   (void)sm_count;
   const bool want_param = (dgamma != nullptr);
   float* part_dg = want_param ? part : nullptr;
@@ -306,11 +431,33 @@ int32_t fb_layernorm_bwd_impl(cudaStream_t stream, int sm_count, float* part, in
     float4 *dx4 = (float4*)dx, *pg4 = (float4*)part_dg, *pb4 = (float4*)part_db;
     const int d4 = (int)(d / 4);
     const unsigned g = (unsigned)groups;
-    switch (v) {
-      case 1: ln_bwd_vec_kernel<1><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
-      case 2: ln_bwd_vec_kernel<2><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
-      case 4: ln_bwd_vec_kernel<4><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
-      default: ln_bwd_vec_kernel<8><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
+    // rows staged through shared memory when at least two stages of (x row, dy row) fit beside a second block
+    const size_t stage_bytes = (size_t)2 * d * sizeof(float);
+    int nst = (int)((size_t)100 * 1024 / stage_bytes);
+    if (nst > LN_PIPE_MAX) nst = LN_PIPE_MAX;
+    if (nst >= 2 && v >= 2) {
+      const size_t smem = (size_t)nst * stage_bytes;
+      switch (v) {
+        case 2:
+          FB_CUDA(cudaFuncSetAttribute(ln_bwd_pipe_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+          ln_bwd_pipe_kernel<2><<<g, LN_THREADS, smem, stream>>>(x, g4, b4, mean, rstd, dy, dx4, pg4, pb4, d4, n, act, nst, dev_err);
+          break;
+        case 4:
+          FB_CUDA(cudaFuncSetAttribute(ln_bwd_pipe_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+          ln_bwd_pipe_kernel<4><<<g, LN_THREADS, smem, stream>>>(x, g4, b4, mean, rstd, dy, dx4, pg4, pb4, d4, n, act, nst, dev_err);
+          break;
+        default:
+          FB_CUDA(cudaFuncSetAttribute(ln_bwd_pipe_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+          ln_bwd_pipe_kernel<8><<<g, LN_THREADS, smem, stream>>>(x, g4, b4, mean, rstd, dy, dx4, pg4, pb4, d4, n, act, nst, dev_err);
+          break;
+      }
+    } else {
+      switch (v) {
+        case 1: ln_bwd_vec_kernel<1><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
+        case 2: ln_bwd_vec_kernel<2><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
+        case 4: ln_bwd_vec_kernel<4><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
+        default: ln_bwd_vec_kernel<8><<<g, LN_THREADS, 0, stream>>>(x4, g4, b4, mean, rstd, dy4, dx4, pg4, pb4, d4, n, act); break;
+      }
     }
   }
   FB_LAUNCH_CHECK();
@@ -352,7 +499,7 @@ FB_API int32_t fb_layernorm_bwd(fb_ctx* ctx, void* stream_, const float* x, cons
     if (!part) return FB_ERR_ALLOC;
   }
   return fb_layernorm_bwd_impl(stream, ctx->sm_count, part, groups, x, gamma, beta, mean, rstd, dy, dx, dgamma, dbeta,
-                               d, n, act);
+                               d, n, act, ctx->dev_error);
 }
 
 // ------------------------------------------------------------- LayerNorm backward without allocation ---
@@ -427,5 +574,5 @@ FB_API int32_t fb_layernorm_bwd_noalloc(void* stream_, const float* x, const flo
   // Every block overwrites all d columns of its own partial rows before the reduction reads exactly
   // groups * d of them, so nothing left behind by an earlier call is ever read.
   return fb_layernorm_bwd_impl(stream, sd.sm_count, sd.scratch, groups, x, gamma, beta, mean, rstd, dy, dx, dgamma, dbeta,
-                               d, n, act);
+                               d, n, act, nullptr);
 }

@@ -17,7 +17,7 @@ ERR_NAMES = {-1: "FB_ERR_INVALID_ARG", -2: "FB_ERR_SHAPE", -3: "FB_ERR_ALLOC", -
              -5: "FB_ERR_NCCL", -6: "FB_ERR_TIMEOUT", -7: "FB_ERR_UNSUPPORTED"}
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "sigmoid": 3, "gelu_tanh": 4, "gelu": 4, "gelu_erf": 5}
-PREC = {"default": 0, "fp32_simt": 1, "3xtf32": 2, "tf32": 3}
+PREC = {"default": 0, "fp32_simt": 1, "3xtf32": 2, "tf32": 3, "3xtf32_pair": 4}
 OP = {"+": 0, "sum": 0, "avg": 1}
 UNIQUE_ID_BYTES = 128
 

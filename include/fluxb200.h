@@ -53,6 +53,7 @@ extern "C" {
 #define FB_PREC_FP32_SIMT 1 /* always the fp32 FMA kernel */
 #define FB_PREC_3XTF32 2  /* tcgen05 tensor cores, error-compensated TF32 (fp32-level accuracy) */
 #define FB_PREC_TF32 3    /* tcgen05 tensor cores, single TF32 pass */
+#define FB_PREC_3XTF32_PAIR 4 /* 3xTF32 on 256 x 256 tiles computed by CTA pairs (cta_group::2) where M, N >= 256 */
 
 /* reduction op for collectives (DistributedUtils.avg is FB_OP_AVG) */
 #define FB_OP_SUM 0

@@ -12,7 +12,7 @@ from util import P, close, dempty, dev, host, stream
 pytestmark = pytest.mark.gpu
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "sigmoid": 3, "gelu_tanh": 4, "gelu_erf": 5}
-PREC = {"default": 0, "simt": 1, "3xtf32": 2, "tf32": 3}
+PREC = {"default": 0, "simt": 1, "3xtf32": 2, "tf32": 3, "pair": 4}
 
 
 @pytest.fixture(scope="module")
@@ -64,6 +64,22 @@ def test_gemm_all_layouts(fb, prec, ta, tb, m, n, k):
     # accumulate: C += op(A) op(B)
     fb.call("fb_gemm_f32", ta, tb, m, n, k, P(dA), A.shape[0], P(dB), B.shape[0], P(dC), m, 1, PREC[prec])
     close(host(dC, (m, n)), 2 * ref, name="gemm accumulate")
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(512, 768, 300), (260, 1000, 2100), (1024, 256, 4100)])
+def test_gemm_cta_pair_tiles(fb, ta, tb, m, n, k):
+    """The cta_group::2 variant (256 x 256 tiles computed by two CTAs) in all four operand layouts, with ragged
+    edges and more than one accumulation segment."""
+    rng = np.random.default_rng(m + n + k + ta * 2 + tb)
+    A = rng.normal(size=(k, m) if ta else (m, k)).astype(np.float32)
+    B = rng.normal(size=(n, k) if tb else (k, n)).astype(np.float32)
+    dA, dB, dC = dev(A), dev(B), dempty(m, n)
+    fb.call("fb_gemm_f32", ta, tb, m, n, k, P(dA), A.shape[0], P(dB), B.shape[0], P(dC), m, 0, PREC["pair"])
+    ref = (A.T if ta else A).astype(np.float64) @ (B.T if tb else B).astype(np.float64)
+    close(host(dC, (m, n)), ref, name=f"pair gemm ta={ta} tb={tb}")
+    fb.call("fb_gemm_f32", ta, tb, m, n, k, P(dA), A.shape[0], P(dB), B.shape[0], P(dC), m, 1, PREC["pair"])
+    close(host(dC, (m, n)), 2 * ref, name="pair gemm accumulate")
 
 
 def test_gemm_3xtf32_is_fp32_accurate_and_tf32_is_not(fb):
