@@ -50,19 +50,34 @@ bn_stats_kernel(const float* __restrict__ x, float* __restrict__ part /* [c][spl
   const int split = gridDim.y, p = blockIdx.y;
   const float shift = __ldg(x + ch * s);  // a value inside the channel's range
   float cnt = 0.0f, s1 = 0.0f, s2 = 0.0f;
-  for (int64_t i = p; i < n; i += split) {
-    const float* row = x + (i * c + ch) * s;
-    if (VEC) {
-      const float4* r4 = (const float4*)row;
-      const int64_t s4 = s >> 2;
-      for (int64_t j = threadIdx.x; j < s4; j += BN_THREADS) {
-        const float4 v = __ldcs(r4 + j);
-        const float a = v.x - shift, b = v.y - shift, cc = v.z - shift, d = v.w - shift;
-        s1 += (a + b) + (cc + d);
-        s2 += (a * a + b * b) + (cc * cc + d * d);
-        cnt += 4.0f;
+  if (VEC) {
+    // four rows per pass: four independent 128-bit loads in flight per thread
+    const int64_t s4 = s >> 2;
+    for (int64_t i = p; i < n; i += 4 * (int64_t)split) {
+      const float4* r4[4];
+      bool ok[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t ii = i + (int64_t)u * split;
+        ok[u] = ii < n;
+        r4[u] = (const float4*)(x + ((ok[u] ? ii : i) * c + ch) * s);
       }
-    } else {
+      for (int64_t j = threadIdx.x; j < s4; j += BN_THREADS) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = ok[u] ? __ldcs(r4[u] + j) : make_float4(shift, shift, shift, shift);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float a = v[u].x - shift, b = v[u].y - shift, cc = v[u].z - shift, d = v[u].w - shift;
+          s1 += (a + b) + (cc + d);
+          s2 += (a * a + b * b) + (cc * cc + d * d);
+          cnt += ok[u] ? 4.0f : 0.0f;
+        }
+      }
+    }
+  } else {
+    for (int64_t i = p; i < n; i += split) {
+      const float* row = x + (i * c + ch) * s;
       for (int64_t j = threadIdx.x; j < s; j += BN_THREADS) {
         const float a = row[j] - shift;
         s1 += a;
@@ -146,6 +161,71 @@ bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ gamma, co
   }
 }
 
+// Row-structured variants for long contiguous rows (s4 >= 32 float4): one (sample, channel) row per block pass, so
+// the per-element channel lookup (an integer division) disappears; two rows per pass for memory-level parallelism.
+__global__ void __launch_bounds__(BN_THREADS)
+bn_apply_rows_kernel(const float4* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                     const float* __restrict__ mean, const float* __restrict__ rstd, float4* __restrict__ y, int64_t s4,
+                     int64_t c, int64_t rows, int act) {
+  for (int64_t r0 = (int64_t)blockIdx.x * 2; r0 < rows; r0 += (int64_t)gridDim.x * 2) {
+    const bool ok2 = r0 + 1 < rows;
+    const int64_t ch0 = r0 % c, ch1 = (r0 + 1) % c;
+    const float mu0 = __ldg(mean + ch0), sc0 = __ldg(rstd + ch0) * (gamma ? __ldg(gamma + ch0) : 1.0f), sf0 = beta ? __ldg(beta + ch0) : 0.0f;
+    const float mu1 = __ldg(mean + ch1), sc1 = __ldg(rstd + ch1) * (gamma ? __ldg(gamma + ch1) : 1.0f), sf1 = beta ? __ldg(beta + ch1) : 0.0f;
+    const float4* xa = x + r0 * s4;
+    float4* ya = y + r0 * s4;
+    for (int64_t j = threadIdx.x; j < s4; j += BN_THREADS) {
+      const float4 va = __ldcs(xa + j);
+      float4 vb = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ok2) vb = __ldcs(xa + s4 + j);
+      float4 oa, ob;
+      oa.x = fmaf(va.x - mu0, sc0, sf0); oa.y = fmaf(va.y - mu0, sc0, sf0); oa.z = fmaf(va.z - mu0, sc0, sf0); oa.w = fmaf(va.w - mu0, sc0, sf0);
+      ob.x = fmaf(vb.x - mu1, sc1, sf1); ob.y = fmaf(vb.y - mu1, sc1, sf1); ob.z = fmaf(vb.z - mu1, sc1, sf1); ob.w = fmaf(vb.w - mu1, sc1, sf1);
+      if (act != FB_ACT_IDENTITY) {
+        oa.x = fb_act_apply(act, oa.x); oa.y = fb_act_apply(act, oa.y); oa.z = fb_act_apply(act, oa.z); oa.w = fb_act_apply(act, oa.w);
+        ob.x = fb_act_apply(act, ob.x); ob.y = fb_act_apply(act, ob.y); ob.z = fb_act_apply(act, ob.z); ob.w = fb_act_apply(act, ob.w);
+      }
+      __stcs(ya + j, oa);
+      if (ok2) __stcs(ya + s4 + j, ob);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(BN_THREADS)
+bn_bwd_apply_rows_kernel(const float4* __restrict__ x, const float4* __restrict__ dy, const float* __restrict__ gamma,
+                         const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ rstd,
+                         const float* __restrict__ coef, float4* __restrict__ dx, int64_t s4, int64_t c, int64_t rows, int act) {
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t ch = r % c;
+    const float mu = __ldg(mean + ch), rs = __ldg(rstd + ch);
+    const float ga = gamma ? __ldg(gamma + ch) : 1.0f, be = beta ? __ldg(beta + ch) : 0.0f;
+    const float m1 = __ldg(coef + ch * 2), m2 = __ldg(coef + ch * 2 + 1), k = ga * rs;
+    const float4* xa = x + r * s4;
+    const float4* da = dy + r * s4;
+    float4* oa = dx + r * s4;
+    for (int64_t j = threadIdx.x; j < s4; j += 2 * BN_THREADS) {
+      const int64_t j2 = j + BN_THREADS;
+      const bool ok2 = j2 < s4;
+      float4 xv[2], dz[2];
+      xv[0] = __ldcs(xa + j); dz[0] = __ldcs(da + j);
+      if (ok2) { xv[1] = __ldcs(xa + j2); dz[1] = __ldcs(da + j2); }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (u == 1 && !ok2) break;
+        const float h0 = (xv[u].x - mu) * rs, h1 = (xv[u].y - mu) * rs, h2 = (xv[u].z - mu) * rs, h3 = (xv[u].w - mu) * rs;
+        if (act != FB_ACT_IDENTITY) {
+          dz[u].x *= fb_act_grad_z(act, fmaf(h0, ga, be)); dz[u].y *= fb_act_grad_z(act, fmaf(h1, ga, be));
+          dz[u].z *= fb_act_grad_z(act, fmaf(h2, ga, be)); dz[u].w *= fb_act_grad_z(act, fmaf(h3, ga, be));
+        }
+        float4 o;
+        o.x = k * (dz[u].x - m1 - h0 * m2); o.y = k * (dz[u].y - m1 - h1 * m2);
+        o.z = k * (dz[u].z - m1 - h2 * m2); o.w = k * (dz[u].w - m1 - h3 * m2);
+        __stcs(oa + (u == 0 ? j : j2), o);
+      }
+    }
+  }
+}
+
 // --------------------------------------------------------------------------- backward reduce ---
 // part[c][split][2] = (sum dz, sum dz*xhat) with dz = dy * act'(gamma*xhat+beta)
 template <bool VEC>
@@ -159,24 +239,35 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy, 
   const float mu = mean[ch], rs = rstd[ch];
   const float ga = gamma ? gamma[ch] : 1.0f, be = beta ? beta[ch] : 0.0f;
   float a1 = 0.0f, a2 = 0.0f;
-  for (int64_t i = p; i < n; i += split) {
-    const int64_t base = (i * c + ch) * s;
-    if (VEC) {
-      const float4* x4 = (const float4*)(x + base);
-      const float4* d4 = (const float4*)(dy + base);
-      const int64_t s4 = s >> 2;
+  if (VEC) {
+    const int64_t s4 = s >> 2;
+    for (int64_t i = p; i < n; i += 2 * (int64_t)split) {
+      const int64_t i2 = i + split;
+      const bool ok2 = i2 < n;
+      const float4* xa = (const float4*)(x + (i * c + ch) * s);
+      const float4* da = (const float4*)(dy + (i * c + ch) * s);
+      const float4* xb = (const float4*)(x + ((ok2 ? i2 : i) * c + ch) * s);
+      const float4* db = (const float4*)(dy + ((ok2 ? i2 : i) * c + ch) * s);
       for (int64_t j = threadIdx.x; j < s4; j += BN_THREADS) {
-        const float4 xv = __ldcs(x4 + j);
-        float4 dz = __ldcs(d4 + j);
-        const float h0 = (xv.x - mu) * rs, h1 = (xv.y - mu) * rs, h2 = (xv.z - mu) * rs, h3 = (xv.w - mu) * rs;
-        if (act != FB_ACT_IDENTITY) {
-          dz.x *= fb_act_grad_z(act, fmaf(h0, ga, be)); dz.y *= fb_act_grad_z(act, fmaf(h1, ga, be));
-          dz.z *= fb_act_grad_z(act, fmaf(h2, ga, be)); dz.w *= fb_act_grad_z(act, fmaf(h3, ga, be));
+        float4 xv[2], dz[2];
+        xv[0] = __ldcs(xa + j); dz[0] = __ldcs(da + j);
+        if (ok2) { xv[1] = __ldcs(xb + j); dz[1] = __ldcs(db + j); }
+        else { xv[1] = make_float4(mu, mu, mu, mu); dz[1] = make_float4(0.f, 0.f, 0.f, 0.f); }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const float h0 = (xv[u].x - mu) * rs, h1 = (xv[u].y - mu) * rs, h2 = (xv[u].z - mu) * rs, h3 = (xv[u].w - mu) * rs;
+          if (act != FB_ACT_IDENTITY) {
+            dz[u].x *= fb_act_grad_z(act, fmaf(h0, ga, be)); dz[u].y *= fb_act_grad_z(act, fmaf(h1, ga, be));
+            dz[u].z *= fb_act_grad_z(act, fmaf(h2, ga, be)); dz[u].w *= fb_act_grad_z(act, fmaf(h3, ga, be));
+          }
+          a1 += (dz[u].x + dz[u].y) + (dz[u].z + dz[u].w);
+          a2 += (dz[u].x * h0 + dz[u].y * h1) + (dz[u].z * h2 + dz[u].w * h3);
         }
-        a1 += (dz.x + dz.y) + (dz.z + dz.w);
-        a2 += (dz.x * h0 + dz.y * h1) + (dz.z * h2 + dz.w * h3);
       }
-    } else {
+    }
+  } else {
+    for (int64_t i = p; i < n; i += split) {
+      const int64_t base = (i * c + ch) * s;
       for (int64_t j = threadIdx.x; j < s; j += BN_THREADS) {
         const float h = (x[base + j] - mu) * rs;
         const float dz = dy[base + j] * fb_act_grad_z(act, fmaf(h, ga, be));
@@ -276,6 +367,14 @@ unsigned bn_elem_grid(const fb_ctx* ctx, int64_t work_items) {
   return (unsigned)blocks;
 }
 
+unsigned bn_row_grid(const fb_ctx* ctx, int64_t rows) {
+  int64_t blocks = (rows + 1) / 2;
+  const int64_t cap = (int64_t)ctx->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
 int32_t bn_check(const char* fn, int64_t s, int64_t c, int64_t n, int act) {
   FB_REQUIRE(s >= 1 && c >= 1 && n >= 0, FB_ERR_SHAPE, "%s: bad shape s=%lld c=%lld n=%lld", fn, (long long)s,
              (long long)c, (long long)n);
@@ -314,7 +413,8 @@ FB_API int32_t fb_batchnorm_fwd_train(fb_ctx* ctx, void* stream_, const float* x
                                                                            upd ? running_var : nullptr);
   FB_LAUNCH_CHECK();
   const int64_t total = s * c * n;
-  if (vec) bn_apply_kernel<true><<<bn_elem_grid(ctx, total / 4), BN_THREADS, 0, stream>>>(x, gamma, beta, save_mean, save_rstd, y, s, c, total, act);
+  if (vec && s >= 128) bn_apply_rows_kernel<<<bn_row_grid(ctx, c * n), BN_THREADS, 0, stream>>>((const float4*)x, gamma, beta, save_mean, save_rstd, (float4*)y, s / 4, c, c * n, act);
+  else if (vec) bn_apply_kernel<true><<<bn_elem_grid(ctx, total / 4), BN_THREADS, 0, stream>>>(x, gamma, beta, save_mean, save_rstd, y, s, c, total, act);
   else bn_apply_kernel<false><<<bn_elem_grid(ctx, total), BN_THREADS, 0, stream>>>(x, gamma, beta, save_mean, save_rstd, y, s, c, total, act);
   FB_LAUNCH_CHECK();
   return FB_OK;
@@ -348,7 +448,8 @@ FB_API int32_t fb_batchnorm_fwd_infer(fb_ctx* ctx, void* stream_, const float* x
   }
   FB_LAUNCH_CHECK();
   const int64_t total = s * c * n;
-  if (vec) bn_apply_kernel<true><<<bn_elem_grid(ctx, total / 4), BN_THREADS, 0, stream>>>(x, gamma, beta, mean, rstd, y, s, c, total, act);
+  if (vec && s >= 128) bn_apply_rows_kernel<<<bn_row_grid(ctx, c * n), BN_THREADS, 0, stream>>>((const float4*)x, gamma, beta, mean, rstd, (float4*)y, s / 4, c, c * n, act);
+  else if (vec) bn_apply_kernel<true><<<bn_elem_grid(ctx, total / 4), BN_THREADS, 0, stream>>>(x, gamma, beta, mean, rstd, y, s, c, total, act);
   else bn_apply_kernel<false><<<bn_elem_grid(ctx, total), BN_THREADS, 0, stream>>>(x, gamma, beta, mean, rstd, y, s, c, total, act);
   FB_LAUNCH_CHECK();
   return FB_OK;
@@ -378,7 +479,8 @@ FB_API int32_t fb_batchnorm_bwd(fb_ctx* ctx, void* stream_, const float* x, cons
   bn_bwd_finalize_kernel<<<(unsigned)((c + 127) / 128), 128, 0, stream>>>(part, split, c, (float)(s * n), coef, dgamma, dbeta);
   FB_LAUNCH_CHECK();
   const int64_t total = s * c * n;
-  if (vec) bn_bwd_apply_kernel<true><<<bn_elem_grid(ctx, total / 4), BN_THREADS, 0, stream>>>(x, dy, gamma, beta, save_mean, save_rstd, coef, dx, s, c, total, act);
+  if (vec && s >= 128) bn_bwd_apply_rows_kernel<<<bn_row_grid(ctx, c * n), BN_THREADS, 0, stream>>>((const float4*)x, (const float4*)dy, gamma, beta, save_mean, save_rstd, coef, (float4*)dx, s / 4, c, c * n, act);
+  else if (vec) bn_bwd_apply_kernel<true><<<bn_elem_grid(ctx, total / 4), BN_THREADS, 0, stream>>>(x, dy, gamma, beta, save_mean, save_rstd, coef, dx, s, c, total, act);
   else bn_bwd_apply_kernel<false><<<bn_elem_grid(ctx, total), BN_THREADS, 0, stream>>>(x, dy, gamma, beta, save_mean, save_rstd, coef, dx, s, c, total, act);
   FB_LAUNCH_CHECK();
   return FB_OK;

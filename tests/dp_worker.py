@@ -1,0 +1,122 @@
+"""Worker of the multi-GPU DistributedUtils test (one process per GPU, launched by torch.distributed.run).
+
+Checks, like the reference's test/ext_distributed scripts: bcast of ones, reduce / allreduce with + and avg against
+closed forms (common.jl:19-87), synchronize of a model and optimiser state (synchronized.jl), shard sizes (data.jl),
+and that data-parallel training with bucketed, overlapped gradient averaging reproduces a single-process run on
+the full batch (optimizer.jl:8-25 extended to the whole model).
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (os.path.join(ROOT, "flux.jl_b200"), os.path.join(ROOT, "oracle")):
+    sys.path.insert(0, p)
+import fluxb200 as F  # noqa: E402
+import flux_oracle as O  # noqa: E402
+
+DU = F.DistributedUtils
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    backend = DU.initialize(DU.NCCLBackend, device=local)
+    assert DU.local_rank(backend) == rank and DU.total_workers(backend) == world
+
+    # collectives: closed forms
+    buf = F.gpu(np.ones(512, np.float32) if rank == 0 else np.zeros(512, np.float32))
+    DU.bcast(backend, buf, root=0)
+    assert (F.cpu(buf) == 1).all()
+    tot = sum(range(1, world + 1))
+    buf = F.gpu(np.full(512, rank + 1.0, np.float32))
+    DU.allreduce(backend, buf, "+")
+    assert (F.cpu(buf) == tot).all()
+    buf = F.gpu(np.full(512, rank + 1.0, np.float32))
+    DU.allreduce(backend, buf, DU.avg)
+    np.testing.assert_allclose(F.cpu(buf), tot / world, rtol=1e-6)
+    src, dst = F.gpu(np.full(512, rank + 1.0, np.float32)), F.gpu(np.zeros(512, np.float32))
+    DU.allreduce(backend, src, dst, "+")
+    assert (F.cpu(dst) == tot).all() and (F.cpu(src) == rank + 1).all()
+    buf = F.gpu(np.full(512, rank + 1.0, np.float32))
+    DU.reduce(backend, buf, "+", root=0)
+    assert (F.cpu(buf) == (tot if rank == 0 else rank + 1)).all()
+
+    # data container: contiguous ceil(n/N) shards whose sizes add up
+    data = np.arange(10 * 7, dtype=np.float32).reshape(7, 10)
+    ddc = DU.DistributedDataContainer(backend, data)
+    assert len(ddc) == min(int(np.ceil(10 / world)), max(10 - rank * int(np.ceil(10 / world)), 0))
+
+    # data-parallel training == single-process training on the full batch
+    rng = np.random.default_rng(7)             # same stream on every rank
+    Dm, Cc, NB, GB, steps = 256, 24, 2, 64, 3
+    blocks = [{"gamma": (rng.normal(size=Dm) * 0.1 + 1).astype(np.float32), "beta": (rng.normal(size=Dm) * 0.1).astype(np.float32),
+               "W": O.glorot_uniform(rng, Dm, Dm), "b": np.zeros(Dm, np.float32)} for _ in range(NB)]
+    head = {"W": O.glorot_uniform(rng, Cc, Dm), "b": np.zeros(Cc, np.float32)}
+    x = rng.standard_normal((Dm, GB), dtype=np.float32)
+    labels = rng.integers(1, Cc + 1, size=GB)
+    layers = []
+    for blk in blocks:
+        ln = F.LayerNorm(Dm)
+        # every rank but 0 starts from different values; synchronize must overwrite them
+        scale = blk["gamma"] if rank == 0 else blk["gamma"] * 0 + 5
+        ln.diag.scale, ln.diag.bias = F.gpu(scale), F.gpu(blk["beta"])
+        layers += [ln, F.Dense(blk["W"] if rank == 0 else blk["W"] * 0, blk["b"], "gelu")]
+    layers.append(F.Dense(head["W"], head["b"]))
+    model = F.Chain(*layers)
+    DU.synchronize(backend, DU.FluxDistributedModel(model))
+    np.testing.assert_array_equal(F.cpu(model.layers[1].weight), blocks[0]["W"])
+    np.testing.assert_array_equal(F.cpu(model.layers[0].diag.scale), blocks[0]["gamma"])
+    params = F.trainables(model)
+    buckets = DU.GradBuckets(backend, params, bucket_mb=0.2)     # several buckets even for this small model
+    assert len(buckets.buckets) >= 3
+    opt = F.setup(DU.DistributedOptimizer(backend, F.Adam(1e-3), buckets), model)
+    DU.synchronize(backend, opt)
+    idx = DU.shard_indices(GB, world, rank)
+    xg, yg = F.gpu(np.ascontiguousarray(x[:, idx])), F.onehotbatch(labels[idx], Cc)
+
+    to64 = lambda d: {k: v.astype(np.float64) for k, v in d.items()}
+    b64, h64 = [to64(b) for b in blocks], to64(head)
+    st_b = [{k: O.adam_init(v) for k, v in b.items()} for b in b64]
+    st_h = {k: O.adam_init(v) for k, v in h64.items()}
+    y1h = O.onehotbatch(labels, Cc, np.float64)
+    for step in range(steps):
+        buckets.begin_step()
+        l, gs = F.withgradient(lambda m: F.logitcrossentropy(m(xg), yg), model, grad_sink=buckets)
+        F.update(opt, model, gs[0])
+        lref, gb, gh = O.dp_mlp_fwd_bwd(b64, h64, x.astype(np.float64), y1h)
+        # the mean of the per-rank local means equals the full-batch mean for equal shards
+        lsum = torch.tensor([l], dtype=torch.float64)
+        if world > 1:
+            torch.distributed.all_reduce(lsum)
+        assert abs(lsum.item() / world - lref) < 1e-4 * abs(lref), (lsum.item() / world, lref)
+        if step == 0:
+            # averaged gradients (read back from the bucket views) against the full-batch oracle gradients
+            g0 = F.cpu(buckets.views[id(model.layers[1].weight)])
+            np.testing.assert_allclose(g0, gb[0]["W"], rtol=2e-4, atol=2e-4 * np.abs(gb[0]["W"]).max())
+            gl = F.cpu(buckets.views[id(model.layers[0].diag.scale)])
+            np.testing.assert_allclose(gl, gb[0]["gamma"], rtol=2e-4, atol=2e-4 * np.abs(gb[0]["gamma"]).max())
+        for blk, g, st in zip(b64, gb, st_b):
+            for k in blk:
+                blk[k] = O.adam_apply(st[k], blk[k], g[k])
+        for k in h64:
+            h64[k] = O.adam_apply(st_h[k], h64[k], gh[k])
+    # replicas stay identical across ranks (bitwise: every rank applies the same averaged gradients)
+    w = model.layers[1].weight
+    chk = torch.stack([w.t.double().sum(), (w.t.double() ** 2).sum()]).cpu()
+    lo, hi = chk.clone(), chk.clone()
+    if world > 1:
+        torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
+        torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
+    assert torch.equal(lo, hi), "replicas diverged"
+    assert np.max(np.abs(F.cpu(w) - b64[0]["W"])) < 3.5e-3        # within the three Adam steps' reach of the oracle
+    assert F.context().device_error() == 0
+    if rank == 0:
+        print("dp_worker ok", world)
+
+
+if __name__ == "__main__":
+    main()
