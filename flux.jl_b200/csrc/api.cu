@@ -50,6 +50,7 @@ FB_API int32_t fb_ctx_create(int32_t device, fb_ctx** out) {
   c->smem_optin = prop.sharedMemPerBlockOptin;
   c->scratch = nullptr;
   c->scratch_bytes = 0;
+  c->retired_count = 0;
   c->dev_error = nullptr;
   c->tmap_cache = nullptr;
   e = cudaMalloc(&c->dev_error, 256);
@@ -67,6 +68,7 @@ FB_API int32_t fb_ctx_destroy(fb_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaDeviceSynchronize();
   if (ctx->scratch) cudaFree(ctx->scratch);
+  for (int i = 0; i < ctx->retired_count; ++i) cudaFree(ctx->retired[i]);
   if (ctx->dev_error) cudaFree(ctx->dev_error);
   fb_tmap_cache_destroy(ctx);
   delete ctx;
@@ -74,22 +76,20 @@ FB_API int32_t fb_ctx_destroy(fb_ctx* ctx) {
 }
 
 void* fb_scratch(fb_ctx* ctx, cudaStream_t stream, size_t bytes) {
+  (void)stream;
   if (bytes <= ctx->scratch_bytes && ctx->scratch != nullptr) return ctx->scratch;
+  // grow geometrically; the outgrown block stays allocated until the context is destroyed, because work already
+  // enqueued - or captured in a CUDA graph - may still name it
   size_t want = bytes < (size_t(1) << 22) ? (size_t(1) << 22) : bytes;
+  if (want < 2 * ctx->scratch_bytes) want = 2 * ctx->scratch_bytes;
   want = (want + 255) & ~size_t(255);
-  if (ctx->scratch) {
-    // work already enqueued may still use the old block: wait for it before releasing
-    cudaStreamSynchronize(stream);
-    cudaFree(ctx->scratch);
-    ctx->scratch = nullptr;
-    ctx->scratch_bytes = 0;
-  }
   void* p = nullptr;
   if (cudaMalloc(&p, want) != cudaSuccess) {
     cudaGetLastError();
     fb_set_error("scratch arena: cudaMalloc of %zu bytes failed", want);
     return nullptr;
   }
+  if (ctx->scratch != nullptr && ctx->retired_count < FB_MAX_RETIRED) ctx->retired[ctx->retired_count++] = ctx->scratch;
   ctx->scratch = p;
   ctx->scratch_bytes = want;
   return p;

@@ -11,12 +11,16 @@
 #define FB_API extern "C" __attribute__((visibility("default")))
 
 // ---------------------------------------------------------------------------- context ---
+constexpr int FB_MAX_RETIRED = 64;   // the arena doubles, so this is never reached
+
 struct fb_ctx {
   int device;
   int sm_count;
   size_t smem_optin;
   void* scratch;         // device arena, grown on demand, reused by every call on this context
   size_t scratch_bytes;
+  void* retired[FB_MAX_RETIRED];   // outgrown arena blocks, released with the context
+  int retired_count;
   int32_t* dev_error;    // device error word written by kernels whose bounded waits ran out
   void* tmap_cache;      // opaque (gemm_tc.cu): encoded TMA descriptors keyed by (ptr, shape)
 };
@@ -25,8 +29,8 @@ struct fb_ctx {
 void fb_set_error(const char* fmt, ...);
 int32_t fb_fail(int32_t code, const char* fmt, ...);
 
-// Returns a pointer into the context arena of at least `bytes` (256-byte aligned); grows the arena
-// (stream-ordered free of the old block) when it is too small.  NULL on allocation failure.
+// Returns a pointer into the context arena of at least `bytes` (256-byte aligned); grows the arena when it is
+// too small (outgrown blocks are kept until fb_ctx_destroy).  NULL on allocation failure.
 void* fb_scratch(fb_ctx* ctx, cudaStream_t stream, size_t bytes);
 
 #define FB_CHECK_CTX(ctx)                                                   \

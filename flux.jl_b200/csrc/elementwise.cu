@@ -159,7 +159,14 @@ struct AdamTable {
 
 __global__ void __launch_bounds__(EW_THREADS)
 adam_kernel(const __grid_constant__ AdamTable tab, float eta, float beta1, float beta2, float eps, float inv_c1,
-            float inv_c2, float grad_scale) {
+            float inv_c2, float grad_scale, const float* __restrict__ bt_dev, const float* __restrict__ guard) {
+  // device-resident step state (used when the step is replayed from a CUDA graph): the running beta powers
+  // and an optional guard scalar (the loss) whose non-finite value skips the update
+  if (guard != nullptr && !isfinite(__ldg(guard))) return;
+  if (bt_dev != nullptr) {
+    inv_c1 = 1.0f / (1.0f - __ldg(bt_dev));
+    inv_c2 = 1.0f / (1.0f - __ldg(bt_dev + 1));
+  }
   int t = 0;
   while (t + 1 < tab.ntensors && (int)blockIdx.x >= tab.block_start[t + 1]) ++t;
   const int64_t begin = (int64_t)(blockIdx.x - tab.block_start[t]) * ADAM_CHUNK;
@@ -426,12 +433,48 @@ FB_API int32_t fb_logitcrossentropy_dense(fb_ctx* ctx, void* stream, const float
   return xent_common(ctx, (cudaStream_t)stream, yhat, nullptr, y, loss, dyhat, c, n, dloss, "fb_logitcrossentropy_dense");
 }
 
+static int32_t adam_common(fb_ctx* ctx, cudaStream_t stream, int32_t ntensors, float* const* w_host,
+                           const float* const* g_host, float* const* m_host, float* const* v_host,
+                           const int64_t* counts_host, float eta, float beta1, float beta2, float eps, float b1t,
+                           float b2t, float grad_scale, const float* bt_dev, const float* guard);
+
 FB_API int32_t fb_adam_step(fb_ctx* ctx, void* stream_, int32_t ntensors, float* const* w_host,
                             const float* const* g_host, float* const* m_host, float* const* v_host,
                             const int64_t* counts_host, float eta, float beta1, float beta2, float eps, float b1t,
                             float b2t, float grad_scale) {
   FB_CHECK_CTX(ctx);
-  cudaStream_t stream = (cudaStream_t)stream_;
+  return adam_common(ctx, (cudaStream_t)stream_, ntensors, w_host, g_host, m_host, v_host, counts_host, eta, beta1, beta2, eps,
+                     b1t, b2t, grad_scale, nullptr, nullptr);
+}
+
+FB_API int32_t fb_adam_step_dev(fb_ctx* ctx, void* stream_, int32_t ntensors, float* const* w_host,
+                                const float* const* g_host, float* const* m_host, float* const* v_host,
+                                const int64_t* counts_host, float eta, float beta1, float beta2, float eps,
+                                const float* bt_dev, const float* guard_dev, float grad_scale) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(bt_dev != nullptr, FB_ERR_INVALID_ARG, "fb_adam_step_dev: bt_dev is NULL");
+  return adam_common(ctx, (cudaStream_t)stream_, ntensors, w_host, g_host, m_host, v_host, counts_host, eta, beta1, beta2, eps,
+                     0.0f, 0.0f, grad_scale, bt_dev, guard_dev);
+}
+
+__global__ void adam_advance_kernel(float* __restrict__ bt, float beta1, float beta2, const float* __restrict__ guard) {
+  if (guard != nullptr && !isfinite(*guard)) return;
+  bt[0] *= beta1;
+  bt[1] *= beta2;
+}
+
+FB_API int32_t fb_adam_advance(fb_ctx* ctx, void* stream_, float* bt_dev, float beta1, float beta2, const float* guard_dev) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(bt_dev != nullptr, FB_ERR_INVALID_ARG, "fb_adam_advance: bt_dev is NULL");
+  adam_advance_kernel<<<1, 1, 0, (cudaStream_t)stream_>>>(bt_dev, beta1, beta2, guard_dev);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}
+
+static int32_t adam_common(fb_ctx* ctx, cudaStream_t stream, int32_t ntensors, float* const* w_host,
+                           const float* const* g_host, float* const* m_host, float* const* v_host,
+                           const int64_t* counts_host, float eta, float beta1, float beta2, float eps, float b1t,
+                           float b2t, float grad_scale, const float* bt_dev, const float* guard) {
   FB_REQUIRE(ntensors >= 0, FB_ERR_INVALID_ARG, "fb_adam_step: negative tensor count");
   if (ntensors == 0) return FB_OK;
   FB_REQUIRE(w_host && g_host && m_host && v_host && counts_host, FB_ERR_INVALID_ARG, "fb_adam_step: NULL table");
@@ -461,7 +504,7 @@ FB_API int32_t fb_adam_step(fb_ctx* ctx, void* stream_, int32_t ntensors, float*
     if (k == 0) continue;
     tab.block_start[k] = blocks;
     tab.ntensors = k;
-    adam_kernel<<<(unsigned)blocks, EW_THREADS, 0, stream>>>(tab, eta, beta1, beta2, eps, inv_c1, inv_c2, grad_scale);
+    adam_kernel<<<(unsigned)blocks, EW_THREADS, 0, stream>>>(tab, eta, beta1, beta2, eps, inv_c1, inv_c2, grad_scale, bt_dev, guard);
     FB_LAUNCH_CHECK();
   }
   return FB_OK;

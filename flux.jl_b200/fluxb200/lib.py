@@ -72,6 +72,9 @@ PROTOTYPES = {
     "fb_cast_bf16_f32": (_i32, [_p, _p, _p, _p, _i64]),
     "fb_adam_step": (_i32, [_p, _p, _i32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_p),
                             C.POINTER(_i64), _f, _f, _f, _f, _f, _f, _f]),
+    "fb_adam_step_dev": (_i32, [_p, _p, _i32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_p),
+                                C.POINTER(_i64), _f, _f, _f, _f, _p, _p, _f]),
+    "fb_adam_advance": (_i32, [_p, _p, _p, _f, _f, _p]),
     "fb_lstm_cache_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "fb_gru_cache_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "fb_lstm_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),

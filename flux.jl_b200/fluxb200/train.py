@@ -138,13 +138,8 @@ def _grad_tree(obj, grads: dict):
     return None
 
 
-def withgradient(f, model, grad_sink=None):
-    """Flux.withgradient(m -> loss, model): returns (loss_value, (grad_tree,)).
-
-    `f(model)` must return a scalar B200Array (or a tuple whose first element is one, like Zygote's
-    auxiliary-output form).  The loss value comes back as a Python float (one device -> host read,
-    the same sync `_eager_step!` pays at src/train.jl:377).
-    """
+def _withgradient_device(f, model, grad_sink=None):
+    """Forward + reverse sweep without any device -> host read: returns (loss B200Array, aux, grad_tree)."""
     assert not Tape.active, "nested withgradient is not supported"
     Tape.reset()
     Tape.active = True
@@ -179,6 +174,17 @@ def withgradient(f, model, grad_sink=None):
         Tape.active = False
         Tape.grad_sink = None
         Tape.reset()
+    return loss, aux, tree
+
+
+def withgradient(f, model, grad_sink=None):
+    """Flux.withgradient(m -> loss, model): returns (loss_value, (grad_tree,)).
+
+    `f(model)` must return a scalar B200Array (or a tuple whose first element is one, like Zygote's
+    auxiliary-output form).  The loss value comes back as a Python float (one device -> host read,
+    the same sync `_eager_step!` pays at src/train.jl:377).
+    """
+    loss, aux, tree = _withgradient_device(f, model, grad_sink)
     val = float(loss.t.item())
     if aux is not None:
         return (val,) + tuple(aux), (tree,)
@@ -325,3 +331,110 @@ def train(loss, model, data, opt_state):
         lv = l[0] if isinstance(l, tuple) else l
         if not math.isfinite(lv):
             raise DomainError(f"Loss is {lv} on data item {i + 1}, stopping training")
+
+
+# ------------------------------------------------------------------ one-launch train step ---
+def _clone_static(b):
+    if isinstance(b, B200Array):
+        return B200Array(b.t.clone(), b.size)
+    if isinstance(b, OneHotLabels):
+        return OneHotLabels(B200Array(b.labels.t.clone(), b.labels.size), b.nclasses)
+    return b
+
+
+def _copy_into(dst, src):
+    if isinstance(dst, B200Array):
+        t = src.t if isinstance(src, B200Array) else src
+        dst.t.copy_(t, non_blocking=True)
+    elif isinstance(dst, OneHotLabels):
+        t = src.labels.t if isinstance(src, OneHotLabels) else src
+        dst.labels.t.copy_(t, non_blocking=True)
+
+
+class GraphedTrainStep:
+    """`trainstep!` for a fixed batch shape as ONE CUDA-graph launch: forward, reverse sweep, gradient averaging
+    (when `opt_state` wraps a DistributedOptimizer) and the Adam update are captured once and replayed.
+
+    This is the device-specific train-step hook Flux already has a slot for (src/train.jl:335-339; the Reactant
+    extension compiles the step per batch shape, ext/FluxReactantExt.jl:147-152).  Semantics follow `_eager_step!`
+    (src/train.jl:375-379): the returned loss is the pre-update loss, and a non-finite loss leaves parameters and
+    optimiser state untouched (the captured Adam kernels read the loss on the device and skip themselves).
+
+    `step(*batch)` accepts B200 arrays / OneHotLabels, or pinned host tensors of the same sizes (copied into the
+    step's static input buffers on the current stream).
+    """
+
+    def __init__(self, loss, model, opt_state, example_batch, grad_sink=None):
+        from .layers import BatchNorm, _walk
+        if not isinstance(example_batch, tuple):
+            example_batch = (example_batch,)
+        rule = opt_state.rule
+        if not isinstance(rule, Adam):
+            raise lib.FluxB200Error(-7, "GraphedTrainStep supports the Adam rule")
+        self.model, self.opt_state, self.sink = model, opt_state, grad_sink
+        self.static = tuple(_clone_static(b) for b in example_batch)
+        self.params = [p for p in opt_state.params]
+        seen = set()
+        self.params = [p for p in self.params if not (id(p) in seen or seen.add(id(p)))]
+        bts = {opt_state.leaves[id(p)].state[2] for p in self.params}
+        if len(bts) != 1:
+            raise lib.FluxB200Error(-7, "GraphedTrainStep needs all leaves at the same step count")
+        self.bt = torch.tensor(list(bts.pop()), dtype=torch.float32, device=self.params[0].t.device)
+        ctx = context()
+        fn = lambda m: loss(m, *self.static)
+        # warm-up outside the graph: grows the library's scratch arena and torch's pools; running statistics of
+        # BatchNorm layers are put back afterwards so that the warm-up leaves no trace
+        bns = [l for l in _walk(model) if isinstance(l, BatchNorm) and l.track_stats]
+        saved = [(l.μ.t.clone(), l.σ2.t.clone()) for l in bns]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            if grad_sink is not None:
+                grad_sink.begin_step()
+            _withgradient_device(fn, model, grad_sink)
+            if grad_sink is not None:
+                grad_sink.finish()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for l, (mu, var) in zip(bns, saved):
+            l.μ.t.copy_(mu)
+            l.σ2.t.copy_(var)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            if grad_sink is not None:
+                grad_sink.begin_step()
+            loss_arr, _, tree = _withgradient_device(fn, model, grad_sink)
+            gmap: dict = {}
+            _flat_grads(model, tree, gmap)
+            outer = getattr(opt_state, "outer", None)
+            if isinstance(outer, DistributedOptimizerBase):
+                outer.average_gradients(opt_state, gmap)
+            ps = [p for p in self.params if id(p) in gmap]
+            k = len(ps)
+            arr_t = C.c_void_p * k
+            self._tables = (arr_t(*[p.t.data_ptr() for p in ps]), arr_t(*[gmap[id(p)].t.data_ptr() for p in ps]),
+                            arr_t(*[opt_state.leaves[id(p)].state[0].t.data_ptr() for p in ps]),
+                            arr_t(*[opt_state.leaves[id(p)].state[1].t.data_ptr() for p in ps]),
+                            (C.c_int64 * k)(*[p.numel() for p in ps]))
+            c = context()
+            lib.call("fb_adam_step_dev", c.handle, c.stream, k, *self._tables, rule.eta, rule.beta[0], rule.beta[1],
+                     rule.epsilon, C.c_void_p(self.bt.data_ptr()), loss_arr.ptr, 1.0)
+            lib.call("fb_adam_advance", c.handle, c.stream, C.c_void_p(self.bt.data_ptr()), rule.beta[0], rule.beta[1],
+                     loss_arr.ptr)
+            self._keep = (loss_arr, tree, gmap)
+        self.loss_arr = loss_arr
+        self._updated = ps
+
+    def __call__(self, *batch):
+        for dst, src in zip(self.static, batch):
+            if src is not dst:
+                _copy_into(dst, src)
+        self.graph.replay()
+        lv = float(self.loss_arr.t.item())
+        if math.isfinite(lv):
+            rule = self.opt_state.rule
+            f32 = np.float32
+            for p in self._updated:
+                st = self.opt_state.leaves[id(p)].state
+                st[2] = (float(f32(st[2][0]) * f32(rule.beta[0])), float(f32(st[2][1]) * f32(rule.beta[1])))
+        return lv

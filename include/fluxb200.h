@@ -218,6 +218,18 @@ int32_t fb_adam_step(fb_ctx* ctx, void* stream, int32_t ntensors, float* const* 
                      const int64_t* counts_host, float eta, float beta1, float beta2, float eps,
                      float b1t, float b2t, float grad_scale);
 
+/* The same update with its step state on the device, for a train step replayed from a CUDA graph (the
+ * device-specific one-launch `trainstep!` hook, src/train.jl:335-339): bt_dev[2] holds the running powers
+ * (beta1^t, beta2^t); guard_dev (optional) is a device scalar - the loss - whose non-finite value skips the update,
+ * as `_eager_step!` does (src/train.jl:377).  fb_adam_advance multiplies the powers by (beta1, beta2) under the
+ * same guard. */
+int32_t fb_adam_step_dev(fb_ctx* ctx, void* stream, int32_t ntensors, float* const* w_host,
+                         const float* const* g_host, float* const* m_host, float* const* v_host,
+                         const int64_t* counts_host, float eta, float beta1, float beta2, float eps,
+                         const float* bt_dev, const float* guard_dev, float grad_scale);
+int32_t fb_adam_advance(fb_ctx* ctx, void* stream, float* bt_dev, float beta1, float beta2,
+                        const float* guard_dev);
+
 /* ------------------------------------------------------------------------- Recurrence -- */
 
 /* Bytes of the saved-for-backward buffer of fb_lstm_fwd / fb_gru_fwd. */

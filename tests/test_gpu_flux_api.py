@@ -264,3 +264,43 @@ def test_dp_block_model_gradients_match_oracle(F):
         close(F.cpu(g["layers"][2 * i + 1]["weight"]), ref["W"], rtol=2e-4, atol_scale=2e-4)
         close(F.cpu(g["layers"][2 * i + 1]["bias"]), ref["b"], rtol=2e-4, atol_scale=2e-4)
     close(F.cpu(g["layers"][-1]["weight"]), gh["W"], rtol=2e-4, atol_scale=2e-4)
+
+
+def test_graphed_trainstep_equals_eager_and_skips_on_nan(F):
+    """The one-launch (CUDA graph) train step against the eager `trainstep` on identical models, and the
+    non-finite-loss rule of `_eager_step!` (src/train.jl:377; test/train.jl:130-141) inside the graph."""
+    rng = np.random.default_rng(11)
+    D, Cc, N = 128, 10, 64
+    Ws = [O.glorot_uniform(rng, D, D), O.glorot_uniform(rng, Cc, D)]
+    x = rng.standard_normal((D, N), dtype=np.float32)
+    labels = rng.integers(1, Cc + 1, size=N)
+
+    def build():
+        ln = F.LayerNorm(D)
+        return F.Chain(ln, F.Dense(Ws[0].copy(), True, "gelu"), F.Dense(Ws[1].copy(), True))
+
+    loss = lambda m, x_, y_: F.logitcrossentropy(m(x_), y_)
+    xg, yg = F.gpu(x), F.onehotbatch(labels, Cc)
+    m1, m2 = build(), build()
+    o1, o2 = F.setup(F.Adam(1e-3), m1), F.setup(F.Adam(1e-3), m2)
+    gstep = F.GraphedTrainStep(loss, m2, o2, (xg, yg))
+    for step in range(4):
+        l1 = F.trainstep(loss, m1, (xg, yg), o1)
+        l2 = gstep(xg, yg)
+        assert l1 == l2, (step, l1, l2)
+    for a, b in zip(F.trainables(m1), F.trainables(m2)):
+        np.testing.assert_array_equal(F.cpu(a), F.cpu(b))
+    assert o1.leaves[id(F.trainables(m1)[0])].state[2] == pytest.approx(o2.leaves[id(F.trainables(m2)[0])].state[2])
+    # a batch that makes the loss NaN: parameters, moments and the beta powers stay as they are
+    before = [F.cpu(p).copy() for p in F.trainables(m2)]
+    bt_before = gstep.bt.cpu().numpy().copy()
+    xbad = x.copy()
+    xbad[0, 0] = np.nan
+    lbad = gstep(F.gpu(xbad), yg)
+    assert not np.isfinite(lbad)
+    for p, b in zip(F.trainables(m2), before):
+        np.testing.assert_array_equal(F.cpu(p), b)
+    np.testing.assert_array_equal(gstep.bt.cpu().numpy(), bt_before)
+    # and the step keeps working afterwards
+    l3 = gstep(xg, yg)
+    assert np.isfinite(l3) and l3 < l2 + 1e-3
