@@ -77,6 +77,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// One 3-d load for a whole MN-major tile: the matrix is viewed as {32 floats, K rows, MN/32 chunks}, the box
+// {32, BK, chunks} lands chunk after chunk, which is the shared-memory layout the MMA descriptor names.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+
 // Asks the memory system to bring a tile into L2 (no shared memory, no barrier): used a few k-blocks ahead of the
 // real load so that the load itself hits L2.
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
@@ -202,7 +211,7 @@ template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR>
 __global__ void __launch_bounds__(Cfg<BN, PASSES, PAIR>::NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                float* __restrict__ C, int64_t ldc, float* __restrict__ Z, const float* __restrict__ bias_n, int M,
-               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int prefetch_kb) {
+               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int prefetch_kb, int a3d, int b3d) {
   using cfg = Cfg<BN, PASSES, PAIR>;
   constexpr int STAGES = cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -310,14 +319,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t b_dst = a_dst + (uint32_t)((PASSES == 3 ? 2 : 1) * cfg::A_BYTES);
         const int k0 = kb * BK;
         if (A_MN) {
+          if (a3d) {
+            tma_load_3d(a_dst, &tmA, 0, k0, m0 >> 5, full_bar(s));
+          } else {
 #pragma unroll
-          for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + (uint32_t)(c * BK * 128), &tmA, m0 + 32 * c, k0, full_bar(s));
+            for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + (uint32_t)(c * BK * 128), &tmA, m0 + 32 * c, k0, full_bar(s));
+          }
         } else {
           tma_load_2d(a_dst, &tmA, k0, m0, full_bar(s));
         }
         if (B_MN) {
+          if (b3d) {
+            tma_load_3d(b_dst, &tmB, 0, k0, nb0 >> 5, full_bar(s));
+          } else {
 #pragma unroll
-          for (int c = 0; c < cfg::BNC / 32; ++c) tma_load_2d(b_dst + (uint32_t)(c * BK * 128), &tmB, nb0 + 32 * c, k0, full_bar(s));
+            for (int c = 0; c < cfg::BNC / 32; ++c) tma_load_2d(b_dst + (uint32_t)(c * BK * 128), &tmB, nb0 + 32 * c, k0, full_bar(s));
+          }
         } else {
           tma_load_2d(b_dst, &tmB, k0, nb0, full_bar(s));
         }
@@ -556,16 +573,39 @@ int prefetch_from_env() {
   return n;
 }
 
+// 3-d view {32, K, MN / 32} of an MN-major matrix (row k holds MN contiguous floats): box {32, BK, chunks}.
+// Only for MN a multiple of 32, so that no chunk straddles the end of a row.
+bool encode_map_mn3d(CUtensorMap* map, const float* base, int64_t K, int64_t MN, int64_t ld, uint32_t chunks) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn || MN % 32 != 0) return false;
+  cuuint64_t gdim[3] = {32, (cuuint64_t)K, (cuuint64_t)(MN / 32)};
+  cuuint64_t gstride[2] = {(cuuint64_t)ld * sizeof(float), 128};
+  cuuint32_t box[3] = {32, (cuuint32_t)BK, chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR>
 int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
   using cfg = Cfg<BN, PASSES, PAIR>;
   CUtensorMap tmA, tmB;
   bool ok;
-  if (A_MN) ok = encode_map(&tmA, a.A, a.K, a.M, a.lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-  else ok = encode_map(&tmA, a.A, a.M, a.K, a.lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_64B);
+  int a3d = 0, b3d = 0;
+  if (A_MN) {
+    a3d = encode_map_mn3d(&tmA, a.A, a.K, a.M, a.lda, BM / 32) ? 1 : 0;
+    ok = a3d || encode_map(&tmA, a.A, a.K, a.M, a.lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  } else {
+    ok = encode_map(&tmA, a.A, a.M, a.K, a.lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_64B);
+  }
   if (ok) {
-    if (B_MN) ok = encode_map(&tmB, a.B, a.K, a.N, a.ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    else ok = encode_map(&tmB, a.B, a.N, a.K, a.ldb, BK, cfg::BNC, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (B_MN) {
+      b3d = encode_map_mn3d(&tmB, a.B, a.K, a.N, a.ldb, cfg::BNC / 32) ? 1 : 0;
+      ok = b3d || encode_map(&tmB, a.B, a.K, a.N, a.ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    } else {
+      ok = encode_map(&tmB, a.B, a.N, a.K, a.ldb, BK, cfg::BNC, CU_TENSOR_MAP_SWIZZLE_64B);
+    }
   }
   if (!ok) return fb_fail(FB_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed (M=%lld N=%lld K=%lld lda=%lld ldb=%lld)",
                           (long long)a.M, (long long)a.N, (long long)a.K, (long long)a.lda, (long long)a.ldb);
@@ -586,7 +626,7 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   lc.attrs = attr;
   lc.numAttrs = 1;
   FB_CUDA(cudaLaunchKernelEx(&lc, kern, tmA, tmB, a.C, a.ldc, a.Z, a.bias_n, (int)a.M, (int)a.N, (int)a.K, a.act,
-                             a.accumulate, ctx->dev_error, prefetch_from_env()));
+                             a.accumulate, ctx->dev_error, prefetch_from_env(), a3d, b3d));
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
@@ -634,8 +674,10 @@ int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& 
   if (!fb_gemm_tc_supported(a)) return FB_ERR_UNSUPPORTED;
   const bool passes_flag_pair = (passes == 32);
   if (passes_flag_pair) passes = 3;
+  // 128 x 256 tiles unless they would leave most of the machine idle: the wider tile does twice the MMA work per
+  // split / barrier round trip, so one 86 %-full wave of them beats two waves of 128 x 128 tiles
   const int64_t tiles256 = ((a.M + BM - 1) / BM) * ((a.N + 255) / 256);
-  const bool narrow = (a.N <= 128) || (tiles256 < ctx->sm_count);
+  const bool narrow = (a.N <= 128) || (2 * tiles256 <= ctx->sm_count);
   if (passes == 3) {
     // two-CTA 256 x 256 tiles when the problem fills the machine with them
     if ((passes_flag_pair || pair_kernel_enabled()) && a.M >= 256 && a.N >= 256 && (a.N + 255) / 256 <= 65535 &&

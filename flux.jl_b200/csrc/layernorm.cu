@@ -355,7 +355,16 @@ fb_colreduce2_kernel(const float* __restrict__ part_a, const float* __restrict__
   const int64_t col = (int64_t)blockIdx.x * 32 + tx;
   float a = 0.0f, b = 0.0f;
   if (col < d) {
-    for (int64_t g = ty; g < groups; g += 8) {
+    // four independent loads per array in flight
+    int64_t g = ty;
+    for (; g + 24 < groups; g += 32) {
+      const float a0 = part_a[g * d + col], a1 = part_a[(g + 8) * d + col], a2 = part_a[(g + 16) * d + col], a3 = part_a[(g + 24) * d + col];
+      float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+      if (part_b) { b0 = part_b[g * d + col]; b1 = part_b[(g + 8) * d + col]; b2 = part_b[(g + 16) * d + col]; b3 = part_b[(g + 24) * d + col]; }
+      a += (a0 + a1) + (a2 + a3);
+      b += (b0 + b1) + (b2 + b3);
+    }
+    for (; g < groups; g += 8) {
       a += part_a[g * d + col];
       if (part_b) b += part_b[g * d + col];
     }
