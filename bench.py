@@ -304,6 +304,136 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------- the other four configurations ---
+def run_small_config(args):
+    """Configurations 1-4 of the benchmark set (single GPU): one JSON line each, same keys as the headline line."""
+    import torch
+    import fluxb200 as F
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import flux_oracle as O
+    torch.cuda.set_device(0)
+    F.context(0)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    tf32 = peaks.get("bf16_tflops", 1590.0) / 2.0
+    rng = np.random.default_rng(args.config)
+    f64 = lambda a: a.astype(np.float64)
+
+    def time_gpu(fn, steps, warmup):
+        for _ in range(max(warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def time_cpu(fn, reps=2):
+        best = None
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        return best
+
+    lines = []
+    if args.config == 1:
+        dims = [(512, 784, "relu"), (512, 512, "relu"), (10, 512, "identity")]
+        Ws = [O.glorot_uniform(np.random.default_rng(0), o, i) for o, i, _ in dims]
+        x = rng.random((784, 1024), dtype=np.float32)
+        labels = rng.integers(1, 11, size=1024)
+        model = F.Chain(*[F.Dense(W.copy(), True, s_) for W, (_, _, s_) in zip(Ws, dims)])
+        opt = F.setup(F.Adam(1e-3), model)
+        xg, yg = F.gpu(x), F.onehotbatch(labels, 10)
+        loss = lambda m, a, b: F.logitcrossentropy(m(a), b)
+        gstep = F.GraphedTrainStep(loss, model, opt, (xg, yg))
+        ms = time_gpu(lambda: gstep(xg, yg), args.steps, args.warmup)
+        ms_eager = time_gpu(lambda: F.trainstep(loss, model, (xg, yg), opt), args.steps, args.warmup)
+        y1h = O.onehotbatch(labels, 10, np.float32)
+        layers = [(W, np.zeros(W.shape[0], np.float32), s_) for W, (_, _, s_) in zip(Ws, dims)]
+        cpu = time_cpu(lambda: O.mlp_chain_fwd_bwd(layers, x, y1h), 3)
+        flops = 3.286e9
+        lines.append(("mlp: Chain(Dense(784=>512,relu),Dense(512=>512,relu),Dense(512=>10)), batch 1024, logitcrossentropy+Adam, CUDA graph step",
+                      1024, ms, {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": tf32, "unit": "TFLOP/s", "frac": flops / ms / 1e9 / tf32,
+                                 "traffic": None, "note": f"launch/latency-bound (3.3 GFLOP per step); eager launches take {ms_eager:.3f} ms per step"},
+                      1024 / cpu, "1024 of 1024 samples, forward+backward (no Adam), best of 3"))
+    elif args.config == 2:
+        xb = (rng.standard_normal((32, 32, 256, 128), dtype=np.float32) * 2 + 0.5)
+        bn = F.trainmode(F.BatchNorm(256, "relu"))
+        xg = F.gpu(xb)
+        ms = time_gpu(lambda: F.withgradient(lambda m: F.sum_abs2(m(xg)), bn), args.steps, args.warmup)
+        E = xb.size
+        xs = xb[:, :, :, :8]
+        cpu = time_cpu(lambda: (O.batchnorm_fwd_train(xs, np.ones(256, np.float32), np.zeros(256, np.float32), np.zeros(256, np.float32), np.ones(256, np.float32), sigma="relu"),
+                                O.batchnorm_bwd(xs, np.ones(256, np.float32), np.zeros(256, np.float32), 2 * xs, sigma="relu")))
+        by = 11.0 * E * 4
+        lines.append(("batchnorm: BatchNorm(256,relu) train, 32x32x256x128 Float32, forward + gradient of sum(abs2,y)", 128, ms,
+                      {"bound": "hbm", "achieved": by / ms / 1e6, "peak": hbm, "unit": "GB/s", "frac": by / ms / 1e6 / hbm, "traffic": None,
+                       "note": "11 passes x 134.2 MB: layer (8) + sum(abs2) read (1) + cotangent 2y read+write (2)"},
+                      8 / cpu, "8 of 128 samples, best of 2"))
+        xl = rng.standard_normal((4096, 16384), dtype=np.float32)
+        ln = F.LayerNorm(4096)
+        xlg = F.gpu(xl)
+        ms = time_gpu(lambda: F.withgradient(lambda m: F.sum_abs2(m(xlg)), ln), args.steps, args.warmup)
+        xls = xl[:, :1024]
+        g1, b1 = np.ones(4096, np.float32), np.zeros(4096, np.float32)
+        cpu = time_cpu(lambda: (O.layernorm_fwd(xls, g1, b1), O.layernorm_bwd(xls, g1, b1, 2 * xls)))
+        by = 8.0 * xl.size * 4
+        lines.append(("layernorm: LayerNorm(4096) on 4096x16384 Float32, forward + gradient of sum(abs2,y)", 16384, ms,
+                      {"bound": "hbm", "achieved": by / ms / 1e6, "peak": hbm, "unit": "GB/s", "frac": by / ms / 1e6 / hbm, "traffic": None,
+                       "note": "8 passes x 268.4 MB: layer (5) + sum(abs2) read (1) + cotangent 2y read+write (2)"},
+                      1024 / cpu, "1024 of 16384 samples, best of 2"))
+    elif args.config == 3:
+        Hh, T, B = 512, 256, 64
+        r1 = np.random.default_rng(1)
+        Wi, Wh = O.glorot_uniform(r1, 4 * Hh, Hh), O.glorot_uniform(r1, 4 * Hh, Hh)
+        x = rng.standard_normal((Hh, T, B), dtype=np.float32)
+        rnn = F.LSTM(Wi, Wh)
+        xg = F.gpu(x)
+        ms = time_gpu(lambda: F.withgradient(lambda m: F.sum_abs2(m(xg)), rnn), args.steps, args.warmup)
+        xs, bz = x[:, :, :4], np.zeros(4 * Hh, np.float32)
+        cpu = time_cpu(lambda: O.lstm_scan_bwd(Wi, Wh, bz, xs, 2 * O.lstm_scan_fwd(Wi, Wh, bz, xs)[0]), 1)
+        flops = 171.8e9
+        lines.append(("lstm: LSTM(512=>512) via Recurrence, 512x256x64 Float32, forward + gradient of sum(abs2,out)", 64, ms,
+                      {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": tf32, "unit": "TFLOP/s", "frac": flops / ms / 1e9 / tf32, "traffic": None,
+                       "note": f"bounded by 2 x 256 dependent steps: {ms * 1e3 / 512:.1f} us per time step (forward and backward)"},
+                      4 / cpu, "4 of 64 sequences, 1 run"))
+    elif args.config == 4:
+        E, S, B, Hn = 1024, 2048, 8, 16
+        r2 = np.random.default_rng(2)
+        Ws = [O.glorot_uniform(r2, E, E) for _ in range(4)]
+        x = rng.standard_normal((E, S, B), dtype=np.float32)
+        mha = F.MultiHeadAttention(*Ws, nheads=Hn)
+        xg = F.gpu(x)
+        ms = time_gpu(lambda: F.withgradient(lambda m: F.sum_abs2(m(xg, mask=F.make_causal_mask())[0]), mha), args.steps, args.warmup)
+        xs = x[:, :512, :1]
+        def cpu_fn():
+            y, _ = O.mha_fwd(*Ws, xs, nheads=Hn, mask=O.make_causal_mask(512))
+            O.mha_bwd(*Ws, xs, 2 * y, nheads=Hn, mask=O.make_causal_mask(512))
+        cpu = time_cpu(cpu_fn, 1)
+        flops = 652.8e9
+        lines.append(("mha: MultiHeadAttention(1024, nheads=16), causal, 1024x2048x8 Float32, forward + backward (loss on y)", 8, ms,
+                      {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": tf32, "unit": "TFLOP/s", "frac": flops / ms / 1e9 / tf32, "traffic": None,
+                       "note": "projections on tcgen05 (3xTF32); the attention core is the fp32 FMA flash kernel in this version"},
+                      (1 * (512 / 2048) ** 2 * 1.0) / cpu * 1.0, "1 of 8 samples at seq 512 (1/16 of a sample's attention work, 1/4 of its projections), 1 run"))
+    if F.context().device_error() != 0:
+        raise SystemExit("a kernel recorded a bounded-wait timeout; the numbers are invalid")
+    cores = os.cpu_count() or 1
+    for workload, samples, ms, roof, cpu_v, cpu_s in lines:
+        print(json.dumps({"metric": METRIC, "value": samples / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic", "config": {"workload": workload}, "roofline": roof,
+                          "cpu_baseline": {"value": cpu_v, "unit": "samples/s", "cores": cores, "kind": "port", "sample": cpu_s}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -312,9 +442,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bucket-mb", dest="bucket_mb", type=float, default=64.0)
     ap.add_argument("--eager", action="store_true", help="launch every kernel from the host each step instead of replaying a CUDA graph")
+    ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5],
+                    help="5 (default): the data-parallel MLP the headline metric is quoted on; 1-4: the single-GPU configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.config != 5:
+        run_small_config(args)
     else:
         run_ours(args)
 

@@ -136,7 +136,7 @@ lstm_fwd_step_kernel(const float* __restrict__ Wh, const float* __restrict__ gx,
 __global__ void __launch_bounds__(RT)
 lstm_bwd_gates_kernel(float* __restrict__ gates_t, int64_t ldg, const float* __restrict__ c_t,
                       const float* __restrict__ c_prev, int64_t ldc, int64_t ldcp,
-                      const float* __restrict__ dout_t, int64_t ldo, const float* __restrict__ dh_rec,
+                      const float* __restrict__ dout_t, int64_t ldo, const float* __restrict__ dh_rec, int nparts,
                       float* __restrict__ dc, int H, int B) {
   const int64_t total = (int64_t)B * H;
   for (int64_t e = (int64_t)blockIdx.x * RT + threadIdx.x; e < total; e += (int64_t)gridDim.x * RT) {
@@ -145,7 +145,8 @@ lstm_bwd_gates_kernel(float* __restrict__ gates_t, int64_t ldg, const float* __r
     const float ig = gr[u], fg = gr[H + u], gg = gr[2 * H + u], og = gr[3 * H + u];
     const float tc = tanhf(c_t[(int64_t)b * ldc + u]);
     const float cp = c_prev ? c_prev[(int64_t)b * ldcp + u] : 0.0f;
-    const float dh = dout_t[(int64_t)b * ldo + u] + (dh_rec ? dh_rec[e] : 0.0f);
+    float dh = dout_t[(int64_t)b * ldo + u];
+    if (dh_rec) for (int p = 0; p < nparts; ++p) dh += dh_rec[(int64_t)p * total + e];   // partials of Wh' * dgates
     const float d_o = dh * tc;
     const float dcc = dc[e] + dh * og * (1.0f - tc * tc);
     gr[u] = dcc * gg * ig * (1.0f - ig);
@@ -153,37 +154,6 @@ lstm_bwd_gates_kernel(float* __restrict__ gates_t, int64_t ldg, const float* __r
     gr[2 * H + u] = dcc * ig * (1.0f - gg * gg);
     gr[3 * H + u] = d_o * og * (1.0f - og);
     dc[e] = dcc * fg;
-  }
-}
-
-// dh_rec[b][u] = (add ? add[b][u] : 0) + sum_r Wm[u][r] * dg[b][r], r over R = NG*H.  Wm is Wh memory [H][R],
-// so the HU rows of a block are contiguous.  A block owns HU units.
-template <int HU>
-__global__ void __launch_bounds__(RT)
-rnn_bwd_dh_kernel(const float* __restrict__ Wh, const float* __restrict__ dg, int64_t ldg, const float* __restrict__ add,
-                  float* __restrict__ dh_rec, int H, int R, int B) {
-  extern __shared__ float sm[];
-  const int kp = (R + KC - 1) / KC * KC;
-  float* Ws = sm;                 // [HU][kp]
-  float* vs = Ws + HU * kp;       // [BC][HS]
-  float* red = vs + BC * HS;      // [4][BC][HU+1]
-  const int u0 = blockIdx.x * HU;
-  for (int e = threadIdx.x; e < HU * kp; e += RT) {
-    const int u = e / kp, k = e % kp;
-    Ws[e] = (u0 + u < H && k < R) ? __ldg(Wh + (int64_t)(u0 + u) * R + k) : 0.0f;
-  }
-  for (int b0 = 0; b0 < B; b0 += BC) {
-    float acc[HU];
-    rows_times_vec<HU>(Ws, kp, dg, ldg, R, b0, B, vs, acc);
-    reduce_quarters<HU>(red, acc);
-    for (int e = threadIdx.x; e < BC * HU; e += RT) {
-      const int bb = e / HU, u = e % HU;
-      const int gb = b0 + bb, gu = u0 + u;
-      if (gb < B && gu < H) {
-        const int64_t o = (int64_t)gb * H + gu;
-        dh_rec[o] = red[bb * (HU + 1) + u] + (add ? add[o] : 0.0f);
-      }
-    }
   }
 }
 
@@ -233,16 +203,17 @@ gru_fwd_step_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, 
 // dh_direct = dh*z (the part of dh_{t-1} that does not go through Wh).
 __global__ void __launch_bounds__(RT)
 gru_bwd_gates_kernel(const float* __restrict__ cache_t, int64_t ldcache, const float* __restrict__ hprev, int64_t ldh,
-                     const float* __restrict__ dout_t, int64_t ldo, const float* __restrict__ dh_rec,
-                     float* __restrict__ dgx_t, float* __restrict__ dgh_t, int64_t ldd, float* __restrict__ dh_direct,
-                     int H, int B) {
+                     const float* __restrict__ dout_t, int64_t ldo, const float* __restrict__ dh_rec, int nparts,
+                     const float* __restrict__ dh_add, float* __restrict__ dgx_t, float* __restrict__ dgh_t, int64_t ldd,
+                     float* __restrict__ dh_direct, int H, int B) {
   const int64_t total = (int64_t)B * H;
   for (int64_t e = (int64_t)blockIdx.x * RT + threadIdx.x; e < total; e += (int64_t)gridDim.x * RT) {
     const int b = (int)(e / H), u = (int)(e % H);
     const float* cr = cache_t + (int64_t)b * ldcache;
     const float r = cr[u], z = cr[H + u], hc = cr[2 * H + u], gh3 = cr[3 * H + u];
     const float hp = hprev ? hprev[(int64_t)b * ldh + u] : 0.0f;
-    const float dh = dout_t[(int64_t)b * ldo + u] + (dh_rec ? dh_rec[e] : 0.0f);
+    float dh = dout_t[(int64_t)b * ldo + u] + (dh_add ? dh_add[e] : 0.0f);
+    if (dh_rec) for (int p = 0; p < nparts; ++p) dh += dh_rec[(int64_t)p * total + e];
     const float da3 = dh * (1.0f - z) * (1.0f - hc * hc);
     const float da2 = dh * (hp - hc) * z * (1.0f - z);
     const float da1 = da3 * gh3 * r * (1.0f - r);
@@ -253,6 +224,224 @@ gru_bwd_gates_kernel(const float* __restrict__ cache_t, int64_t ldcache, const f
     dh_direct[e] = dh * z;
   }
 }
+
+
+// =============================================================================================
+// Fast step kernels (H a multiple of 4 and small enough for shared memory): every global load of a step is a
+// 128-bit load issued up front, so a step costs one memory round trip plus the FMA work.
+// =============================================================================================
+
+// pre[b][r] = sum_k W[r][k] * hprev[b][k] for the NG*4 gate rows of units [u0, u0+4) and a 64-wide batch chunk.
+//   Ws: [NG*4][kp] (kp = H rounded up to 16), hs: [64][kp + 4], red: [4][64][NG*4 + 1].
+//   On return red[b * (NR + 1) + r] holds the sums for this chunk.
+template <int NG>
+__device__ __forceinline__ void fast_gate_preacts(const float* __restrict__ Wh, const float* __restrict__ hprev, int64_t ldh,
+                                                  int H, int B, int b0, int u0, int kp, float* __restrict__ Ws,
+                                                  float* __restrict__ hs, float* __restrict__ red, bool load_w) {
+  constexpr int NR = NG * 4;
+  const int hs_ld = kp + 4;
+  const int k4n = kp >> 2;
+  if (load_w) {
+    // W[k][g][u0 .. u0+3] is one 16-byte piece of the [H][NG*H] weight memory
+    for (int e = threadIdx.x; e < kp * NG; e += RT) {
+      const int k = e / NG, g = e % NG;
+      float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < H) w = __ldg((const float4*)(Wh + (int64_t)k * (NG * H) + g * H + u0));
+      Ws[(g * 4 + 0) * kp + k] = w.x;
+      Ws[(g * 4 + 1) * kp + k] = w.y;
+      Ws[(g * 4 + 2) * kp + k] = w.z;
+      Ws[(g * 4 + 3) * kp + k] = w.w;
+    }
+  }
+  if (hprev != nullptr) {
+    for (int e = threadIdx.x; e < BC * k4n; e += RT) {
+      const int bb = e / k4n, k4 = e % k4n;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (b0 + bb < B && 4 * k4 < H) v = __ldg((const float4*)(hprev + (int64_t)(b0 + bb) * ldh + 4 * k4));
+      *(float4*)(hs + bb * hs_ld + 4 * k4) = v;
+    }
+  }
+  __syncthreads();
+  const int b = threadIdx.x & (BC - 1), kq = threadIdx.x >> 6;
+  float acc[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
+  if (hprev != nullptr) {
+    const int per = k4n >> 2;                       // float4 steps per quarter
+    const float4* hrow = (const float4*)(hs + b * hs_ld) + kq * per;
+    for (int i = 0; i < per; ++i) {
+      const float4 hv = hrow[i];
+      const int kbase = (kq * per + i) * 4;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const float4 w = *(const float4*)(Ws + r * kp + kbase);
+        acc[r] = fmaf(w.x, hv.x, acc[r]);
+        acc[r] = fmaf(w.y, hv.y, acc[r]);
+        acc[r] = fmaf(w.z, hv.z, acc[r]);
+        acc[r] = fmaf(w.w, hv.w, acc[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < NR; ++r) red[(kq * BC + b) * (NR + 1) + r] = acc[r];
+  __syncthreads();
+  for (int e = threadIdx.x; e < BC * NR; e += RT) {
+    const int bb = e / NR, r = e % NR;
+    float sum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) sum += red[(q * BC + bb) * (NR + 1) + r];
+    red[bb * (NR + 1) + r] = sum;
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(RT)
+lstm_fwd_fast_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, int64_t ldgx,
+                     const float* __restrict__ hprev, int64_t ldh, const float* __restrict__ cprev, int64_t ldc,
+                     float* __restrict__ out_t, int64_t ldo, float* __restrict__ gates_t, int64_t ldg,
+                     float* __restrict__ c_t, int64_t ldct, float* __restrict__ hT, float* __restrict__ cT, int H, int B) {
+  extern __shared__ __align__(16) float sm[];
+  const int kp = (H + 15) & ~15;
+  float* Ws = sm;
+  float* hs = Ws + 16 * kp;
+  float* red = hs + BC * (kp + 4);
+  const int u0 = blockIdx.x * 4;
+  for (int b0 = 0; b0 < B; b0 += BC) {
+    if (b0 > 0) __syncthreads();
+    fast_gate_preacts<4>(Wh, hprev, ldh, H, B, b0, u0, kp, Ws, hs, red, b0 == 0);
+    const int bb = threadIdx.x >> 2, u = threadIdx.x & 3;     // 64 x 4 (batch, unit) pairs
+    const int gb = b0 + bb, gu = u0 + u;
+    if (gb < B && gu < H) {
+      const float* pre = red + bb * 17;
+      const float* gxr = gx + (int64_t)gb * ldgx;
+      const float zi = pre[u] + gxr[gu], zf = pre[4 + u] + gxr[H + gu];
+      const float zg = pre[8 + u] + gxr[2 * H + gu], zo = pre[12 + u] + gxr[3 * H + gu];
+      const float ig = 1.0f / (1.0f + expf(-zi)), fg = 1.0f / (1.0f + expf(-zf));
+      const float gg = tanhf(zg), og = 1.0f / (1.0f + expf(-zo));
+      const float cp = cprev ? cprev[(int64_t)gb * ldc + gu] : 0.0f;
+      const float cn = fg * cp + ig * gg;
+      const float hn = og * tanhf(cn);
+      out_t[(int64_t)gb * ldo + gu] = hn;
+      if (gates_t) {
+        float* gr = gates_t + (int64_t)gb * ldg;
+        gr[gu] = ig; gr[H + gu] = fg; gr[2 * H + gu] = gg; gr[3 * H + gu] = og;
+      }
+      c_t[(int64_t)gb * ldct + gu] = cn;
+      if (hT) { hT[(int64_t)gb * H + gu] = hn; cT[(int64_t)gb * H + gu] = cn; }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(RT)
+gru_fwd_fast_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, int64_t ldgx,
+                    const float* __restrict__ hprev, int64_t ldh, float* __restrict__ out_t, int64_t ldo,
+                    float* __restrict__ cache_t, int64_t ldcache, float* __restrict__ hT, int H, int B) {
+  extern __shared__ __align__(16) float sm[];
+  const int kp = (H + 15) & ~15;
+  float* Ws = sm;
+  float* hs = Ws + 12 * kp;
+  float* red = hs + BC * (kp + 4);
+  const int u0 = blockIdx.x * 4;
+  for (int b0 = 0; b0 < B; b0 += BC) {
+    if (b0 > 0) __syncthreads();
+    fast_gate_preacts<3>(Wh, hprev, ldh, H, B, b0, u0, kp, Ws, hs, red, b0 == 0);
+    const int bb = threadIdx.x >> 2, u = threadIdx.x & 3;
+    const int gb = b0 + bb, gu = u0 + u;
+    if (gb < B && gu < H) {
+      const float* pre = red + bb * 13;
+      const float* gxr = gx + (int64_t)gb * ldgx;   // includes the bias
+      const float gh3 = pre[8 + u];
+      const float r = 1.0f / (1.0f + expf(-(gxr[gu] + pre[u])));
+      const float z = 1.0f / (1.0f + expf(-(gxr[H + gu] + pre[4 + u])));
+      const float hc = tanhf(gxr[2 * H + gu] + r * gh3);
+      const float hp = hprev ? hprev[(int64_t)gb * ldh + gu] : 0.0f;
+      const float hn = (1.0f - z) * hc + z * hp;
+      out_t[(int64_t)gb * ldo + gu] = hn;
+      if (cache_t) {
+        float* cr = cache_t + (int64_t)gb * ldcache;
+        cr[gu] = r; cr[H + gu] = z; cr[2 * H + gu] = hc; cr[3 * H + gu] = gh3;
+      }
+      if (hT) hT[(int64_t)gb * H + gu] = hn;
+    }
+  }
+}
+
+size_t fast_fwd_smem(int ng, int H) {
+  const int kp = (H + 15) & ~15;
+  return (size_t)(ng * 4 * kp + BC * (kp + 4) + 4 * BC * (ng * 4 + 1)) * sizeof(float);
+}
+
+// dh partials, 2-d decomposition: block (ub, rb, bz) computes, for units [64 ub, +64) and batch rows [64 bz, +64),
+// the partial sum over gate rows r in [256 rb, +256):  part[rb][b][u] = sum_r dg[b][r] * Wm[u][r].
+// Wm is the weight memory [H][R] (rows of R contiguous floats), so both operands stream as 128-bit loads.
+constexpr int DH_U = 64, DH_R = 256, DH_LD = DH_R + 4;
+
+__global__ void __launch_bounds__(RT)
+rnn_bwd_dh2d_kernel(const float* __restrict__ Wh, const float* __restrict__ dg, int64_t ldg, float* __restrict__ part,
+                    int H, int R, int B) {
+  extern __shared__ __align__(16) float sm[];
+  float* Ws = sm;                   // [64 u][DH_LD]
+  float* Ds = Ws + DH_U * DH_LD;    // [64 b][DH_LD]
+  const int u0 = blockIdx.x * DH_U, r0 = blockIdx.y * DH_R, b0 = blockIdx.z * BC;
+  const bool vec = ((R & 3) == 0) && ((ldg & 3) == 0) && ((((uintptr_t)Wh | (uintptr_t)dg) & 15) == 0);
+  for (int e = threadIdx.x; e < DH_U * (DH_R / 4); e += RT) {
+    const int row = e / (DH_R / 4), c4 = e % (DH_R / 4);
+    const int r = r0 + 4 * c4;
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f), d = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (vec && r + 3 < R) {
+      if (u0 + row < H) w = __ldg((const float4*)(Wh + (int64_t)(u0 + row) * R + r));
+      if (b0 + row < B) d = __ldg((const float4*)(dg + (int64_t)(b0 + row) * ldg + r));
+    } else {
+      float wv[4] = {0.f, 0.f, 0.f, 0.f}, dv[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int i = 0; i < 4; ++i)
+        if (r + i < R) {
+          if (u0 + row < H) wv[i] = Wh[(int64_t)(u0 + row) * R + r + i];
+          if (b0 + row < B) dv[i] = dg[(int64_t)(b0 + row) * ldg + r + i];
+        }
+      w = make_float4(wv[0], wv[1], wv[2], wv[3]);
+      d = make_float4(dv[0], dv[1], dv[2], dv[3]);
+    }
+    *(float4*)(Ws + row * DH_LD + 4 * c4) = w;
+    *(float4*)(Ds + row * DH_LD + 4 * c4) = d;
+  }
+  __syncthreads();
+  // 16 x 16 threads, each a 4 x 4 tile: rows b = ty + 16 i, columns u = tx + 16 j
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  for (int c = 0; c < DH_R; c += 4) {
+    float4 a[4], b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = *(const float4*)(Ds + (ty + 16 * i) * DH_LD + c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b[j] = *(const float4*)(Ws + (tx + 16 * j) * DH_LD + c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+      }
+  }
+  float* pp = part + (int64_t)blockIdx.y * B * H;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gb = b0 + ty + 16 * i;
+    if (gb >= B) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gu = u0 + tx + 16 * j;
+      if (gu < H) pp[(int64_t)gb * H + gu] = acc[i][j];
+    }
+  }
+}
+
+constexpr size_t DH2D_SMEM = (size_t)2 * DH_U * DH_LD * sizeof(float);
 
 // hprev_all[(b, t)] = t == 0 ? h0[b] (or 0) : out[(b, t-1)]
 __global__ void __launch_bounds__(RT)
@@ -285,11 +474,6 @@ int pick_hu(int ng, int H, size_t smem_optin, size_t extra) {
 size_t fwd_smem(int ng, int hu, int H) {
   const int kp = (H + KC - 1) / KC * KC;
   return (size_t)(ng * hu) * kp * 4 + (size_t)BC * HS * 4 + (size_t)4 * BC * (ng * hu + 1) * 4;
-}
-
-size_t dh_smem(int hu, int R) {
-  const int kp = (R + KC - 1) / KC * KC;
-  return (size_t)hu * kp * 4 + (size_t)BC * HS * 4 + (size_t)4 * BC * (hu + 1) * 4;
 }
 
 int32_t check_dims(const char* fn, int64_t in_dim, int64_t H, int64_t T, int64_t B) {
@@ -347,11 +531,14 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
   st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
   if (st != FB_OK) return st;
   // (2) time loop
-  const int hu = pick_hu(4, H, ctx->smem_optin, (size_t)BC * HS * 4);
+  const bool fast = (H % 4 == 0) && fb_aligned16(Wh) && fb_aligned16(out) && (!h0 || fb_aligned16(h0)) &&
+                    fast_fwd_smem(4, H) <= ctx->smem_optin;
+  const int hu = fast ? 4 : pick_hu(4, H, ctx->smem_optin, (size_t)BC * HS * 4);
   FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_lstm_fwd: hidden size %d does not fit the step kernel's shared memory", H);
-  const size_t smem = fwd_smem(4, hu, H);
+  const size_t smem = fast ? fast_fwd_smem(4, H) : fwd_smem(4, hu, H);
   auto kern = hu == 4 ? lstm_fwd_step_kernel<4> : hu == 2 ? lstm_fwd_step_kernel<2> : lstm_fwd_step_kernel<1>;
-  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (fast) FB_CUDA(cudaFuncSetAttribute(lstm_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
   const int64_t ldrow = T * H;       // stride between batch rows of out / cached c at a fixed t
   for (int64_t t = 0; t < T; ++t) {
@@ -372,10 +559,15 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
       c_t = cst + (t & 1) * (int64_t)B * H;
       ldct = H;
     }
-    // the kernel reads cprev at stride ldc and writes c_t at stride ldcache_c; both are passed
-    kern<<<grid, RT, smem, stream>>>(Wh, gx + t * 4 * H, hprev, ldh, cprev, ldcp, out + t * H, ldrow,
-                                     gates ? gates + t * 4 * H : nullptr, c_t, T * 4 * H, ldct,
-                                     (t == T - 1) ? hT : nullptr, (t == T - 1) ? cT : nullptr, H, B, T * 4 * H);
+    float* g_t = gates ? gates + t * 4 * H : nullptr;
+    float* hT_t = (t == T - 1) ? hT : nullptr;
+    float* cT_t = (t == T - 1) ? cT : nullptr;
+    if (fast)
+      lstm_fwd_fast_kernel<<<grid, RT, smem, stream>>>(Wh, gx + t * 4 * H, T * 4 * H, hprev, ldh, cprev, ldcp, out + t * H, ldrow,
+                                                       g_t, T * 4 * H, c_t, ldct, hT_t, cT_t, H, B);
+    else
+      kern<<<grid, RT, smem, stream>>>(Wh, gx + t * 4 * H, hprev, ldh, cprev, ldcp, out + t * H, ldrow, g_t, c_t, T * 4 * H, ldct,
+                                       hT_t, cT_t, H, B, T * 4 * H);
     FB_LAUNCH_CHECK();
   }
   return FB_OK;
@@ -396,34 +588,30 @@ FB_API int32_t fb_lstm_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
   const int64_t T = seq_len, rows = T * batch, ldrow = T * H;
   float* gates = (float*)cache;              // overwritten in place by the gate derivatives
   const float* cst = gates + rows * 4 * H;
-  float* ws = (float*)fb_scratch(ctx, stream, (size_t)(3 * (int64_t)B * H) * sizeof(float));
+  const int R = 4 * H;
+  const int nparts = (R + DH_R - 1) / DH_R;
+  float* ws = (float*)fb_scratch(ctx, stream, (size_t)((1 + nparts) * (int64_t)B * H) * sizeof(float));
   if (!ws) return FB_ERR_ALLOC;
   float* dc = ws;                            // [B][H]
-  float* dh_a = ws + (int64_t)B * H;         // ping-pong recurrent dh
-  float* dh_b = dh_a + (int64_t)B * H;
+  float* parts = ws + (int64_t)B * H;        // [nparts][B][H] partial sums of Wh' * dgates
   if (dcT) FB_CUDA(cudaMemcpyAsync(dc, dcT, (size_t)B * H * sizeof(float), cudaMemcpyDeviceToDevice, stream));
   else FB_CUDA(cudaMemsetAsync(dc, 0, (size_t)B * H * sizeof(float), stream));
-  const int hu = pick_hu(1, 4 * H, ctx->smem_optin, (size_t)BC * HS * 4);
-  FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_lstm_bwd: hidden size %d does not fit the step kernel's shared memory", H);
-  const size_t smem = dh_smem(hu, 4 * H);
-  auto kern = hu == 4 ? rnn_bwd_dh_kernel<4> : hu == 2 ? rnn_bwd_dh_kernel<2> : rnn_bwd_dh_kernel<1>;
-  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const unsigned grid_dh = (unsigned)((H + hu - 1) / hu);
+  FB_CUDA(cudaFuncSetAttribute(rnn_bwd_dh2d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DH2D_SMEM));
+  const dim3 grid_dh((unsigned)((H + DH_U - 1) / DH_U), (unsigned)nparts, (unsigned)((B + BC - 1) / BC));
   int64_t eb = ((int64_t)B * H + RT - 1) / RT;
   if (eb > ctx->sm_count * 8) eb = ctx->sm_count * 8;
-  const float* dh_rec = dhT;                 // recurrent dh entering step t (dhT at the last step)
   for (int64_t t = T - 1; t >= 0; --t) {
     float* g_t = gates + t * 4 * H;
     const float* c_prev = t == 0 ? c0 : cst + (t - 1) * H;
+    // recurrent dh entering step t: dhT at the last step, the partials of the step after it otherwise
+    const float* dh_rec = (t == T - 1) ? dhT : parts;
     lstm_bwd_gates_kernel<<<(unsigned)eb, RT, 0, stream>>>(g_t, T * 4 * H, cst + t * H, c_prev, ldrow,
                                                            t == 0 ? (int64_t)H : ldrow, dout + t * H, ldrow, dh_rec,
-                                                           dc, H, B);
+                                                           (t == T - 1) ? 1 : nparts, dc, H, B);
     FB_LAUNCH_CHECK();
     if (t > 0) {
-      float* dh_next = (dh_rec == dh_a) ? dh_b : dh_a;
-      kern<<<grid_dh, RT, smem, stream>>>(Wh, g_t, T * 4 * H, nullptr, dh_next, H, 4 * H, B);
+      rnn_bwd_dh2d_kernel<<<grid_dh, RT, DH2D_SMEM, stream>>>(Wh, g_t, T * 4 * H, parts, H, R, B);
       FB_LAUNCH_CHECK();
-      dh_rec = dh_next;
     }
   }
   // bulk GEMMs over all T*B columns (dg = gates buffer, [rows][4H])
@@ -490,17 +678,25 @@ FB_API int32_t fb_gru_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
   a.M = rows; a.N = 3 * hidden; a.K = in_dim; a.act = FB_ACT_IDENTITY; a.accumulate = 0;
   st = fb_gemm_dispatch(ctx, stream, a, FB_PREC_DEFAULT);
   if (st != FB_OK) return st;
-  const int hu = pick_hu(3, H, ctx->smem_optin, (size_t)BC * HS * 4);
+  const bool fast = (H % 4 == 0) && fb_aligned16(Wh) && fb_aligned16(out) && (!h0 || fb_aligned16(h0)) &&
+                    fast_fwd_smem(3, H) <= ctx->smem_optin;
+  const int hu = fast ? 4 : pick_hu(3, H, ctx->smem_optin, (size_t)BC * HS * 4);
   FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_gru_fwd: hidden size %d does not fit the step kernel's shared memory", H);
-  const size_t smem = fwd_smem(3, hu, H);
+  const size_t smem = fast ? fast_fwd_smem(3, H) : fwd_smem(3, hu, H);
   auto kern = hu == 4 ? gru_fwd_step_kernel<4> : hu == 2 ? gru_fwd_step_kernel<2> : gru_fwd_step_kernel<1>;
-  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (fast) FB_CUDA(cudaFuncSetAttribute(gru_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
   for (int64_t t = 0; t < T; ++t) {
     const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
     const int64_t ldh = t == 0 ? H : ldrow;
-    kern<<<grid, RT, smem, stream>>>(Wh, gx + t * 3 * H, T * 3 * H, hprev, ldh, out + t * H, ldrow,
-                                     cch ? cch + t * 4 * H : nullptr, T * 4 * H, (t == T - 1) ? hT : nullptr, H, B);
+    float* c_t = cch ? cch + t * 4 * H : nullptr;
+    float* hT_t = (t == T - 1) ? hT : nullptr;
+    if (fast)
+      gru_fwd_fast_kernel<<<grid, RT, smem, stream>>>(Wh, gx + t * 3 * H, T * 3 * H, hprev, ldh, out + t * H, ldrow, c_t, T * 4 * H,
+                                                      hT_t, H, B);
+    else
+      kern<<<grid, RT, smem, stream>>>(Wh, gx + t * 3 * H, T * 3 * H, hprev, ldh, out + t * H, ldrow, c_t, T * 4 * H, hT_t, H, B);
     FB_LAUNCH_CHECK();
   }
   return FB_OK;
@@ -520,31 +716,27 @@ FB_API int32_t fb_gru_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
   const float* cch = (const float*)cache;          // [rows][4H]
   float* dgx = (float*)cache + rows * 4 * H;       // [rows][3H], over the input projection
   float* dgh = dgx + rows * 3 * H;                 // [rows][3H]
-  float* ws = (float*)fb_scratch(ctx, stream, (size_t)(3 * (int64_t)B * H) * sizeof(float));
+  const int R = 3 * H;
+  const int nparts = (R + DH_R - 1) / DH_R;
+  float* ws = (float*)fb_scratch(ctx, stream, (size_t)((1 + nparts) * (int64_t)B * H) * sizeof(float));
   if (!ws) return FB_ERR_ALLOC;
-  float* dh_direct = ws;
-  float* dh_a = ws + (int64_t)B * H;
-  float* dh_b = dh_a + (int64_t)B * H;
-  const int hu = pick_hu(1, 3 * H, ctx->smem_optin, (size_t)BC * HS * 4);
-  FB_REQUIRE(hu > 0, FB_ERR_UNSUPPORTED, "fb_gru_bwd: hidden size %d does not fit the step kernel's shared memory", H);
-  const size_t smem = dh_smem(hu, 3 * H);
-  auto kern = hu == 4 ? rnn_bwd_dh_kernel<4> : hu == 2 ? rnn_bwd_dh_kernel<2> : rnn_bwd_dh_kernel<1>;
-  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const unsigned grid_dh = (unsigned)((H + hu - 1) / hu);
+  float* dh_direct = ws;                     // dh * z, the part of dh_{t-1} that bypasses Wh
+  float* parts = ws + (int64_t)B * H;        // [nparts][B][H] partial sums of Wh' * dgh
+  FB_CUDA(cudaFuncSetAttribute(rnn_bwd_dh2d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DH2D_SMEM));
+  const dim3 grid_dh((unsigned)((H + DH_U - 1) / DH_U), (unsigned)nparts, (unsigned)((B + BC - 1) / BC));
   int64_t eb = ((int64_t)B * H + RT - 1) / RT;
   if (eb > ctx->sm_count * 8) eb = ctx->sm_count * 8;
-  const float* dh_rec = dhT;
   for (int64_t t = T - 1; t >= 0; --t) {
     const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
-    gru_bwd_gates_kernel<<<(unsigned)eb, RT, 0, stream>>>(cch + t * 4 * H, T * 4 * H, hprev, t == 0 ? (int64_t)H : ldrow, dout + t * H, ldrow,
-                                                          dh_rec, dgx + t * 3 * H, dgh + t * 3 * H, T * 3 * H,
-                                                          dh_direct, H, B);
+    const bool last = (t == T - 1);
+    gru_bwd_gates_kernel<<<(unsigned)eb, RT, 0, stream>>>(cch + t * 4 * H, T * 4 * H, hprev, t == 0 ? (int64_t)H : ldrow,
+                                                          dout + t * H, ldrow, last ? dhT : parts, last ? 1 : nparts,
+                                                          last ? nullptr : dh_direct, dgx + t * 3 * H, dgh + t * 3 * H,
+                                                          T * 3 * H, dh_direct, H, B);
     FB_LAUNCH_CHECK();
     if (t > 0) {
-      float* dh_next = (dh_rec == dh_a) ? dh_b : dh_a;
-      kern<<<grid_dh, RT, smem, stream>>>(Wh, dgh + t * 3 * H, T * 3 * H, dh_direct, dh_next, H, 3 * H, B);
+      rnn_bwd_dh2d_kernel<<<grid_dh, RT, DH2D_SMEM, stream>>>(Wh, dgh + t * 3 * H, T * 3 * H, parts, H, R, B);
       FB_LAUNCH_CHECK();
-      dh_rec = dh_next;
     }
   }
   fb_gemm_args a;

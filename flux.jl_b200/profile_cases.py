@@ -7,10 +7,10 @@ Cases (each holds well under a few GB on the device; inputs exceed the 126 MB L2
     gemm_dw     the dW GEMM of the same layer (MN-major x MN-major, K = batch)
     gemm_dx     the dX GEMM of the same layer (K-major x K-major)
     layernorm   LayerNorm(4096) forward + backward on 4096 x 8192
-    batchnorm   BatchNorm(256, relu) training forward + backward on 32 x 32 x 256 x 64
+    batchnorm   BatchNorm(256, relu) training forward + backward on 32 x 32 x 256 x 128
     adam        Adam step over 32 Mi parameters in 4 leaves
     attention   causal attention forward + backward, E = 1024, 16 heads, S = 1024, B = 2
-    lstm        LSTM(512=>512) forward + backward, T = 16, B = 64
+    lstm        LSTM(512=>512) forward + backward, T = 32, B = 64
     xent        logitcrossentropy forward + backward, 1000 x 8192
 With --time the case is also timed with CUDA events (L2 flushed between iterations) and achieved GB/s or TFLOP/s
 against the algorithmic bytes / flops is printed.
@@ -73,7 +73,7 @@ def main():
             call("fb_layernorm_bwd", P(x), P(gam), P(bet), P(mean), P(rstd), P(dy), P(dx), P(dg), P(db), d, n, 0)
         work = (5.0 * d * n * 4, "GB/s")
     elif case == "batchnorm":
-        s, c, n = 1024, 256, 64
+        s, c, n = 1024, 256, 128
         x, dy, gam, bet = rn(s * c * n) * 2 + 0.5, rn(s * c * n), rn(c), rn(c)
         rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
         y, dx = torch.empty_like(x), torch.empty_like(x)
@@ -102,7 +102,7 @@ def main():
             call("fb_attn_bwd", P(q), P(k_), P(v_), None, P(o), P(lse), P(do), P(dq), P(dk), P(dv), E, E, S, S, B, H, 1)
         work = (3.5 * 0.5 * 4.0 * S * S * (E // H) * H * B, "TFLOP/s")
     elif case == "lstm":
-        I, Hd, T, B = 512, 512, 16, 64
+        I, Hd, T, B = 512, 512, 32, 64
         Wi, Wh, b, x = rn(4 * Hd * I) * 0.05, rn(4 * Hd * Hd) * 0.05, rn(4 * Hd) * 0.1, rn(I * T * B)
         out, hT, cT, dout = torch.empty(Hd * T * B, device="cuda"), torch.empty(Hd * B, device="cuda"), torch.empty(Hd * B, device="cuda"), rn(Hd * T * B)
         cache = torch.empty(lib.raw().fb_lstm_cache_bytes(I, Hd, T, B) // 4, device="cuda")
