@@ -10,11 +10,16 @@
 // cluster of two CTAs computes a 256 x 256 tile with cta_group::2 MMAs: each CTA loads and splits 128 rows of A
 // and 128 columns of B, the leader CTA issues one M = 256 MMA per k-step that reads both CTAs' shared memory,
 // and each CTA's tensor memory receives its own 128 rows.  K is walked in blocks of 16 floats through a ring of
-// 4-6 stages.  No TMA load is multicast.
+// 4-7 stages.  No TMA load is multicast.
+//
+// The kernel is persistent: one CTA (pair) per SM (pair of SMs) walks the tile grid with stride G, the stage ring
+// and the two accumulator buffers run on across tiles, so the epilogue of one tile overlaps the main loop of the
+// next and barrier / tensor-memory setup is paid once per launch.
 //
 // Warp roles: warp 0 issues TMA loads; warp 1 owns tensor memory and issues the MMAs; warps 2-5 are the
-// epilogue (one TMEM lane quadrant each); warps 6-13 are two groups of split warps that take alternate
-// k-blocks, so that the proxy fence each split ends with overlaps the next block's split.
+// epilogue (one TMEM lane quadrant each); the remaining warps are groups of four split warps (two groups for the
+// one-CTA tile, four for the pair) that take k-blocks in turn, so that the latency of one split (load, store,
+// proxy fence, arrive) overlaps the splits of the following blocks.
 //
 // Operands may be K-major (k contiguous) or MN-major (m / n contiguous) in global memory; the shared-memory
 // layouts are the canonical ones the MMA descriptors name: 64-byte swizzle for K-major tiles (8 rows x 64 B
@@ -37,7 +42,6 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;               // floats per k-block (64 bytes)
-constexpr int SPLIT_GROUPS = 2;      // groups of four split warps taking alternate k-blocks
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr int SEG_KB = 128;          // k-blocks per accumulation segment (2048 k-values)
 
@@ -191,8 +195,9 @@ __device__ __forceinline__ void tc_mma2_tf32(uint32_t d_tmem, uint64_t a_desc, u
 }
 
 
-template <int BN, int PASSES, bool PAIR>
+template <int BN, int PASSES, bool PAIR, int SG>
 struct Cfg {
+  static constexpr int SPLIT_GROUPS = SG;                   // groups of four split warps taking k-blocks in turn
   static_assert(!PAIR || PASSES == 3, "the two-CTA tile exists for the 3-pass scheme only");
   static constexpr int BNC = PAIR ? BN / 2 : BN;            // B columns this CTA loads per stage
   static constexpr int A_BYTES = BM * BK * 4;               // 8 KB
@@ -207,12 +212,14 @@ struct Cfg {
   static constexpr uint32_t ARRIVALS = PAIR ? 8 : 4;        // four warps per CTA arrive on ready / tmem_empty
 };
 
-template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR>
-__global__ void __launch_bounds__(Cfg<BN, PASSES, PAIR>::NUM_THREADS, 1)
+template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR, int SG>
+__global__ void __launch_bounds__(Cfg<BN, PASSES, PAIR, SG>::NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                float* __restrict__ C, int64_t ldc, float* __restrict__ Z, const float* __restrict__ bias_n, int M,
-               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int prefetch_kb, int a3d, int b3d) {
-  using cfg = Cfg<BN, PASSES, PAIR>;
+               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int prefetch_kb, int a3d, int b3d,
+               int num_tiles, int tiles_n) {
+  using cfg = Cfg<BN, PASSES, PAIR, SG>;
+  constexpr int SPLIT_GROUPS = SG;
   constexpr int STAGES = cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -232,12 +239,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
   const bool leader = (rank == 0);
-  // rows of A / C this CTA owns, columns of the tile, and the B columns this CTA loads
-  const int m0 = PAIR ? (int)(blockIdx.x >> 1) * 256 + 128 * (int)rank : (int)blockIdx.y * BM;
-  const int n0 = PAIR ? (int)blockIdx.y * BN : (int)blockIdx.x * BN;
-  const int nb0 = PAIR ? n0 + cfg::BNC * (int)rank : n0;
+  // Persistent schedule: CTA (pair) number cid of G takes tiles cid, cid + G, ... of the tiles_m x tiles_n grid,
+  // n fastest, so that the tiles in flight at any moment are neighbours and share operand panels in L2.
+  const int cid = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int G = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int my_tiles = cid < num_tiles ? (num_tiles - cid + G - 1) / G : 0;
   const int num_kb = (K + BK - 1) / BK;
   const int num_seg = (num_kb + SEG_KB - 1) / SEG_KB;
+  // rows of A / C this CTA owns in tile t, the tile's first column, and the first B column this CTA loads
+  auto tile_m0 = [&](int t) { return PAIR ? (t / tiles_n) * 256 + 128 * (int)rank : (t / tiles_n) * BM; };
+  auto tile_n0 = [&](int t) { return (t % tiles_n) * BN; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -293,6 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer ---
     if (lane == 0) {
+      int m0 = 0, nb0 = 0;
       auto prefetch = [&](int kbp) {
         const int kp = kbp * BK;
         if (A_MN) {
@@ -308,35 +320,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tma_prefetch_2d(&tmB, kp, nb0);
         }
       };
-      for (int kb = 0; kb < prefetch_kb && kb < num_kb; ++kb) prefetch(kb);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (prefetch_kb > 0 && kb + prefetch_kb < num_kb) prefetch(kb + prefetch_kb);
-        if (!mbar_wait_cluster(empty_bar(s), ph ^ 1u, s_abort)) break;
-        mbar_arrive_expect_tx(full_bar(s), (uint32_t)(cfg::A_BYTES + cfg::B_BYTES));
-        const uint32_t a_dst = smem_base + (uint32_t)(s * cfg::STAGE_BYTES);
-        const uint32_t b_dst = a_dst + (uint32_t)((PASSES == 3 ? 2 : 1) * cfg::A_BYTES);
-        const int k0 = kb * BK;
-        if (A_MN) {
-          if (a3d) {
-            tma_load_3d(a_dst, &tmA, 0, k0, m0 >> 5, full_bar(s));
-          } else {
+      int it = 0;   // k-blocks issued so far over all tiles: names the stage and its phase
+      bool ok = true;
+      for (int t = cid; t < num_tiles && ok; t += G) {
+        m0 = tile_m0(t);
+        nb0 = tile_n0(t) + (PAIR ? cfg::BNC * (int)rank : 0);
+        for (int kb = 0; kb < prefetch_kb && kb < num_kb; ++kb) prefetch(kb);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+          if (prefetch_kb > 0 && kb + prefetch_kb < num_kb) prefetch(kb + prefetch_kb);
+          ok = mbar_wait_cluster(empty_bar(s), ph ^ 1u, s_abort);
+          if (!ok) break;
+          mbar_arrive_expect_tx(full_bar(s), (uint32_t)(cfg::A_BYTES + cfg::B_BYTES));
+          const uint32_t a_dst = smem_base + (uint32_t)(s * cfg::STAGE_BYTES);
+          const uint32_t b_dst = a_dst + (uint32_t)((PASSES == 3 ? 2 : 1) * cfg::A_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN) {
+            if (a3d) {
+              tma_load_3d(a_dst, &tmA, 0, k0, m0 >> 5, full_bar(s));
+            } else {
 #pragma unroll
-            for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + (uint32_t)(c * BK * 128), &tmA, m0 + 32 * c, k0, full_bar(s));
-          }
-        } else {
-          tma_load_2d(a_dst, &tmA, k0, m0, full_bar(s));
-        }
-        if (B_MN) {
-          if (b3d) {
-            tma_load_3d(b_dst, &tmB, 0, k0, nb0 >> 5, full_bar(s));
+              for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + (uint32_t)(c * BK * 128), &tmA, m0 + 32 * c, k0, full_bar(s));
+            }
           } else {
-#pragma unroll
-            for (int c = 0; c < cfg::BNC / 32; ++c) tma_load_2d(b_dst + (uint32_t)(c * BK * 128), &tmB, nb0 + 32 * c, k0, full_bar(s));
+            tma_load_2d(a_dst, &tmA, k0, m0, full_bar(s));
           }
-        } else {
-          tma_load_2d(b_dst, &tmB, k0, nb0, full_bar(s));
+          if (B_MN) {
+            if (b3d) {
+              tma_load_3d(b_dst, &tmB, 0, k0, nb0 >> 5, full_bar(s));
+            } else {
+#pragma unroll
+              for (int c = 0; c < cfg::BNC / 32; ++c) tma_load_2d(b_dst + (uint32_t)(c * BK * 128), &tmB, nb0 + 32 * c, k0, full_bar(s));
+            }
+          } else {
+            tma_load_2d(b_dst, &tmB, k0, nb0, full_bar(s));
+          }
         }
       }
     }
@@ -347,11 +366,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((PAIR ? 256 : BM) >> 4) << 24);
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        const int seg = kb / SEG_KB, kb_in_seg = kb % SEG_KB;
-        const int buf = seg & 1, use = seg >> 1;
+      int it = 0, sc = 0;   // k-blocks and accumulation segments issued so far over all tiles
+      for (int t = 0; t < my_tiles && ok; ++t)
+      for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        const int kb_in_seg = kb % SEG_KB;
+        const int buf = sc & 1, use = sc >> 1;
         if (kb_in_seg == 0 && use > 0) {
           // the epilogue warps must have drained this accumulator buffer's previous segment
           ok = mbar_wait_cluster(tmem_empty_bar(buf), (uint32_t)(use - 1) & 1u, s_abort);
@@ -401,17 +422,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_commit(empty_bar(s));
           if (seg_end) tc_commit(tmem_full_bar(buf));
         }
+        if (seg_end) ++sc;
       }
     }
   } else if (warp < 6) {
     // -------------------------------------------------------------- epilogue warps ---
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int row = m0 + 32 * q + lane;
+    bool ok = true;
+    int sc = 0;                             // segments drained so far over all tiles
+    for (int t = cid; t < num_tiles && ok; t += G) {
+    const int n0 = tile_n0(t);
+    const int row = tile_m0(t) + 32 * q + lane;
     float* crow = C + (int64_t)row * ldc;
     float* zrow = Z ? Z + (int64_t)row * ldc : nullptr;
-    bool ok = true;
-    for (int seg = 0; seg < num_seg && ok; ++seg) {
-      const int buf = seg & 1, use = seg >> 1;
+    for (int seg = 0; seg < num_seg && ok; ++seg, ++sc) {
+      const int buf = sc & 1, use = sc >> 1;
       ok = mbar_wait_cluster(tmem_full_bar(buf), (uint32_t)use & 1u, s_abort);
       if (!ok) break;
       tc_fence_after();
@@ -464,22 +489,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
-      if (!last) {
-        // this buffer may be overwritten once every epilogue warp (of both CTAs) has read its quadrant
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (PAIR) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0u));
-          else mbar_arrive(tmem_empty_bar(buf));
-        }
+      // this buffer may be overwritten once every epilogue warp (of both CTAs) has read its quadrant
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0u));
+        else mbar_arrive(tmem_empty_bar(buf));
       }
+    }
     }
   } else {
     // ------------------------------------------- split warps: write lo = x - trunc_tf32(x) ---
     const int group = (warp - 6) >> 2;
     const int tt = ((warp - 6) & 3) * 32 + lane;   // 0..127 inside the group
     bool ok = true;
-    for (int kb = group; kb < num_kb && ok; kb += SPLIT_GROUPS) {
+    const int total_kb = my_tiles * num_kb;   // the stage ring runs on across tiles
+    for (int kb = group; kb < total_kb && ok; kb += SPLIT_GROUPS) {
       const int s = kb % STAGES;
       const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
       ok = mbar_wait(full_bar(s), ph, s_abort);
@@ -587,9 +612,9 @@ bool encode_map_mn3d(CUtensorMap* map, const float* base, int64_t K, int64_t MN,
   return r == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR>
+template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR, int SG>
 int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
-  using cfg = Cfg<BN, PASSES, PAIR>;
+  using cfg = Cfg<BN, PASSES, PAIR, SG>;
   CUtensorMap tmA, tmB;
   bool ok;
   int a3d = 0, b3d = 0;
@@ -609,12 +634,19 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   }
   if (!ok) return fb_fail(FB_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed (M=%lld N=%lld K=%lld lda=%lld ldb=%lld)",
                           (long long)a.M, (long long)a.N, (long long)a.K, (long long)a.lda, (long long)a.ldb);
-  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, PASSES, PAIR>;
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, PASSES, PAIR, SG>;
   FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+  const int tiles_n = (int)((a.N + BN - 1) / BN);
+  const int64_t tiles_m = PAIR ? (a.M + 255) / 256 : (a.M + BM - 1) / BM;
+  const int64_t num_tiles = tiles_m * tiles_n;
+  if (num_tiles > 0x7fffffff) return fb_fail(FB_ERR_UNSUPPORTED, "gemm: too many tiles");
+  // one CTA (pair) per SM (pair of SMs), each walking the tile grid with stride G
+  int64_t G = PAIR ? ctx->sm_count / 2 : ctx->sm_count;
+  if (G < 1) G = 1;
+  if (G > num_tiles) G = num_tiles;
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
-  if (PAIR) lc.gridDim = dim3((unsigned)(2 * ((a.M + 255) / 256)), (unsigned)((a.N + BN - 1) / BN), 1);
-  else lc.gridDim = dim3((unsigned)((a.N + BN - 1) / BN), (unsigned)((a.M + BM - 1) / BM), 1);
+  lc.gridDim = dim3((unsigned)(PAIR ? 2 * G : G), 1, 1);
   lc.blockDim = dim3(cfg::NUM_THREADS, 1, 1);
   lc.dynamicSmemBytes = cfg::SMEM_BYTES;
   lc.stream = stream;
@@ -626,29 +658,37 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   lc.attrs = attr;
   lc.numAttrs = 1;
   FB_CUDA(cudaLaunchKernelEx(&lc, kern, tmA, tmB, a.C, a.ldc, a.Z, a.bias_n, (int)a.M, (int)a.N, (int)a.K, a.act,
-                             a.accumulate, ctx->dev_error, prefetch_from_env(), a3d, b3d));
+                             a.accumulate, ctx->dev_error, prefetch_from_env(), a3d, b3d, (int)num_tiles, tiles_n));
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
 
-template <int BN, int PASSES, bool PAIR>
-int32_t launch_layout(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
+template <int BN, int PASSES, bool PAIR, int SG>
+int32_t launch_layout_sg(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
   if (a.a_mn_major) {
-    if (a.b_mn_major) return launch_variant<true, true, BN, PASSES, PAIR>(ctx, stream, a);
-    return launch_variant<true, false, BN, PASSES, PAIR>(ctx, stream, a);
+    if (a.b_mn_major) return launch_variant<true, true, BN, PASSES, PAIR, SG>(ctx, stream, a);
+    return launch_variant<true, false, BN, PASSES, PAIR, SG>(ctx, stream, a);
   }
-  if (a.b_mn_major) return launch_variant<false, true, BN, PASSES, PAIR>(ctx, stream, a);
-  return launch_variant<false, false, BN, PASSES, PAIR>(ctx, stream, a);
+  if (a.b_mn_major) return launch_variant<false, true, BN, PASSES, PAIR, SG>(ctx, stream, a);
+  return launch_variant<false, false, BN, PASSES, PAIR, SG>(ctx, stream, a);
 }
 
-// FLUXB200_PAIR = 1 selects the two-CTA 256 x 256 tiles for large problems.  Measured on B200 the one-CTA tile is
-// the faster of the two (it is bound by shared-memory bandwidth at ~56 % tensor-pipe activity, the pair by the
-// latency of its cross-CTA barrier chain at ~50 %), so the pair is opt-in.
+// Split-warp groups: the one-CTA tile is bound by shared-memory bandwidth and gains nothing beyond two groups; the
+// two-CTA tile is bound by the latency of one split (wait, load, store, proxy fence, remote arrive) and keeps
+// gaining up to four (measured 157 -> 175 -> 182 TFLOP/s for 2 -> 3 -> 4 groups at 4096^3).
+template <int BN, int PASSES, bool PAIR>
+int32_t launch_layout(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
+  return launch_layout_sg<BN, PASSES, PAIR, (PAIR ? 4 : 2)>(ctx, stream, a);
+}
+
+// FLUXB200_PAIR = 0 keeps every problem on one-CTA tiles.  Measured on B200 (4096^3, 3xTF32, persistent kernels):
+// one-CTA 128 x 256 tiles 200-213 TFLOP/s (shared-memory bandwidth bound: every MMA re-reads all 256 B columns),
+// two-CTA 256 x 256 tiles 215-232 TFLOP/s (each CTA reads only its 128 B columns).
 bool pair_kernel_enabled() {
   static int on = -1;
   if (on < 0) {
     const char* e = getenv("FLUXB200_PAIR");
-    on = (e != nullptr && e[0] == '1') ? 1 : 0;
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
   return on != 0;
 }
@@ -658,7 +698,6 @@ bool pair_kernel_enabled() {
 bool fb_gemm_tc_supported(const fb_gemm_args& a) {
   if (a.M < 1 || a.N < 1 || a.K < 1) return false;
   if (a.M > 0x7fffff00 || a.N > 0x7fffff00 || a.K > 0x7fffff00) return false;
-  if ((a.M + BM - 1) / BM > 65535) return false;
   if (a.bias_m != nullptr) return false;
   if (!fb_aligned16(a.A) || !fb_aligned16(a.B) || !fb_aligned16(a.C)) return false;
   if (a.Z && !fb_aligned16(a.Z)) return false;
@@ -679,9 +718,9 @@ int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& 
   const int64_t tiles256 = ((a.M + BM - 1) / BM) * ((a.N + 255) / 256);
   const bool narrow = (a.N <= 128) || (2 * tiles256 <= ctx->sm_count);
   if (passes == 3) {
-    // two-CTA 256 x 256 tiles when the problem fills the machine with them
-    if ((passes_flag_pair || pair_kernel_enabled()) && a.M >= 256 && a.N >= 256 && (a.N + 255) / 256 <= 65535 &&
-        (passes_flag_pair || 2 * ((a.M + 255) / 256) * ((a.N + 255) / 256) >= ctx->sm_count))
+    // two-CTA 256 x 256 tiles once there are enough of them to occupy a good part of the SM pairs
+    const int64_t pair_tiles = ((a.M + 255) / 256) * ((a.N + 255) / 256);
+    if (a.M >= 256 && a.N >= 256 && (passes_flag_pair || (pair_kernel_enabled() && 4 * pair_tiles >= ctx->sm_count)))
       return launch_layout<256, 3, true>(ctx, stream, a);
     if (narrow) return launch_layout<128, 3, false>(ctx, stream, a);
     return launch_layout<256, 3, false>(ctx, stream, a);
