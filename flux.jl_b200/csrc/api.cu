@@ -59,6 +59,12 @@ FB_API int32_t fb_ctx_create(int32_t device, fb_ctx** out) {
     return fb_fail(FB_ERR_ALLOC, "fb_ctx_create: cudaMalloc failed: %s", cudaGetErrorString(e));
   }
   cudaMemset(c->dev_error, 0, 256);
+  const int32_t ws_status = fb_gemm_workspace_create(c);
+  if (ws_status != FB_OK) {
+    cudaFree(c->dev_error);
+    delete c;
+    return ws_status;
+  }
   *out = c;
   return FB_OK;
 }
@@ -163,6 +169,10 @@ FB_API int32_t fb_device_error(fb_ctx* ctx, void* stream, int32_t* out_host) {
   FB_REQUIRE(out_host, FB_ERR_INVALID_ARG, "fb_device_error: out is NULL");
   FB_CUDA(cudaMemcpyAsync(out_host, ctx->dev_error, sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   FB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-  if (*out_host != 0) FB_CUDA(cudaMemsetAsync(ctx->dev_error, 0, sizeof(int32_t), (cudaStream_t)stream));
+  if (*out_host != 0) {
+    // a kernel that gave up may have left GEMM tickets drawn: start the next launch from a clean state
+    fb_gemm_workspace_reset(ctx, (cudaStream_t)stream);
+    FB_CUDA(cudaMemsetAsync(ctx->dev_error, 0, sizeof(int32_t), (cudaStream_t)stream));
+  }
   return FB_OK;
 }

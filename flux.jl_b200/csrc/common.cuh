@@ -22,7 +22,7 @@ struct fb_ctx {
   void* retired[FB_MAX_RETIRED];   // outgrown arena blocks, released with the context
   int retired_count;
   int32_t* dev_error;    // device error word written by kernels whose bounded waits ran out
-  void* tmap_cache;      // opaque (gemm_tc.cu): encoded TMA descriptors keyed by (ptr, shape)
+  void* tmap_cache;      // opaque (gemm_tc.cu): workspace of the split-tile GEMM schedule
 };
 
 // thread-local last-error message
@@ -183,6 +183,8 @@ int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& 
 bool fb_gemm_tc_supported(const fb_gemm_args& a);
 int32_t fb_gemm_dispatch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a, int precision);
 void fb_tmap_cache_destroy(fb_ctx* ctx);
+int32_t fb_gemm_workspace_create(fb_ctx* ctx);
+void fb_gemm_workspace_reset(fb_ctx* ctx, cudaStream_t stream);
 
 // delta = dy .* act'(.) and db[j] = sum_rows delta[row][j]   (rows x cols row-major; cols = out_dim)
 int32_t fb_act_bwd_colsum(fb_ctx* ctx, cudaStream_t stream, int act, const float* dy, const float* y,

@@ -195,6 +195,55 @@ __device__ __forceinline__ void tc_mma2_tf32(uint32_t d_tmem, uint64_t a_desc, u
 }
 
 
+// Work schedule of one launch.  Tiles [0, dp_tiles) are taken whole: CTA (pair) cid of G takes cid, cid + G, ...
+// (n fastest, so the tiles in flight are neighbours and share operand panels in L2).  The remaining tiles - a
+// last wave that would leave most SMs idle - are cut along K into units of UNIT_KB k-blocks; the U units are
+// dealt out as G contiguous ranges, so a tile may be computed by several CTAs ("parts").  Each part writes its
+// partial sums to a workspace slot; the part that finishes last (an atomic ticket per tile, no waiting) adds the
+// slots in k order and applies the epilogue.
+constexpr int UNIT_KB = 32;
+struct Sched {
+  int num_tiles, tiles_n, dp_tiles;
+  int nu;            // units per tile
+  int U;             // units in the tail: (num_tiles - dp_tiles) * nu
+  float* ws;         // [2 * G * ranks] slots of BM x 256 floats
+  int* tickets;      // [G * ranks * 4], zero between launches
+};
+struct Portion {
+  int tile, kb0, kb1;
+  int partial;       // 0: the whole tile, results go to C
+  int tail_tile;     // index of the tile inside the tail (partial only)
+  int trail;         // 1 when this CTA's range began before the tile's first unit (names the slot)
+};
+struct WorkIter {
+  int w, ta, tb, t0;
+  __device__ WorkIter(const Sched& s, int cid, int G) : w(0) {
+    ta = t0 = (int)((long long)cid * s.U / G);
+    tb = (int)((long long)(cid + 1) * s.U / G);
+  }
+  __device__ bool next(const Sched& s, int cid, int G, int num_kb, Portion& p) {
+    if (w * G + cid < s.dp_tiles) {
+      p.tile = w * G + cid; p.kb0 = 0; p.kb1 = num_kb; p.partial = 0; p.tail_tile = 0; p.trail = 0;
+      ++w;
+      return true;
+    }
+    if (ta < tb) {
+      const int tr = ta / s.nu, ua = ta % s.nu;
+      const int rem = tb - ta;
+      const int ub = (ua + rem < s.nu) ? ua + rem : s.nu;
+      p.tile = s.dp_tiles + tr;
+      p.kb0 = ua * UNIT_KB;
+      p.kb1 = (ub == s.nu) ? num_kb : ub * UNIT_KB;
+      p.partial = (ua == 0 && ub == s.nu) ? 0 : 1;
+      p.tail_tile = tr;
+      p.trail = (t0 < tr * s.nu) ? 1 : 0;
+      ta += ub - ua;
+      return true;
+    }
+    return false;
+  }
+};
+
 template <int BN, int PASSES, bool PAIR, int SG>
 struct Cfg {
   static constexpr int SPLIT_GROUPS = SG;                   // groups of four split warps taking k-blocks in turn
@@ -217,7 +266,7 @@ __global__ void __launch_bounds__(Cfg<BN, PASSES, PAIR, SG>::NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                float* __restrict__ C, int64_t ldc, float* __restrict__ Z, const float* __restrict__ bias_n, int M,
                int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int prefetch_kb, int a3d, int b3d,
-               int num_tiles, int tiles_n) {
+               const Sched sch) {
   using cfg = Cfg<BN, PASSES, PAIR, SG>;
   constexpr int SPLIT_GROUPS = SG;
   constexpr int STAGES = cfg::STAGES;
@@ -239,13 +288,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
   const bool leader = (rank == 0);
-  // Persistent schedule: CTA (pair) number cid of G takes tiles cid, cid + G, ... of the tiles_m x tiles_n grid,
-  // n fastest, so that the tiles in flight at any moment are neighbours and share operand panels in L2.
   const int cid = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int G = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-  const int my_tiles = cid < num_tiles ? (num_tiles - cid + G - 1) / G : 0;
+  const int tiles_n = sch.tiles_n;
   const int num_kb = (K + BK - 1) / BK;
-  const int num_seg = (num_kb + SEG_KB - 1) / SEG_KB;
   // rows of A / C this CTA owns in tile t, the tile's first column, and the first B column this CTA loads
   auto tile_m0 = [&](int t) { return PAIR ? (t / tiles_n) * 256 + 128 * (int)rank : (t / tiles_n) * BM; };
   auto tile_n0 = [&](int t) { return (t % tiles_n) * BN; };
@@ -322,14 +368,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       };
       int it = 0;   // k-blocks issued so far over all tiles: names the stage and its phase
       bool ok = true;
-      for (int t = cid; t < num_tiles && ok; t += G) {
-        m0 = tile_m0(t);
-        nb0 = tile_n0(t) + (PAIR ? cfg::BNC * (int)rank : 0);
-        for (int kb = 0; kb < prefetch_kb && kb < num_kb; ++kb) prefetch(kb);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      WorkIter wi(sch, cid, G);
+      Portion p;
+      while (ok && wi.next(sch, cid, G, num_kb, p)) {
+        m0 = tile_m0(p.tile);
+        nb0 = tile_n0(p.tile) + (PAIR ? cfg::BNC * (int)rank : 0);
+        for (int kb = p.kb0; kb < p.kb0 + prefetch_kb && kb < p.kb1; ++kb) prefetch(kb);
+        for (int kb = p.kb0; kb < p.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-          if (prefetch_kb > 0 && kb + prefetch_kb < num_kb) prefetch(kb + prefetch_kb);
+          if (prefetch_kb > 0 && kb + prefetch_kb < p.kb1) prefetch(kb + prefetch_kb);
           ok = mbar_wait_cluster(empty_bar(s), ph ^ 1u, s_abort);
           if (!ok) break;
           mbar_arrive_expect_tx(full_bar(s), (uint32_t)(cfg::A_BYTES + cfg::B_BYTES));
@@ -367,11 +415,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((PAIR ? 256 : BM) >> 4) << 24);
       bool ok = true;
       int it = 0, sc = 0;   // k-blocks and accumulation segments issued so far over all tiles
-      for (int t = 0; t < my_tiles && ok; ++t)
-      for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+      WorkIter wi(sch, cid, G);
+      Portion p;
+      while (ok && wi.next(sch, cid, G, num_kb, p))
+      for (int kb = p.kb0; kb < p.kb1 && ok; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-        const int kb_in_seg = kb % SEG_KB;
+        const int kb_in_seg = (kb - p.kb0) % SEG_KB;
         const int buf = sc & 1, use = sc >> 1;
         if (kb_in_seg == 0 && use > 0) {
           // the epilogue warps must have drained this accumulator buffer's previous segment
@@ -414,7 +464,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_mma_tf32(d_tmem, da_hi, db_hi, idesc, first);
           }
         }
-        const bool seg_end = (kb_in_seg == SEG_KB - 1 || kb == num_kb - 1);
+        const bool seg_end = (kb_in_seg == SEG_KB - 1 || kb == p.kb1 - 1);
         if (PAIR) {
           tc_commit2_mc(empty_bar(s), (uint16_t)3);                 // frees the stage in both CTAs
           if (seg_end) tc_commit2_mc(tmem_full_bar(buf), (uint16_t)3);
@@ -428,82 +478,202 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp < 6) {
     // -------------------------------------------------------------- epilogue warps ---
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    constexpr int RANKS = PAIR ? 2 : 1;
     bool ok = true;
     int sc = 0;                             // segments drained so far over all tiles
-    for (int t = cid; t < num_tiles && ok; t += G) {
-    const int n0 = tile_n0(t);
-    const int row = tile_m0(t) + 32 * q + lane;
-    float* crow = C + (int64_t)row * ldc;
-    float* zrow = Z ? Z + (int64_t)row * ldc : nullptr;
-    for (int seg = 0; seg < num_seg && ok; ++seg, ++sc) {
-      const int buf = sc & 1, use = sc >> 1;
-      ok = mbar_wait_cluster(tmem_full_bar(buf), (uint32_t)use & 1u, s_abort);
-      if (!ok) break;
-      tc_fence_after();
-      // intermediate segments add into C (round-to-nearest fp32 adds); the last one also applies bias,
-      // pre-activation store and activation
-      const bool last = (seg == num_seg - 1);
-      const bool add_c = (seg > 0) || (accumulate != 0);
+    WorkIter wi(sch, cid, G);
+    Portion p;
+    while (ok && wi.next(sch, cid, G, num_kb, p)) {
+      const int n0 = tile_n0(p.tile);
+      const int row = tile_m0(p.tile) + 32 * q + lane;
+      float* crow = C + (int64_t)row * ldc;
+      float* zrow = Z ? Z + (int64_t)row * ldc : nullptr;
+      // u: 4 consecutive columns starting at n of this lane's row.  add_c: add what C holds; fin: this is the
+      // tile's final value, so bias, pre-activation store and activation apply.
+      auto emit4 = [&](float* u, int n, bool add_c, bool fin) {
+        if (row >= M) return;
+        if (n + 3 < N) {
+          if (add_c) {
+            const float4 c4 = *(const float4*)(crow + n);
+            u[0] += c4.x; u[1] += c4.y; u[2] += c4.z; u[3] += c4.w;
+          }
+          if (fin) {
+            if (bias_n) {
+              const float4 b4 = __ldg((const float4*)(bias_n + n));
+              u[0] += b4.x; u[1] += b4.y; u[2] += b4.z; u[3] += b4.w;
+            }
+            if (zrow) *(float4*)(zrow + n) = make_float4(u[0], u[1], u[2], u[3]);
+            if (act != FB_ACT_IDENTITY) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) u[e] = fb_act_apply(act, u[e]);
+            }
+          }
+          *(float4*)(crow + n) = make_float4(u[0], u[1], u[2], u[3]);
+        } else {
+          for (int e = 0; e < 4 && n + e < N; ++e) {
+            float x = u[e];
+            if (add_c) x += crow[n + e];
+            if (fin) {
+              if (bias_n) x += __ldg(bias_n + n + e);
+              if (zrow) zrow[n + e] = x;
+              x = fb_act_apply(act, x);
+            }
+            crow[n + e] = x;
+          }
+        }
+      };
+      // A part of a split tile collects its sums in a workspace slot (always 256 floats per row).  The parts of
+      // a tile are the CTAs c_first .. c_last whose unit ranges meet it (those with an empty range excepted).
+      float* srow = nullptr;
+      int c_first = 0, c_last = 0, nparts = 0, rem_first = 0, r_first = 0, u_lo = 0;
+      int* ticket = nullptr;
+      const int row_off = (32 * q + lane) * 256;
+      const int step_q = sch.U / G, step_r = sch.U % G;
+      if (p.partial) {
+        srow = sch.ws + (size_t)((2 * cid + p.trail) * RANKS + (int)rank) * BM * 256 + row_off;
+        u_lo = p.tail_tile * sch.nu;
+        const int u_hi = u_lo + sch.nu - 1;
+        c_first = (int)(((long long)(u_lo + 1) * G - 1) / sch.U);
+        c_last = (int)(((long long)(u_hi + 1) * G - 1) / sch.U);
+        ticket = sch.tickets + (c_first * RANKS + (int)rank) * 4 + q;
+        // r(pc) = floor(pc * U / G), the first unit of CTA pc, is stepped from c_first on without dividing
+        r_first = (int)((long long)c_first * sch.U / G);
+        rem_first = (int)((long long)c_first * sch.U % G);
+        int r0 = r_first;
+        int rem = rem_first;
+        for (int pc = c_first; pc <= c_last; ++pc) {
+          int r1 = r0 + step_q;
+          int rem1 = rem + step_r;
+          if (rem1 >= G) { rem1 -= G; ++r1; }
+          nparts += (r1 > r0) ? 1 : 0;
+          r0 = r1;
+          rem = rem1;
+        }
+      }
+      // v[0 .. 4 * NV) += columns [col, col + 4 * NV) of this lane's row summed over parts pc_from .. c_last, in order
+      auto add_parts = [&](float* v, int col, int pc_from) {
+        int r0 = r_first;
+        int rem = rem_first;
+        for (int pc = c_first; pc <= c_last; ++pc) {
+          int r1 = r0 + step_q;
+          int rem1 = rem + step_r;
+          if (rem1 >= G) { rem1 -= G; ++r1; }
+          if (r1 > r0 && pc >= pc_from) {
+            const int tr = (r0 < u_lo) ? 1 : 0;
+            const float4* prow =
+                (const float4*)(sch.ws + (size_t)((2 * pc + tr) * RANKS + (int)rank) * BM * 256 + row_off + col);
+            float4 x[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = __ldcg(prow + j);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              v[4 * j] += x[j].x; v[4 * j + 1] += x[j].y; v[4 * j + 2] += x[j].z; v[4 * j + 3] += x[j].w;
+            }
+          }
+          r0 = r1;
+          rem = rem1;
+        }
+      };
+      const int nseg = (p.kb1 - p.kb0 + SEG_KB - 1) / SEG_KB;
+      bool fused = false;
+      for (int seg = 0; seg < nseg && ok; ++seg, ++sc) {
+        const int buf = sc & 1, use = sc >> 1;
+        ok = mbar_wait_cluster(tmem_full_bar(buf), (uint32_t)use & 1u, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        // later segments add into what the earlier ones left (round-to-nearest fp32 adds)
+        const bool last = (seg == nseg - 1);
+        if (p.partial && last && cid == c_first) {
+          // The first part of a tile usually finishes last (it is the end of its CTA's range, the other parts are
+          // the beginning of theirs).  When every other part has already drawn its ticket, their slots are
+          // complete: add them to this last segment on its way out and write C directly.
+          int seen = 0;
+          if (lane == 0) seen = *(volatile int*)ticket;
+          seen = __shfl_sync(0xffffffffu, seen, 0);
+          fused = (seen == nparts - 1);
+          if (fused) __threadfence();
+        }
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        const int nb = n0 + cc * 32;
-        if (nb >= N) break;   // warp-uniform
-        uint32_t r[32];
-        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * BN + cc * 32), r);
-        tc_wait_ld();
-        if (row < M) {
+        for (int cc = 0; cc < BN / 32; ++cc) {
+          const int nb = n0 + cc * 32;
+          if (nb >= N) break;   // warp-uniform
+          uint32_t r[32];
+          tc_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * BN + cc * 32), r);
+          tc_wait_ld();
+          float* v = reinterpret_cast<float*>(r);
+          if (!p.partial) {
+            const bool add_c = (seg > 0) || (accumulate != 0);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int n = nb + 4 * j;
-            float v[4] = {__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                          __uint_as_float(r[4 * j + 3])};
-            if (n + 3 < N) {
-              if (add_c) {
-                const float4 c4 = *(const float4*)(crow + n);
-                v[0] += c4.x; v[1] += c4.y; v[2] += c4.z; v[3] += c4.w;
-              }
-              if (last) {
-                if (bias_n) {
-                  const float4 b4 = __ldg((const float4*)(bias_n + n));
-                  v[0] += b4.x; v[1] += b4.y; v[2] += b4.z; v[3] += b4.w;
-                }
-                if (zrow) *(float4*)(zrow + n) = make_float4(v[0], v[1], v[2], v[3]);
-                if (act != FB_ACT_IDENTITY) {
+            for (int j = 0; j < 8; ++j) emit4(v + 4 * j, nb + 4 * j, add_c, last);
+          } else {
+            float4* s4 = (float4*)(srow + cc * 32);
+            if (seg > 0) {
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) v[e] = fb_act_apply(act, v[e]);
-                }
+              for (int j = 0; j < 8; ++j) {
+                const float4 o = s4[j];
+                v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
               }
-              *(float4*)(crow + n) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+            if (last && fused) {
+              add_parts(v, cc * 32, c_first + 1);
+              add_parts(v + 16, cc * 32 + 16, c_first + 1);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) emit4(v + 4 * j, nb + 4 * j, accumulate != 0, true);
             } else {
-              for (int e = 0; e < 4 && n + e < N; ++e) {
-                float u = v[e];
-                if (add_c) u += crow[n + e];
-                if (last) {
-                  if (bias_n) u += __ldg(bias_n + n + e);
-                  if (zrow) zrow[n + e] = u;
-                  u = fb_act_apply(act, u);
-                }
-                crow[n + e] = u;
-              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) s4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
           }
         }
+        // this buffer may be overwritten once every epilogue warp (of both CTAs) has read its quadrant
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0u));
+          else mbar_arrive(tmem_empty_bar(buf));
+        }
       }
-      // this buffer may be overwritten once every epilogue warp (of both CTAs) has read its quadrant
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (PAIR) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0u));
-        else mbar_arrive(tmem_empty_bar(buf));
+      if (p.partial && ok) {
+        if (fused) {
+          __syncwarp();
+          if (lane == 0) *ticket = 0;   // every part is accounted for: ready for the next launch
+        } else {
+          // whoever draws the last ticket adds the slots up, in k order (the same sums as the fused path makes)
+          __threadfence();
+          __syncwarp();
+          int drawn = 0;
+          if (lane == 0) drawn = atomicAdd(ticket, 1);
+          drawn = __shfl_sync(0xffffffffu, drawn, 0);
+          if (drawn == nparts - 1) {
+            __threadfence();
+#pragma unroll 1
+            for (int hc = 0; hc < BN / 16; ++hc) {
+              const int nb = n0 + hc * 16;
+              if (nb >= N) break;
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+              add_parts(v, hc * 16, c_first);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) emit4(v + 4 * j, nb + 4 * j, accumulate != 0, true);
+            }
+            __syncwarp();
+            if (lane == 0) *ticket = 0;   // ready for the next launch
+          }
+        }
       }
-    }
     }
   } else {
     // ------------------------------------------- split warps: write lo = x - trunc_tf32(x) ---
     const int group = (warp - 6) >> 2;
     const int tt = ((warp - 6) & 3) * 32 + lane;   // 0..127 inside the group
     bool ok = true;
-    const int total_kb = my_tiles * num_kb;   // the stage ring runs on across tiles
+    int total_kb = 0;   // the stage ring runs on across tiles
+    {
+      WorkIter wi(sch, cid, G);
+      Portion p;
+      while (wi.next(sch, cid, G, num_kb, p)) total_kb += p.kb1 - p.kb0;
+    }
     for (int kb = group; kb < total_kb && ok; kb += SPLIT_GROUPS) {
       const int s = kb % STAGES;
       const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
@@ -598,6 +768,22 @@ int prefetch_from_env() {
   return n;
 }
 
+// Workspace of the split-tile schedule, owned by the context: slots for partial sums and the tickets.
+struct GemmWorkspace {
+  float* ws;
+  int* tickets;
+};
+
+// FLUXB200_STREAMK = 0 keeps every tile whole.
+bool stream_k_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUXB200_STREAMK");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
 // 3-d view {32, K, MN / 32} of an MN-major matrix (row k holds MN contiguous floats): box {32, BK, chunks}.
 // Only for MN a multiple of 32, so that no chunk straddles the end of a row.
 bool encode_map_mn3d(CUtensorMap* map, const float* base, int64_t K, int64_t MN, int64_t ld, uint32_t chunks) {
@@ -640,10 +826,29 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   const int64_t tiles_m = PAIR ? (a.M + 255) / 256 : (a.M + BM - 1) / BM;
   const int64_t num_tiles = tiles_m * tiles_n;
   if (num_tiles > 0x7fffffff) return fb_fail(FB_ERR_UNSUPPORTED, "gemm: too many tiles");
-  // one CTA (pair) per SM (pair of SMs), each walking the tile grid with stride G
-  int64_t G = PAIR ? ctx->sm_count / 2 : ctx->sm_count;
-  if (G < 1) G = 1;
-  if (G > num_tiles) G = num_tiles;
+  // one CTA (pair) per SM (pair of SMs)
+  const int64_t Gmax = PAIR ? (ctx->sm_count / 2 > 0 ? ctx->sm_count / 2 : 1) : ctx->sm_count;
+  const int num_kb = (int)((a.K + BK - 1) / BK);
+  Sched sch;
+  sch.num_tiles = (int)num_tiles;
+  sch.tiles_n = tiles_n;
+  sch.dp_tiles = (int)num_tiles;
+  sch.nu = (num_kb + UNIT_KB - 1) / UNIT_KB;
+  sch.U = 0;
+  sch.ws = nullptr;
+  sch.tickets = nullptr;
+  int64_t G = Gmax < num_tiles ? Gmax : num_tiles;
+  // A last wave that fills less than 3/4 of the machine is cut along K and spread over all CTAs.  (Fuller waves
+  // gain nothing: the kernel runs at the power limit, where idle SMs let the busy ones clock higher.)
+  const int64_t rest = num_tiles % Gmax;
+  const GemmWorkspace* gw = (const GemmWorkspace*)ctx->tmap_cache;
+  if (rest != 0 && 4 * rest < 3 * Gmax && sch.nu > 1 && rest * sch.nu < 0x40000000 && gw != nullptr && stream_k_enabled()) {
+    sch.dp_tiles = (int)(num_tiles - rest);
+    sch.U = (int)(rest * sch.nu);
+    sch.ws = gw->ws;
+    sch.tickets = gw->tickets;
+    G = Gmax;
+  }
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
   lc.gridDim = dim3((unsigned)(PAIR ? 2 * G : G), 1, 1);
@@ -658,7 +863,7 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   lc.attrs = attr;
   lc.numAttrs = 1;
   FB_CUDA(cudaLaunchKernelEx(&lc, kern, tmA, tmB, a.C, a.ldc, a.Z, a.bias_n, (int)a.M, (int)a.N, (int)a.K, a.act,
-                             a.accumulate, ctx->dev_error, prefetch_from_env(), a3d, b3d, (int)num_tiles, tiles_n));
+                             a.accumulate, ctx->dev_error, prefetch_from_env(), a3d, b3d, sch));
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
@@ -729,4 +934,36 @@ int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& 
   return launch_layout<256, 1, false>(ctx, stream, a);
 }
 
-void fb_tmap_cache_destroy(fb_ctx* ctx) { (void)ctx; }
+// Called by fb_ctx_create / fb_ctx_destroy.  The workspace is allocated up front (2 slots of 128 x 256 floats per
+// SM, 37 MiB on 148 SMs) so that no launch allocates; calls that share a context must be ordered on one stream.
+int32_t fb_gemm_workspace_create(fb_ctx* ctx) {
+  GemmWorkspace* gw = new GemmWorkspace();
+  gw->ws = nullptr;
+  gw->tickets = nullptr;
+  const size_t slots = (size_t)2 * (size_t)ctx->sm_count;
+  const size_t tickets = (size_t)ctx->sm_count * 4;
+  if (cudaMalloc(&gw->ws, slots * BM * 256 * sizeof(float)) != cudaSuccess ||
+      cudaMalloc(&gw->tickets, tickets * sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    if (gw->ws) cudaFree(gw->ws);
+    delete gw;
+    return fb_fail(FB_ERR_ALLOC, "fb_ctx_create: GEMM workspace allocation failed");
+  }
+  cudaMemset(gw->tickets, 0, tickets * sizeof(int));
+  ctx->tmap_cache = gw;
+  return FB_OK;
+}
+
+void fb_gemm_workspace_reset(fb_ctx* ctx, cudaStream_t stream) {
+  GemmWorkspace* gw = (GemmWorkspace*)ctx->tmap_cache;
+  if (gw != nullptr && gw->tickets != nullptr) cudaMemsetAsync(gw->tickets, 0, (size_t)ctx->sm_count * 4 * sizeof(int), stream);
+}
+
+void fb_tmap_cache_destroy(fb_ctx* ctx) {
+  GemmWorkspace* gw = (GemmWorkspace*)ctx->tmap_cache;
+  if (gw == nullptr) return;
+  if (gw->ws) cudaFree(gw->ws);
+  if (gw->tickets) cudaFree(gw->tickets);
+  delete gw;
+  ctx->tmap_cache = nullptr;
+}
