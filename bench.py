@@ -281,7 +281,11 @@ def run_ours(args):
         avg_ms = float(np.mean(durs))
         alg = 2.0 * nloc * D * D / (avg_ms * 1e-3) / 1e12
         peak = bf16 / 2.0
-        roof = {"bound": "tensor", "achieved": alg, "peak": peak, "unit": "TFLOP/s", "frac": alg / peak, "traffic": None,
+        # DRAM bytes per launch from one ncu capture of this kernel at batch 8192 (dram__bytes_read + write = 693.6 +
+        # 200.3 MB, against 335 MB algorithmic); for a smaller local batch it is scaled by the rows processed
+        traffic = 893.9e6 * nloc / 8192.0
+        roof = {"bound": "tensor", "achieved": alg, "peak": peak, "unit": "TFLOP/s", "frac": alg / peak, "traffic": traffic,
+                "traffic_source": "ncu capture of the same kernel at batch 8192 (profiles/gemm_tc_kernel_dense4096_batch8192.md), scaled by local batch",
                 "kernel": "gemm_tc_kernel (Dense 4096=>4096 forward, 3xTF32, persistent two-CTA 256x256 tiles)", "launch_ms": avg_ms, "launches_timed": len(durs),
                 "issued_frac": 3.0 * alg / peak, "peak_kind": peak_kind,
                 "note": "achieved = algorithmic 2*M*N*K per launch / CUDA-event launch time; 3xTF32 issues 3x that on the tensor pipe"}

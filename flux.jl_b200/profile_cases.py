@@ -1,6 +1,6 @@
 """Small single-kernel workloads for Nsight Compute captures and CUDA-event timing.
 
-    python flux.jl_b200/profile_cases.py <case> [--iters N] [--time]
+    python flux.jl_b200/profile_cases.py <case> [--iters N] [--time] [--batch B]
 
 Cases (each holds well under a few GB on the device; inputs exceed the 126 MB L2 so DRAM counters mean something):
     gemm_fwd    Dense 4096=>4096 forward, batch 4096 (3xTF32 tcgen05 GEMM, K-major x MN-major)
@@ -39,6 +39,7 @@ def main():
     ap.add_argument("case")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--batch", type=int, default=4096, help="batch size of the gemm_* cases (8192 = the headline bench shape)")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     h = C.c_void_p()
@@ -52,7 +53,7 @@ def main():
     case = args.case
     work = None      # (algorithmic quantity per iteration, unit)
     if case in ("gemm_fwd", "gemm_dw", "gemm_dx"):
-        n, d = 4096, 4096
+        n, d = args.batch, 4096
         W, x, dy = rn(d * d) * 0.02, rn(n * d), rn(n * d)
         y, dW, dx, b = torch.empty(n * d, device="cuda"), torch.empty(d * d, device="cuda"), torch.empty(n * d, device="cuda"), rn(d)
         if case == "gemm_fwd":
