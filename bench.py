@@ -49,12 +49,36 @@ def make_params(seed=3):
 
 # ------------------------------------------------------------------------------------- clocks ---
 class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU while the timed region runs: NVML reads every 5 ms from a
+    thread (a timed region can be shorter than one nvidia-smi period); nvidia-smi -lms 100 when NVML is missing."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
     def __init__(self, gpu_index):
         self.proc = None
         self.lines = []
+        self.samples = []          # (sm_mhz, reasons bitmask) from NVML
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                import torch
+                pr = torch.cuda.get_device_properties(gpu_index)
+                bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+                self.handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -63,11 +87,31 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def _poll(self):
+        nv = self.nvml
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append((float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)), int(get_reasons(self.handle))))
+            except Exception:
+                pass
+            time.sleep(0.005)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            sm = [a for a, _ in self.samples]
+            mask = 0
+            for _, r in self.samples:
+                mask |= r
+            reasons = sorted(name for name, bit in self.REASON_BITS if mask & bit)
+            return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                    "samples": len(sm), "source": "NVML, 5 ms period"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -88,7 +132,8 @@ class ClockSampler:
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvidia-smi -lms 100"}
 
 
 # --------------------------------------------------------------------------- CPU baseline arms ---
@@ -175,6 +220,8 @@ def run_ours(args):
     DU.synchronize(backend, DU.FluxDistributedModel(model))
     params = F.trainables(model)
     buckets = DU.GradBuckets(backend, params, bucket_mb=args.bucket_mb)
+    if args.timeline:
+        buckets.enable_timeline()
     opt = F.setup(DU.DistributedOptimizer(backend, F.Adam(1e-3), buckets), model)
     DU.synchronize(backend, opt)
 
@@ -229,7 +276,7 @@ def run_ours(args):
     else:
         # the one-launch train step: forward, backward, bucketed all-reduce and Adam replayed from a CUDA graph
         k0 = lib.raw().fb_kernel_launches()
-        gstep = F.GraphedTrainStep(loss_fn, model, opt, (x_dev, y_dev), grad_sink=buckets)
+        gstep = F.GraphedTrainStep(loss_fn, model, opt, (x_dev, y_dev), grad_sink=buckets, shard_optimizer=not args.no_shard)
         launches_per_step = (lib.raw().fb_kernel_launches() - k0) // 2      # warm-up pass + captured pass
         step_resident = lambda: gstep(x_dev, y_dev)                          # inputs already in HBM
         step_e2e = lambda: gstep(x_host, lab_host)                           # pinned host -> static device buffers
@@ -262,6 +309,9 @@ def run_ours(args):
     if F.context().device_error() != 0:
         raise SystemExit("a kernel recorded a bounded-wait timeout; the numbers are invalid")
 
+    if args.timeline and rank in (0, world - 1):
+        for name, us in buckets.timeline():
+            print(f"[timeline rank {rank}] {us:10.1f} us  {name}", file=sys.stderr)
     if rank != 0:
         return
     value = GLOBAL_BATCH * args.steps / (ms * 1e-3)
@@ -298,6 +348,8 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": nloc, "parallelism": f"dp{world}",
                        "matmul": "3xTF32 tcgen05", "gelu": "tanh approximation", "bucket_mb": args.bucket_mb,
                        "step": "eager launches" if args.eager else "CUDA graph replay (GraphedTrainStep)",
+                       "optimizer": ("sharded Adam (reduce-scatter, 1/N update, all-gather per bucket)"
+                                     if (not args.eager and getattr(gstep, "sharded", False)) else "Adam on every rank"),
                        "l2": "inputs larger than L2 (553 MB parameters, >3 GB activations per step)"},
             "tflops_algorithmic": value * FLOPS_PER_SAMPLE / 1e12,
             "e2e": {"value": GLOBAL_BATCH * args.steps / (ms_e2e * 1e-3), "unit": "samples/s",
@@ -445,6 +497,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bucket-mb", dest="bucket_mb", type=float, default=64.0)
+    ap.add_argument("--timeline", action="store_true",
+                    help="print, on stderr, device time marks of the last step (compute and communication streams)")
+    ap.add_argument("--no-shard", dest="no_shard", action="store_true",
+                    help="N > 1: all-reduce gradients and run Adam on every rank instead of reduce-scatter + sharded Adam + all-gather")
     ap.add_argument("--eager", action="store_true", help="launch every kernel from the host each step instead of replaying a CUDA graph")
     ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5],
                     help="5 (default): the data-parallel MLP the headline metric is quoted on; 1-4: the single-GPU configurations")

@@ -47,6 +47,7 @@ FB_API int32_t fb_ctx_create(int32_t device, fb_ctx** out) {
   fb_ctx* c = new fb_ctx();
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
+  c->reserved_sms = 0;
   c->smem_optin = prop.sharedMemPerBlockOptin;
   c->scratch = nullptr;
   c->scratch_bytes = 0;
@@ -66,6 +67,14 @@ FB_API int32_t fb_ctx_create(int32_t device, fb_ctx** out) {
     return ws_status;
   }
   *out = c;
+  return FB_OK;
+}
+
+FB_API int32_t fb_ctx_set_reserved_sms(fb_ctx* ctx, int32_t n) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(n >= 0 && n <= ctx->sm_count - 2, FB_ERR_INVALID_ARG, "fb_ctx_set_reserved_sms: %d is outside [0, %d]", n,
+             ctx->sm_count - 2);
+  ctx->reserved_sms = n;
   return FB_OK;
 }
 

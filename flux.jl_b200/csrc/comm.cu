@@ -22,6 +22,8 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
   int (*Broadcast)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
   int (*Reduce)(const void*, void*, size_t, int, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*ReduceScatter)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t) = nullptr;
   int (*CommGetAsyncError)(NcclComm, int*) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   bool ok = false;
@@ -47,6 +49,8 @@ NcclApi& nccl() {
   FB_SYM(AllReduce, "ncclAllReduce");
   FB_SYM(Broadcast, "ncclBroadcast");
   FB_SYM(Reduce, "ncclReduce");
+  FB_SYM(ReduceScatter, "ncclReduceScatter");
+  FB_SYM(AllGather, "ncclAllGather");
   FB_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
   FB_SYM(GetErrorString, "ncclGetErrorString");
 #undef FB_SYM
@@ -118,6 +122,32 @@ FB_API int32_t fb_allreduce(fb_comm* comm, void* stream, const float* send, floa
   const int rc = n.AllReduce(send, recv, (size_t)count, NCCL_FLOAT32, op == FB_OP_AVG ? NCCL_AVG : NCCL_SUM, comm->comm,
                              (cudaStream_t)stream);
   if (rc != 0) return nccl_fail("ncclAllReduce", rc);
+  return FB_OK;
+}
+
+FB_API int32_t fb_reduce_scatter(fb_comm* comm, void* stream, const float* send, float* recv, int64_t recv_count, int32_t op) {
+  FB_REQUIRE(comm, FB_ERR_INVALID_ARG, "fb_reduce_scatter: comm is NULL");
+  FB_REQUIRE(recv_count >= 0, FB_ERR_INVALID_ARG, "fb_reduce_scatter: negative count");
+  FB_REQUIRE(op == FB_OP_SUM || op == FB_OP_AVG, FB_ERR_INVALID_ARG, "fb_reduce_scatter: op must be FB_OP_SUM or FB_OP_AVG");
+  if (recv_count == 0) return FB_OK;
+  FB_REQUIRE(send && recv, FB_ERR_INVALID_ARG, "fb_reduce_scatter: NULL pointer");
+  NcclApi& n = nccl();
+  if (!n.ok || !n.ReduceScatter) return fb_fail(FB_ERR_NCCL, "fb_reduce_scatter: NCCL is not available");
+  const int rc = n.ReduceScatter(send, recv, (size_t)recv_count, NCCL_FLOAT32, op == FB_OP_AVG ? NCCL_AVG : NCCL_SUM,
+                                 comm->comm, (cudaStream_t)stream);
+  if (rc != 0) return nccl_fail("ncclReduceScatter", rc);
+  return FB_OK;
+}
+
+FB_API int32_t fb_allgather(fb_comm* comm, void* stream, const float* send, float* recv, int64_t send_count) {
+  FB_REQUIRE(comm, FB_ERR_INVALID_ARG, "fb_allgather: comm is NULL");
+  FB_REQUIRE(send_count >= 0, FB_ERR_INVALID_ARG, "fb_allgather: negative count");
+  if (send_count == 0) return FB_OK;
+  FB_REQUIRE(send && recv, FB_ERR_INVALID_ARG, "fb_allgather: NULL pointer");
+  NcclApi& n = nccl();
+  if (!n.ok || !n.AllGather) return fb_fail(FB_ERR_NCCL, "fb_allgather: NCCL is not available");
+  const int rc = n.AllGather(send, recv, (size_t)send_count, NCCL_FLOAT32, comm->comm, (cudaStream_t)stream);
+  if (rc != 0) return nccl_fail("ncclAllGather", rc);
   return FB_OK;
 }
 

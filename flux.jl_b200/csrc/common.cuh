@@ -16,6 +16,7 @@ constexpr int FB_MAX_RETIRED = 64;   // the arena doubles, so this is never reac
 struct fb_ctx {
   int device;
   int sm_count;
+  int reserved_sms;      // SMs the persistent GEMM leaves free (for communication kernels running beside it)
   size_t smem_optin;
   void* scratch;         // device arena, grown on demand, reused by every call on this context
   size_t scratch_bytes;

@@ -340,6 +340,22 @@ FB_API int32_t fb_fill(fb_ctx* ctx, void* stream, float* x, float value, int64_t
   return FB_OK;
 }
 
+// One thread stores the GPU's nanosecond timer: a stream-ordered time mark that also works inside a captured graph
+// (where events cannot be timed).
+__global__ void timestamp_kernel(uint64_t* out) {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *out = t;
+}
+
+FB_API int32_t fb_timestamp(fb_ctx* ctx, void* stream, uint64_t* out_dev) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(out_dev, FB_ERR_INVALID_ARG, "fb_timestamp: NULL pointer");
+  timestamp_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(out_dev);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}
+
 FB_API int32_t fb_axpy(fb_ctx* ctx, void* stream, float alpha, const float* x, float* y, int64_t count) {
   FB_CHECK_CTX(ctx);
   FB_REQUIRE(count >= 0, FB_ERR_INVALID_ARG, "fb_axpy: negative count");

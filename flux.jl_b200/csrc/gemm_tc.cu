@@ -827,7 +827,10 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   const int64_t num_tiles = tiles_m * tiles_n;
   if (num_tiles > 0x7fffffff) return fb_fail(FB_ERR_UNSUPPORTED, "gemm: too many tiles");
   // one CTA (pair) per SM (pair of SMs)
-  const int64_t Gmax = PAIR ? (ctx->sm_count / 2 > 0 ? ctx->sm_count / 2 : 1) : ctx->sm_count;
+  // (fewer when the caller reserved SMs for communication kernels that run beside this one: a persistent grid that
+  // does not fit waits for them to finish)
+  const int sms = ctx->sm_count - ctx->reserved_sms;
+  const int64_t Gmax = PAIR ? (sms / 2 > 0 ? sms / 2 : 1) : sms;
   const int num_kb = (int)((a.K + BK - 1) / BK);
   Sched sch;
   sch.num_tiles = (int)num_tiles;

@@ -37,6 +37,10 @@ class Context:
     def stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
+    def set_reserved_sms(self, n: int):
+        """SMs the persistent GEMM leaves free for communication kernels that run beside it (0 = none)."""
+        lib.call("fb_ctx_set_reserved_sms", self.handle, int(n))
+
     def device_error(self) -> int:
         out = C.c_int32(0)
         lib.call("fb_device_error", self.handle, self.stream, C.byref(out))

@@ -203,21 +203,37 @@ class GradBuckets:
     when a bucket's last gradient has landed, its mean all-reduce starts on the communication stream
     while the backward pass continues."""
 
-    def __init__(self, backend, params, bucket_mb: float = 64.0):
+    def __init__(self, backend, params, bucket_mb: float = 64.0, reserved_sms: int | None = None):
         self.backend = backend
+        # SMs the reverse sweep's persistent GEMMs leave free for the NCCL kernels that run beside them.  Measured at
+        # 8 GPUs, per-GPU batch 1024: 0, 16 and 32 reserved SMs give 6.43-6.51, 6.52-6.56 and 6.85 ms per step, so the
+        # default reserves none (FLUXB200_SM_RESERVE or the argument overrides).
+        if reserved_sms is None:
+            reserved_sms = int(os.environ.get("FLUXB200_SM_RESERVE", "0"))
+        self.reserved_sms = reserved_sms if backend.size > 1 else 0
         self.params = list(params)
         pad = lambda n: (n + 63) // 64 * 64          # every slice starts on a 256-byte boundary
         total = sum(pad(p.numel()) for p in self.params)
         dev = self.params[0].t.device
         self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
-        self.views, self.bucket_of = {}, {}
+        self.views, self.bucket_of, self.offsets = {}, {}, {}
         self.buckets = []   # [start, end, pending ids, all ids]
+        # sharded-optimiser mode (shard_optimizer): parameters / Adam moments re-homed in flat buffers laid out
+        # like the gradient buffer; `armed` is set by the step that captured the update kernels
+        self.pflat = self.mflat = self.vflat = None
+        self.adam = None
+        self.armed = False
+        self.loss = None
+        # optional timeline: device time marks (fb_timestamp) placed on both streams; see enable_timeline
+        self.marks = None
+        self.mark_names = []
         limit = int(bucket_mb * (1 << 20) / 4)
         off = 0
         cur_start, cur_ids = 0, []
         for p in reversed(self.params):
             n = p.numel()
             self.views[id(p)] = B200Array(self.flat[off:off + n], p.size)
+            self.offsets[id(p)] = off
             cur_ids.append(id(p))
             off += pad(n)
             if off - cur_start >= limit:
@@ -232,10 +248,34 @@ class GradBuckets:
         self.launched = [False] * len(self.buckets)
         self.begin_step()
 
+    def enable_timeline(self, slots: int = 256):
+        """Time marks on the compute and communication streams (they are captured with the step when it is a
+        graph): after a step `timeline()` lists (name, microseconds since the step's first mark)."""
+        self.marks = torch.zeros(slots, dtype=torch.int64, device=self.flat.device)
+        self.mark_names = []
+
+    def _mark(self, name, stream=None):
+        if self.marks is None or len(self.mark_names) >= self.marks.numel():
+            return
+        from .core import context
+        st = C.c_void_p(stream.cuda_stream) if stream is not None else context().stream
+        lib.call("fb_timestamp", context().handle, st, C.c_void_p(self.marks.data_ptr() + 8 * len(self.mark_names)))
+        self.mark_names.append(name)
+
+    def timeline(self):
+        if self.marks is None:
+            return []
+        t = self.marks[:len(self.mark_names)].cpu().tolist()
+        t0 = min(t) if t else 0
+        return sorted(((n, (v - t0) / 1e3) for n, v in zip(self.mark_names, t)), key=lambda kv: kv[1])
+
     def begin_step(self):
         for b in self.buckets:
             b[2] = set(b[3])
         self.launched = [False] * len(self.buckets)
+        if self.marks is not None:
+            self.mark_names = []
+            self._mark("step start")
 
     def buffer_for(self, param):
         return self.views.get(id(param)) if param is not None else None
@@ -250,17 +290,67 @@ class GradBuckets:
         if not b[2] and not self.launched[bi]:
             self._launch(bi)
 
+    def shard_optimizer(self, opt_state, bt: torch.Tensor) -> bool:
+        """Sharded optimiser state: after every bucket's reduce-scatter each rank runs Adam on its 1/N block of
+        the bucket and the blocks are put together again by an all-gather, all on the communication stream while
+        the backward pass continues (the layers of a finished bucket are not read again in the step).  The result
+        equals all-reduce + Adam on every rank; the update costs 1/N of the HBM traffic per rank.
+
+        Parameters and moments are re-homed (values kept) in flat buffers with the gradient buffer's layout; a
+        rank's moments are current only inside its own blocks.  `bt` is the device tensor holding (β1ᵗ, β2ᵗ).
+        Returns False (and changes nothing) when a bucket does not divide by the number of workers."""
+        from .train import Adam
+        n = self.backend.size
+        rule = opt_state.rule
+        if n == 1 or not isinstance(rule, Adam) or any((b[1] - b[0]) % n for b in self.buckets):
+            return False
+        if self.pflat is None:
+            self.pflat, self.mflat, self.vflat = (torch.zeros_like(self.flat) for _ in range(3))
+            for p in self.params:
+                off, cnt = self.offsets[id(p)], p.numel()
+                st = opt_state.leaves[id(p)].state
+                for flat, arr in ((self.pflat, p), (self.mflat, st[0]), (self.vflat, st[1])):
+                    view = flat[off:off + cnt]
+                    view.copy_(arr.t)
+                    arr.t = view
+        self.adam = (rule, bt)
+        return True
+
+    def set_loss(self, loss):
+        """The step's loss (device scalar): the captured update kernels skip themselves when it is not finite."""
+        self.loss = loss
+        self._mark("forward end")
+
     def _launch(self, bi):
         self.launched[bi] = True
         be = self.backend
         if be.size == 1:
             return
         start, end = self.buckets[bi][0], self.buckets[bi][1]
+        self._mark(f"bucket {bi} ready")
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream())
         be.stream.wait_event(ev)
+        self._mark(f"bucket {bi} comm start", be.stream)
+        cs = C.c_void_p(be.stream.cuda_stream)
         ptr = C.c_void_p(self.flat.data_ptr() + 4 * start)
-        lib.call("fb_allreduce", be.comm, C.c_void_p(be.stream.cuda_stream), ptr, ptr, end - start, lib.OP["avg"])
+        if self.armed and self.adam is not None and self.loss is not None:
+            from .core import context
+            rule, bt = self.adam
+            blk = (end - start) // be.size
+            lo = 4 * (start + be.rank * blk)
+            g, pp = self.flat.data_ptr() + lo, self.pflat.data_ptr() + lo
+            lib.call("fb_reduce_scatter", be.comm, cs, ptr, C.c_void_p(g), blk, lib.OP["avg"])
+            self._mark(f"bucket {bi} reduce-scatter end", be.stream)
+            one = C.c_void_p * 1
+            lib.call("fb_adam_step_dev", context().handle, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
+                     one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
+                     rule.epsilon, C.c_void_p(bt.data_ptr()), self.loss.ptr, 1.0)
+            self._mark(f"bucket {bi} adam end", be.stream)
+            lib.call("fb_allgather", be.comm, cs, C.c_void_p(pp), C.c_void_p(self.pflat.data_ptr() + 4 * start), blk)
+        else:
+            lib.call("fb_allreduce", be.comm, cs, ptr, ptr, end - start, lib.OP["avg"])
+        self._mark(f"bucket {bi} comm end", be.stream)
         self.events[bi].record(be.stream)
 
     def finish(self):
@@ -268,9 +358,11 @@ class GradBuckets:
         for bi in range(len(self.buckets)):
             if not self.launched[bi]:
                 self._launch(bi)
+        self._mark("backward end")
         if self.backend.size > 1:
             for ev in self.events:
                 torch.cuda.current_stream().wait_event(ev)
+        self._mark("step end")
 
 
 class DistributedOptimizer(DistributedOptimizerBase):

@@ -42,6 +42,7 @@ PROTOTYPES = {
     "fb_version": (_i32, []),
     "fb_kernel_launches": (_i64, []),
     "fb_ctx_create": (_i32, [_i32, C.POINTER(_p)]),
+    "fb_ctx_set_reserved_sms": (_i32, [_p, _i32]),
     "fb_ctx_destroy": (_i32, [_p]),
     "fb_last_error": (C.c_char_p, []),
     "fb_malloc": (_i32, [_p, _i64, C.POINTER(_p)]),
@@ -65,6 +66,7 @@ PROTOTYPES = {
     "fb_logitcrossentropy_dense": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f]),
     "fb_sumsq": (_i32, [_p, _p, _p, _i64, _p]),
     "fb_sum": (_i32, [_p, _p, _p, _i64, _p]),
+    "fb_timestamp": (_i32, [_p, _p, _p]),
     "fb_fill": (_i32, [_p, _p, _p, _f, _i64]),
     "fb_scale": (_i32, [_p, _p, _p, _f, _p, _i64]),
     "fb_axpy": (_i32, [_p, _p, _f, _p, _p, _i64]),
@@ -90,6 +92,8 @@ PROTOTYPES = {
     "fb_comm_rank": (_i32, [_p]),
     "fb_comm_size": (_i32, [_p]),
     "fb_allreduce": (_i32, [_p, _p, _p, _p, _i64, _i32]),
+    "fb_reduce_scatter": (_i32, [_p, _p, _p, _p, _i64, _i32]),
+    "fb_allgather": (_i32, [_p, _p, _p, _p, _i64]),
     "fb_bcast": (_i32, [_p, _p, _p, _p, _i64, _i32]),
     "fb_reduce": (_i32, [_p, _p, _p, _p, _i64, _i32, _i32]),
     "fb_comm_async_error": (_i32, [_p, C.POINTER(_i32)]),

@@ -155,10 +155,16 @@ def _withgradient_device(f, model, grad_sink=None):
             loss, aux = out[0], out[1:]
         if not isinstance(loss, B200Array) or loss.numel() != 1:
             raise TypeError("withgradient: the function must return a scalar B200Array")
+        if grad_sink is not None and hasattr(grad_sink, "set_loss"):
+            grad_sink.set_loss(loss)
         grads: dict = {}
         keep: dict = {}
         grads[id(loss)] = _One(B200Array(torch.ones(1, device=loss.t.device), ()))
         keep[id(loss)] = loss
+        # gradient averaging runs beside the reverse sweep: leave it the SMs it needs
+        reserve = int(getattr(grad_sink, "reserved_sms", 0) or 0)
+        if reserve:
+            context().set_reserved_sms(reserve)
         for outs, inputs, pullback in reversed(Tape.entries):
             gs = [grads.get(id(o)) for o in outs]
             if all(g is None for g in gs):
@@ -171,6 +177,8 @@ def _withgradient_device(f, model, grad_sink=None):
                     grad_sink.ready(arr)
         tree = _grad_tree(model, grads)
     finally:
+        if int(getattr(grad_sink, "reserved_sms", 0) or 0):
+            context().set_reserved_sms(0)
         Tape.active = False
         Tape.grad_sink = None
         Tape.reset()
@@ -364,7 +372,7 @@ class GraphedTrainStep:
     step's static input buffers on the current stream).
     """
 
-    def __init__(self, loss, model, opt_state, example_batch, grad_sink=None):
+    def __init__(self, loss, model, opt_state, example_batch, grad_sink=None, shard_optimizer=False):
         from .layers import BatchNorm, _walk
         if not isinstance(example_batch, tuple):
             example_batch = (example_batch,)
@@ -399,26 +407,38 @@ class GraphedTrainStep:
         for l, (mu, var) in zip(bns, saved):
             l.μ.t.copy_(mu)
             l.σ2.t.copy_(var)
+        # sharded optimiser: the sink's bucket launches carry reduce-scatter + Adam on this rank's block + all-gather
+        self.sharded = bool(shard_optimizer and grad_sink is not None and hasattr(grad_sink, "shard_optimizer")
+                            and all(id(p) in grad_sink.views for p in self.params)
+                            and grad_sink.shard_optimizer(opt_state, self.bt))
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             if grad_sink is not None:
                 grad_sink.begin_step()
-            loss_arr, _, tree = _withgradient_device(fn, model, grad_sink)
-            gmap: dict = {}
-            _flat_grads(model, tree, gmap)
-            outer = getattr(opt_state, "outer", None)
-            if isinstance(outer, DistributedOptimizerBase):
-                outer.average_gradients(opt_state, gmap)
+                grad_sink.armed = self.sharded
+            try:
+                loss_arr, _, tree = _withgradient_device(fn, model, grad_sink)
+                gmap: dict = {}
+                _flat_grads(model, tree, gmap)
+                outer = getattr(opt_state, "outer", None)
+                if isinstance(outer, DistributedOptimizerBase):
+                    outer.average_gradients(opt_state, gmap)
+                elif self.sharded:
+                    grad_sink.finish()
+            finally:
+                if grad_sink is not None:
+                    grad_sink.armed = False
             ps = [p for p in self.params if id(p) in gmap]
-            k = len(ps)
-            arr_t = C.c_void_p * k
-            self._tables = (arr_t(*[p.t.data_ptr() for p in ps]), arr_t(*[gmap[id(p)].t.data_ptr() for p in ps]),
-                            arr_t(*[opt_state.leaves[id(p)].state[0].t.data_ptr() for p in ps]),
-                            arr_t(*[opt_state.leaves[id(p)].state[1].t.data_ptr() for p in ps]),
-                            (C.c_int64 * k)(*[p.numel() for p in ps]))
             c = context()
-            lib.call("fb_adam_step_dev", c.handle, c.stream, k, *self._tables, rule.eta, rule.beta[0], rule.beta[1],
-                     rule.epsilon, C.c_void_p(self.bt.data_ptr()), loss_arr.ptr, 1.0)
+            if not self.sharded:
+                k = len(ps)
+                arr_t = C.c_void_p * k
+                self._tables = (arr_t(*[p.t.data_ptr() for p in ps]), arr_t(*[gmap[id(p)].t.data_ptr() for p in ps]),
+                                arr_t(*[opt_state.leaves[id(p)].state[0].t.data_ptr() for p in ps]),
+                                arr_t(*[opt_state.leaves[id(p)].state[1].t.data_ptr() for p in ps]),
+                                (C.c_int64 * k)(*[p.numel() for p in ps]))
+                lib.call("fb_adam_step_dev", c.handle, c.stream, k, *self._tables, rule.eta, rule.beta[0], rule.beta[1],
+                         rule.epsilon, C.c_void_p(self.bt.data_ptr()), loss_arr.ptr, 1.0)
             lib.call("fb_adam_advance", c.handle, c.stream, C.c_void_p(self.bt.data_ptr()), rule.beta[0], rule.beta[1],
                      loss_arr.ptr)
             self._keep = (loss_arr, tree, gmap)

@@ -75,6 +75,12 @@ int64_t fb_kernel_launches(void);
  * Replaces what CUDA.jl's task-local state gives FluxCUDAExt (ext/FluxCUDAExt.jl:1-13). */
 int32_t fb_ctx_create(int32_t device, fb_ctx** out);
 int32_t fb_ctx_destroy(fb_ctx* ctx);
+/* The persistent GEMM launches one CTA per SM; a communication kernel (NCCL) that holds a few SMs when the GEMM
+ * starts would make part of that grid wait until the communication ends.  With n SMs reserved the GEMM grid is
+ * sized for sm_count - n, so both run side by side.  0 (the default) uses every SM.  Host-side setting, read at
+ * launch (a captured graph keeps the grid it was captured with).  No counterpart in the reference. */
+int32_t fb_ctx_set_reserved_sms(fb_ctx* ctx, int32_t n);
+
 
 /* Message of the last error raised on the calling thread ("" if none). */
 const char* fb_last_error(void);
@@ -196,6 +202,10 @@ int32_t fb_sumsq(fb_ctx* ctx, void* stream, const float* x, int64_t count, float
 int32_t fb_sum(fb_ctx* ctx, void* stream, const float* x, int64_t count, float* out);
 /* x[i] = value for all i (Base.fill!, the cotangent of sum). */
 int32_t fb_fill(fb_ctx* ctx, void* stream, float* x, float value, int64_t count);
+/* out_dev[0] = the GPU's nanosecond timer when the stream reaches this point: a time mark that can be placed
+ * inside a captured graph (on any stream) to see how compute and communication interleave.  Measurement aid, no
+ * counterpart in the reference. */
+int32_t fb_timestamp(fb_ctx* ctx, void* stream, uint64_t* out_dev);
 /* y = alpha * x (the cotangent 2y of sum(abs2, y); Optimisers' eta scaling). */
 int32_t fb_scale(fb_ctx* ctx, void* stream, const float* x, float alpha, float* y, int64_t count);
 /* y += alpha * x (tangent accumulation `+` of Zygote; `x .-= dx` of Optimisers.update!). */
@@ -301,6 +311,13 @@ int32_t fb_comm_size(const fb_comm* comm);
 /* DistributedUtils.allreduce! on a Float32 device buffer, in place when send == recv
  * (NCCL.Allreduce!, FluxMPINCCLExt.jl:61-78); FB_OP_AVG is DistributedUtils.avg. */
 int32_t fb_allreduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op);
+/* The two halves of an all-reduce, for an optimiser whose state is sharded over the workers: every rank receives
+ * the reduced block `rank` of `send` (recv_count elements; send holds nranks * recv_count), updates its share of the
+ * parameters, and fb_allgather puts the blocks together again (recv holds nranks * send_count; in place when
+ * send == recv + rank * send_count).  No counterpart in the reference, whose DistributedOptimizer all-reduces and
+ * updates everything on every rank (src/distributed/public_api.jl:286-294); results are the same. */
+int32_t fb_reduce_scatter(fb_comm* comm, void* stream, const float* send, float* recv, int64_t recv_count, int32_t op);
+int32_t fb_allgather(fb_comm* comm, void* stream, const float* send, float* recv, int64_t send_count);
 /* DistributedUtils.bcast! (NCCL.Broadcast!, FluxMPINCCLExt.jl:38-53). */
 int32_t fb_bcast(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t root);
 /* DistributedUtils.reduce! (NCCL.Reduce!, FluxMPINCCLExt.jl:86-102). */

@@ -114,6 +114,40 @@ def main():
     assert torch.equal(lo, hi), "replicas diverged"
     assert np.max(np.abs(F.cpu(w) - b64[0]["W"])) < 3.5e-3        # within the three Adam steps' reach of the oracle
     assert F.context().device_error() == 0
+
+    # one-launch train step: sharded optimiser (reduce-scatter, Adam on this rank's block, all-gather, all inside the
+    # bucket launches) against all-reduce + Adam on every rank
+    def build():
+        ls = []
+        for blk in blocks:
+            ln = F.LayerNorm(Dm)
+            ln.diag.scale, ln.diag.bias = F.gpu(blk["gamma"]), F.gpu(blk["beta"])
+            ls += [ln, F.Dense(blk["W"], blk["b"], "gelu")]
+        ls.append(F.Dense(head["W"], head["b"]))
+        return F.Chain(*ls)
+
+    runs = []
+    for shard in (False, True):
+        m = build()
+        bk = DU.GradBuckets(backend, F.trainables(m), bucket_mb=0.2)
+        o = F.setup(DU.DistributedOptimizer(backend, F.Adam(1e-3), bk), m)
+        gs = F.GraphedTrainStep(lambda mm, xx, yy: F.logitcrossentropy(mm(xx), yy), m, o, (xg, yg), grad_sink=bk,
+                                shard_optimizer=shard)
+        assert gs.sharded == (shard and world > 1)
+        runs.append((m, [gs(xg, yg) for _ in range(3)]))
+    (ma, la), (mb, lb) = runs
+    np.testing.assert_allclose(la, lb, rtol=1e-5)
+    assert la[2] < la[0]
+    for pa, pb in zip(F.trainables(ma), F.trainables(mb)):
+        np.testing.assert_allclose(F.cpu(pb), F.cpu(pa), rtol=0, atol=3e-6)
+    wb = mb.layers[1].weight
+    chk = torch.stack([wb.t.double().sum(), (wb.t.double() ** 2).sum()]).cpu()
+    lo, hi = chk.clone(), chk.clone()
+    if world > 1:
+        torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
+        torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
+    assert torch.equal(lo, hi), "replicas diverged under the sharded optimiser"
+    assert F.context().device_error() == 0
     if rank == 0:
         print("dp_worker ok", world)
 
