@@ -7,6 +7,8 @@
 // Backward: T step kernels in reverse (gate derivatives, then dh_{t-1} = Wh' * dgates), followed by three
 //           GEMMs over all T*B columns for dWi, dWh and dx.
 // Steps are ordered by the stream (one launch per step), so no kernel ever waits on another block.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
@@ -234,13 +236,49 @@ gru_bwd_gates_kernel(const float* __restrict__ cache_t, int64_t ldcache, const f
 // pre[b][r] = sum_k W[r][k] * hprev[b][k] for the NG*4 gate rows of units [u0, u0+4) and a 64-wide batch chunk.
 //   Ws: [NG*4][kp] (kp = H rounded up to 16), hs: [64][kp + 4], red: [4][64][NG*4 + 1].
 //   On return red[b * (NR + 1) + r] holds the sums for this chunk.
-template <int NG>
-__device__ __forceinline__ void fast_gate_preacts(const float* __restrict__ Wh, const float* __restrict__ hprev, int64_t ldh,
+// Bounded wait on a shared-memory mbarrier phase.
+__device__ __forceinline__ bool rnn_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < (1u << 22); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+// BULK (persistent kernels): h_{t-1} was written by other blocks of this same launch; its rows (H contiguous floats
+// each) are brought into shared memory by one cp.async.bulk per row, which reads through L2 and completes on `bar`.
+// hs must have been zeroed once (padding columns and rows past the batch are never written).  Returns false when the
+// bounded wait for the copies ran out (uniform over the block).
+template <int NG, bool BULK = false>
+__device__ __forceinline__ bool fast_gate_preacts(const float* __restrict__ Wh, const float* hprev, int64_t ldh,
                                                   int H, int B, int b0, int u0, int kp, float* __restrict__ Ws,
-                                                  float* __restrict__ hs, float* __restrict__ red, bool load_w) {
+                                                  float* __restrict__ hs, float* __restrict__ red, bool load_w,
+                                                  uint32_t bar = 0, uint32_t parity = 0) {
   constexpr int NR = NG * 4;
   const int hs_ld = kp + 4;
   const int k4n = kp >> 2;
+  int ok = 1;
+  if (BULK && hprev != nullptr && threadIdx.x < 32) {
+    const int nrows = (B - b0) < BC ? (B - b0) : BC;
+    asm volatile("fence.proxy.async;" ::: "memory");   // h rows were written through the generic proxy
+    if (threadIdx.x == 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(nrows * H * 4)) : "memory");
+    __syncwarp();
+    for (int r = threadIdx.x; r < nrows; r += 32) {
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(hs + r * hs_ld);
+      const float* src = hprev + (int64_t)(b0 + r) * ldh;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                   "r"((uint32_t)(H * 4)), "r"(bar)
+                   : "memory");
+    }
+  }
   if (load_w) {
     // W[k][g][u0 .. u0+3] is one 16-byte piece of the [H][NG*H] weight memory
     for (int e = threadIdx.x; e < kp * NG; e += RT) {
@@ -254,14 +292,18 @@ __device__ __forceinline__ void fast_gate_preacts(const float* __restrict__ Wh, 
     }
   }
   if (hprev != nullptr) {
-    for (int e = threadIdx.x; e < BC * k4n; e += RT) {
-      const int bb = e / k4n, k4 = e % k4n;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (b0 + bb < B && 4 * k4 < H) v = __ldg((const float4*)(hprev + (int64_t)(b0 + bb) * ldh + 4 * k4));
-      *(float4*)(hs + bb * hs_ld + 4 * k4) = v;
+    if (BULK) {
+      ok = rnn_mbar_wait(bar, parity) ? 1 : 0;
+    } else {
+      for (int e = threadIdx.x; e < BC * k4n; e += RT) {
+        const int bb = e / k4n, k4 = e % k4n;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b0 + bb < B && 4 * k4 < H) v = __ldg((const float4*)(hprev + (int64_t)(b0 + bb) * ldh + 4 * k4));
+        *(float4*)(hs + bb * hs_ld + 4 * k4) = v;
+      }
     }
   }
-  __syncthreads();
+  if (!__syncthreads_and(ok)) return false;
   const int b = threadIdx.x & (BC - 1), kq = threadIdx.x >> 6;
   float acc[NR];
 #pragma unroll
@@ -293,6 +335,7 @@ __device__ __forceinline__ void fast_gate_preacts(const float* __restrict__ Wh, 
     red[bb * (NR + 1) + r] = sum;
   }
   __syncthreads();
+  return true;
 }
 
 __global__ void __launch_bounds__(RT)
@@ -363,6 +406,112 @@ gru_fwd_fast_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, 
       }
       if (hT) hT[(int64_t)gb * H + gu] = hn;
     }
+  }
+}
+
+// Barrier over all blocks of a cooperative launch (every block is resident, so every block arrives).  `counter` starts
+// at 0 for the launch and counts arrivals; generation g is complete when it reaches g * gridDim.x.  The wait is
+// bounded: when it runs out the block records `code` in the error word and every caller leaves its time loop.
+constexpr unsigned GRID_WAIT_LIMIT = 1u << 22;
+__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int32_t* dev_err, int32_t code) {
+  __syncthreads();
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    unsigned spins = 0;
+    for (;;) {
+      unsigned seen;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+      if (seen >= target) break;
+      if (++spins > GRID_WAIT_LIMIT || *(volatile int32_t*)dev_err != 0) {
+        atomicCAS(dev_err, 0, code);
+        ok = 0;
+        break;
+      }
+    }
+    __threadfence();
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// The whole forward time loop in one cooperative launch: block u0/4 keeps its 16 rows of Wh in shared memory for all
+// T steps; a step reads h_{t-1} (written by all blocks in the previous step), adds the hoisted input projection,
+// applies the gates and writes its 4 units of h_t / c_t; a grid barrier separates the steps.
+__global__ void __launch_bounds__(RT)
+lstm_fwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, const float* __restrict__ h0,
+                        const float* __restrict__ c0, float* out, float* gates, float* cst, int cached, float* __restrict__ hT,
+                        float* __restrict__ cT, int H, int B, int T, unsigned* counter, int32_t* dev_err) {
+  extern __shared__ __align__(16) float sm[];
+  const int kp = (H + 15) & ~15;
+  float* Ws = sm;
+  float* hs = Ws + 16 * kp;
+  float* red = hs + BC * (kp + 4);
+  const int u0 = blockIdx.x * 4;
+  const int64_t ldrow = (int64_t)T * H, ldg = (int64_t)T * 4 * H;
+  __shared__ __align__(8) uint64_t h_bar;
+  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&h_bar);
+  for (int e = threadIdx.x; e < BC * (kp + 4); e += RT) hs[e] = 0.0f;
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeros precede the async-proxy row copies
+  __syncthreads();
+  uint32_t loads = 0;   // bulk loads waited for so far: names the barrier phase
+  bool alive = true;
+  for (int t = 0; t < T && alive; ++t) {
+    const float* hprev = t == 0 ? h0 : out + (int64_t)(t - 1) * H;
+    const int64_t ldh = t == 0 ? H : ldrow;
+    const float* cprev;
+    float* c_t;
+    int64_t ldcp, ldct;
+    if (cached) {
+      cprev = t == 0 ? c0 : cst + (int64_t)(t - 1) * H;
+      ldcp = t == 0 ? H : ldrow;
+      c_t = cst + (int64_t)t * H;
+      ldct = ldrow;
+    } else {
+      cprev = t == 0 ? c0 : cst + (int64_t)((t - 1) & 1) * B * H;
+      ldcp = H;
+      c_t = cst + (int64_t)(t & 1) * B * H;
+      ldct = H;
+    }
+    const float* gx_t = gx + (int64_t)t * 4 * H;
+    float* out_t = out + (int64_t)t * H;
+    float* gates_t = gates ? gates + (int64_t)t * 4 * H : nullptr;
+    const bool lastt = (t == T - 1);
+    for (int b0 = 0; b0 < B; b0 += BC) {
+      if (b0 > 0) __syncthreads();
+      if (!fast_gate_preacts<4, true>(Wh, hprev, ldh, H, B, b0, u0, kp, Ws, hs, red, t == 0 && b0 == 0, bar, loads & 1u)) {
+        if (threadIdx.x == 0) atomicCAS(dev_err, 0, 3002);
+        alive = false;
+        break;
+      }
+      if (hprev != nullptr) ++loads;
+      const int bb = threadIdx.x >> 2, u = threadIdx.x & 3;
+      const int gb = b0 + bb, gu = u0 + u;
+      if (gb < B && gu < H) {
+        const float* pre = red + bb * 17;
+        const float* gxr = gx_t + (int64_t)gb * ldg;
+        const float zi = pre[u] + gxr[gu], zf = pre[4 + u] + gxr[H + gu];
+        const float zg = pre[8 + u] + gxr[2 * H + gu], zo = pre[12 + u] + gxr[3 * H + gu];
+        const float ig = 1.0f / (1.0f + expf(-zi)), fg = 1.0f / (1.0f + expf(-zf));
+        const float gg = tanhf(zg), og = 1.0f / (1.0f + expf(-zo));
+        // c of (gb, gu) was written by this same thread one step earlier
+        const float cp = cprev ? cprev[(int64_t)gb * ldcp + gu] : 0.0f;
+        const float cn = fg * cp + ig * gg;
+        const float hn = og * tanhf(cn);
+        out_t[(int64_t)gb * ldrow + gu] = hn;
+        if (gates_t) {
+          float* gr = gates_t + (int64_t)gb * ldg;
+          gr[gu] = ig; gr[H + gu] = fg; gr[2 * H + gu] = gg; gr[3 * H + gu] = og;
+        }
+        c_t[(int64_t)gb * ldct + gu] = cn;
+        if (lastt && hT) { hT[(int64_t)gb * H + gu] = hn; cT[(int64_t)gb * H + gu] = cn; }
+      }
+    }
+    if (alive && !lastt && !grid_barrier(counter, (unsigned)(t + 1) * gridDim.x, dev_err, 3001)) break;
   }
 }
 
@@ -443,6 +592,137 @@ rnn_bwd_dh2d_kernel(const float* __restrict__ Wh, const float* __restrict__ dg, 
 
 constexpr size_t DH2D_SMEM = (size_t)2 * DH_U * DH_LD * sizeof(float);
 
+// The whole LSTM reverse time loop in one cooperative launch.  Block (ub, rb, bz) keeps the 64 x 128 tile
+// Wm[64 ub .. +64][128 rb .. +128] of the recurrent weights in shared memory for all T steps.  A step has two phases
+// separated by grid barriers: (1) every thread turns its (b, u) elements' dh = dout + sum of the partials of the step
+// after into the four gate derivatives (written over the cached gates) and carries dc; (2) every block multiplies
+// its weight tile with its 64 x 128 tile of those derivatives (rows brought in by cp.async.bulk) into the partial sums
+// part[rb][b][u] that phase 1 of the next step adds up.
+constexpr int PB_R = 128, PB_LD = PB_R + 4;
+constexpr size_t PB_SMEM = (size_t)2 * DH_U * PB_LD * sizeof(float);
+
+__global__ void __launch_bounds__(RT)
+lstm_bwd_persist_kernel(const float* __restrict__ Wh, float* gates, const float* __restrict__ cst, const float* __restrict__ c0,
+                        const float* __restrict__ dout, const float* __restrict__ dhT, float* dc, float* parts, int H, int B, int T,
+                        int UB, int NP, unsigned* counter, int32_t* dev_err) {
+  extern __shared__ __align__(16) float sm[];
+  float* Ws = sm;                   // [64 u][PB_LD]
+  float* Ds = Ws + DH_U * PB_LD;    // [64 b][PB_LD]
+  __shared__ __align__(8) uint64_t d_bar;
+  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&d_bar);
+  const int R = 4 * H;
+  const int ub = blockIdx.x % UB, rb = (blockIdx.x / UB) % NP, bz = blockIdx.x / (UB * NP);
+  const int u0 = ub * DH_U, r0 = rb * PB_R, b0 = bz * BC;
+  const int64_t ldrow = (int64_t)T * H, ldg = (int64_t)T * 4 * H, total = (int64_t)B * H;
+  for (int e = threadIdx.x; e < DH_U * (PB_R / 4); e += RT) {
+    const int row = e / (PB_R / 4), c4 = e % (PB_R / 4);
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (u0 + row < H) w = __ldg((const float4*)(Wh + (int64_t)(u0 + row) * R + r0 + 4 * c4));
+    *(float4*)(Ws + row * PB_LD + 4 * c4) = w;
+    *(float4*)(Ds + row * PB_LD + 4 * c4) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  const int nrows = (B - b0) < BC ? (B - b0) : BC;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  unsigned gen = 0;      // grid barriers passed
+  uint32_t loads = 0;    // bulk loads waited for
+  for (int t = T - 1; t >= 0; --t) {
+    // ---- phase 1: gate derivatives of step t
+    {
+      float* g_t = gates + (int64_t)t * 4 * H;
+      const float* c_t = cst + (int64_t)t * H;
+      const float* c_prev = t == 0 ? c0 : cst + (int64_t)(t - 1) * H;
+      const int64_t ldcp = t == 0 ? (int64_t)H : ldrow;
+      const float* dout_t = dout + (int64_t)t * H;
+      const bool lastt = (t == T - 1);
+      for (int64_t e = (int64_t)blockIdx.x * RT + threadIdx.x; e < total; e += (int64_t)gridDim.x * RT) {
+        const int b = (int)(e / H), u = (int)(e % H);
+        float* gr = g_t + (int64_t)b * ldg;
+        const float ig = gr[u], fg = gr[H + u], gg = gr[2 * H + u], og = gr[3 * H + u];
+        const float tc = tanhf(c_t[(int64_t)b * ldrow + u]);
+        const float cp = c_prev ? c_prev[(int64_t)b * ldcp + u] : 0.0f;
+        float dh = dout_t[(int64_t)b * ldrow + u];
+        if (lastt) {
+          if (dhT) dh += dhT[e];
+        } else {
+          for (int p = 0; p < NP; ++p) dh += __ldcg(parts + (int64_t)p * total + e);   // written by other blocks
+        }
+        const float d_o = dh * tc;
+        const float dcc = dc[e] + dh * og * (1.0f - tc * tc);   // dc[e] is carried by this same thread
+        gr[u] = dcc * gg * ig * (1.0f - ig);
+        gr[H + u] = dcc * cp * fg * (1.0f - fg);
+        gr[2 * H + u] = dcc * ig * (1.0f - gg * gg);
+        gr[3 * H + u] = d_o * og * (1.0f - og);
+        dc[e] = dcc * fg;
+      }
+    }
+    if (t == 0) break;
+    ++gen;
+    if (!grid_barrier(counter, gen * gridDim.x, dev_err, 3003)) break;
+    // ---- phase 2: partial sums of Wh' * dgates for step t - 1
+    if (threadIdx.x < 32) {
+      asm volatile("fence.proxy.async;" ::: "memory");   // the derivatives were written through the generic proxy
+      if (threadIdx.x == 0)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(nrows * PB_R * 4)) : "memory");
+      __syncwarp();
+      for (int r = threadIdx.x; r < nrows; r += 32) {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Ds + r * PB_LD);
+        const float* src = gates + (int64_t)t * 4 * H + (int64_t)(b0 + r) * ldg + r0;
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                     "r"((uint32_t)(PB_R * 4)), "r"(bar)
+                     : "memory");
+      }
+    }
+    const int got = rnn_mbar_wait(bar, loads & 1u) ? 1 : 0;
+    ++loads;
+    if (!__syncthreads_and(got)) {
+      if (threadIdx.x == 0) atomicCAS(dev_err, 0, 3004);
+      break;
+    }
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+#pragma unroll 4
+    for (int c = 0; c < PB_R; c += 4) {
+      float4 a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = *(const float4*)(Ds + (ty + 16 * i) * PB_LD + c);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = *(const float4*)(Ws + (tx + 16 * j) * PB_LD + c);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i].x, w[j].x, acc[i][j]);
+          acc[i][j] = fmaf(a[i].y, w[j].y, acc[i][j]);
+          acc[i][j] = fmaf(a[i].z, w[j].z, acc[i][j]);
+          acc[i][j] = fmaf(a[i].w, w[j].w, acc[i][j]);
+        }
+    }
+    float* pp = parts + (int64_t)rb * total;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int gb = b0 + ty + 16 * i;
+      if (gb >= B) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int gu = u0 + tx + 16 * j;
+        if (gu < H) pp[(int64_t)gb * H + gu] = acc[i][j];
+      }
+    }
+    ++gen;
+    if (!grid_barrier(counter, gen * gridDim.x, dev_err, 3003)) break;
+  }
+}
+
+
 // hprev_all[(b, t)] = t == 0 ? h0[b] (or 0) : out[(b, t-1)]
 __global__ void __launch_bounds__(RT)
 shift_prev_kernel(const float* __restrict__ out, const float* __restrict__ h0, float* __restrict__ hprev_all, int H,
@@ -474,6 +754,16 @@ int pick_hu(int ng, int H, size_t smem_optin, size_t extra) {
 size_t fwd_smem(int ng, int hu, int H) {
   const int kp = (H + KC - 1) / KC * KC;
   return (size_t)(ng * hu) * kp * 4 + (size_t)BC * HS * 4 + (size_t)4 * BC * (ng * hu + 1) * 4;
+}
+
+// FLUXB200_RNN_PERSIST = 0 keeps one launch per time step.
+bool persistent_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUXB200_RNN_PERSIST");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
 }
 
 int32_t check_dims(const char* fn, int64_t in_dim, int64_t H, int64_t T, int64_t B) {
@@ -541,6 +831,23 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
   else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
   const int64_t ldrow = T * H;       // stride between batch rows of out / cached c at a fixed t
+  if (fast && T > 1 && T * (int64_t)grid < 0x7fffffff && persistent_enabled()) {
+    // one cooperative launch for the whole sequence when every block can be resident at once
+    int per_sm = 0;
+    FB_CUDA(cudaFuncSetAttribute(lstm_fwd_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lstm_fwd_persist_kernel, RT, smem));
+    if ((int64_t)per_sm * ctx->sm_count >= (int64_t)grid) {
+      unsigned* counter = (unsigned*)(ctx->dev_error + 16);
+      FB_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned), stream));
+      int cached = cache ? 1 : 0, Hi = H, Bi = B, Ti = (int)T;
+      int32_t* dev_err = ctx->dev_error;
+      void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&c0, (void*)&out, (void*)&gates, (void*)&cst, (void*)&cached,
+                      (void*)&hT, (void*)&cT, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&counter, (void*)&dev_err};
+      FB_CUDA(cudaLaunchCooperativeKernel((const void*)lstm_fwd_persist_kernel, dim3(grid), dim3(RT), args, smem, stream));
+      FB_LAUNCH_CHECK();
+      return FB_OK;
+    }
+  }
   for (int64_t t = 0; t < T; ++t) {
     const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
     const int64_t ldh = t == 0 ? H : ldrow;
@@ -589,18 +896,39 @@ FB_API int32_t fb_lstm_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
   float* gates = (float*)cache;              // overwritten in place by the gate derivatives
   const float* cst = gates + rows * 4 * H;
   const int R = 4 * H;
-  const int nparts = (R + DH_R - 1) / DH_R;
+  // one cooperative launch for the whole reverse time loop when its grid can be resident at once
+  const int UBp = (H + DH_U - 1) / DH_U, NPp = R / PB_R, BZp = (B + BC - 1) / BC;
+  const int64_t pgrid = (int64_t)UBp * NPp * BZp;
+  bool persist = T > 1 && (H % 32 == 0) && fb_aligned16(Wh) && fb_aligned16(cache) && pgrid >= 1 && pgrid <= 4096 &&
+                 2 * T * pgrid < 0x7fffffff && persistent_enabled();
+  if (persist) {
+    int per_sm = 0;
+    FB_CUDA(cudaFuncSetAttribute(lstm_bwd_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PB_SMEM));
+    FB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lstm_bwd_persist_kernel, RT, PB_SMEM));
+    persist = (int64_t)per_sm * ctx->sm_count >= pgrid;
+  }
+  const int nparts = persist ? NPp : (R + DH_R - 1) / DH_R;
   float* ws = (float*)fb_scratch(ctx, stream, (size_t)((1 + nparts) * (int64_t)B * H) * sizeof(float));
   if (!ws) return FB_ERR_ALLOC;
   float* dc = ws;                            // [B][H]
   float* parts = ws + (int64_t)B * H;        // [nparts][B][H] partial sums of Wh' * dgates
   if (dcT) FB_CUDA(cudaMemcpyAsync(dc, dcT, (size_t)B * H * sizeof(float), cudaMemcpyDeviceToDevice, stream));
   else FB_CUDA(cudaMemsetAsync(dc, 0, (size_t)B * H * sizeof(float), stream));
+  if (persist) {
+    unsigned* counter = (unsigned*)(ctx->dev_error + 16);
+    FB_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned), stream));
+    int Hi = H, Bi = B, Ti = (int)T, ubi = UBp, npi = NPp;
+    int32_t* dev_err = ctx->dev_error;
+    void* args[] = {(void*)&Wh, (void*)&gates, (void*)&cst, (void*)&c0, (void*)&dout, (void*)&dhT, (void*)&dc, (void*)&parts,
+                    (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&ubi, (void*)&npi, (void*)&counter, (void*)&dev_err};
+    FB_CUDA(cudaLaunchCooperativeKernel((const void*)lstm_bwd_persist_kernel, dim3((unsigned)pgrid), dim3(RT), args, PB_SMEM, stream));
+    FB_LAUNCH_CHECK();
+  }
   FB_CUDA(cudaFuncSetAttribute(rnn_bwd_dh2d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DH2D_SMEM));
   const dim3 grid_dh((unsigned)((H + DH_U - 1) / DH_U), (unsigned)nparts, (unsigned)((B + BC - 1) / BC));
   int64_t eb = ((int64_t)B * H + RT - 1) / RT;
   if (eb > ctx->sm_count * 8) eb = ctx->sm_count * 8;
-  for (int64_t t = T - 1; t >= 0; --t) {
+  for (int64_t t = persist ? -1 : T - 1; t >= 0; --t) {
     float* g_t = gates + t * 4 * H;
     const float* c_prev = t == 0 ? c0 : cst + (t - 1) * H;
     // recurrent dh entering step t: dhT at the last step, the partials of the step after it otherwise
