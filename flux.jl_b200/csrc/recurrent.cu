@@ -460,6 +460,8 @@ lstm_fwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ 
   __syncthreads();
   uint32_t loads = 0;   // bulk loads waited for so far: names the barrier phase
   bool alive = true;
+  float gxv[4] = {0.f, 0.f, 0.f, 0.f};
+  bool have_gx = false;
   for (int t = 0; t < T && alive; ++t) {
     const float* hprev = t == 0 ? h0 : out + (int64_t)(t - 1) * H;
     const int64_t ldh = t == 0 ? H : ldrow;
@@ -493,9 +495,12 @@ lstm_fwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ 
       const int gb = b0 + bb, gu = u0 + u;
       if (gb < B && gu < H) {
         const float* pre = red + bb * 17;
-        const float* gxr = gx_t + (int64_t)gb * ldg;
-        const float zi = pre[u] + gxr[gu], zf = pre[4 + u] + gxr[H + gu];
-        const float zg = pre[8 + u] + gxr[2 * H + gu], zo = pre[12 + u] + gxr[3 * H + gu];
+        if (!have_gx) {
+          const float* gxr = gx_t + (int64_t)gb * ldg;
+          gxv[0] = gxr[gu]; gxv[1] = gxr[H + gu]; gxv[2] = gxr[2 * H + gu]; gxv[3] = gxr[3 * H + gu];
+        }
+        const float zi = pre[u] + gxv[0], zf = pre[4 + u] + gxv[1];
+        const float zg = pre[8 + u] + gxv[2], zo = pre[12 + u] + gxv[3];
         const float ig = 1.0f / (1.0f + expf(-zi)), fg = 1.0f / (1.0f + expf(-zf));
         const float gg = tanhf(zg), og = 1.0f / (1.0f + expf(-zo));
         // c of (gb, gu) was written by this same thread one step earlier
@@ -509,6 +514,16 @@ lstm_fwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ 
         }
         c_t[(int64_t)gb * ldct + gu] = cn;
         if (lastt && hT) { hT[(int64_t)gb * H + gu] = hn; cT[(int64_t)gb * H + gu] = cn; }
+      }
+    }
+    // the input projection of the next step does not depend on the recurrence: fetch it while waiting at the barrier
+    have_gx = false;
+    if (B <= BC && !lastt) {
+      const int gb = threadIdx.x >> 2, gu = u0 + (threadIdx.x & 3);
+      if (gb < B && gu < H) {
+        const float* gxr = gx + (int64_t)(t + 1) * 4 * H + (int64_t)gb * ldg;
+        gxv[0] = gxr[gu]; gxv[1] = gxr[H + gu]; gxv[2] = gxr[2 * H + gu]; gxv[3] = gxr[3 * H + gu];
+        have_gx = true;
       }
     }
     if (alive && !lastt && !grid_barrier(counter, (unsigned)(t + 1) * gridDim.x, dev_err, 3001)) break;
@@ -596,7 +611,7 @@ constexpr size_t DH2D_SMEM = (size_t)2 * DH_U * DH_LD * sizeof(float);
 // Wm[64 ub .. +64][128 rb .. +128] of the recurrent weights in shared memory for all T steps.  A step has two phases
 // separated by grid barriers: (1) every thread turns its (b, u) elements' dh = dout + sum of the partials of the step
 // after into the four gate derivatives (written over the cached gates) and carries dc; (2) every block multiplies
-// its weight tile with its 64 x 128 tile of those derivatives (rows brought in by cp.async.bulk) into the partial sums
+// its weight tile with its 64 x 128 tile of those derivatives into the partial sums
 // part[rb][b][u] that phase 1 of the next step adds up.
 constexpr int PB_R = 128, PB_LD = PB_R + 4;
 constexpr size_t PB_SMEM = (size_t)2 * DH_U * PB_LD * sizeof(float);
@@ -608,8 +623,6 @@ lstm_bwd_persist_kernel(const float* __restrict__ Wh, float* gates, const float*
   extern __shared__ __align__(16) float sm[];
   float* Ws = sm;                   // [64 u][PB_LD]
   float* Ds = Ws + DH_U * PB_LD;    // [64 b][PB_LD]
-  __shared__ __align__(8) uint64_t d_bar;
-  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&d_bar);
   const int R = 4 * H;
   const int ub = blockIdx.x % UB, rb = (blockIdx.x / UB) % NP, bz = blockIdx.x / (UB * NP);
   const int u0 = ub * DH_U, r0 = rb * PB_R, b0 = bz * BC;
@@ -621,16 +634,10 @@ lstm_bwd_persist_kernel(const float* __restrict__ Wh, float* gates, const float*
     *(float4*)(Ws + row * PB_LD + 4 * c4) = w;
     *(float4*)(Ds + row * PB_LD + 4 * c4) = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  if (threadIdx.x == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1u) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
   const int nrows = (B - b0) < BC ? (B - b0) : BC;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   unsigned gen = 0;      // grid barriers passed
-  uint32_t loads = 0;    // bulk loads waited for
   for (int t = T - 1; t >= 0; --t) {
     // ---- phase 1: gate derivatives of step t
     {
@@ -650,7 +657,15 @@ lstm_bwd_persist_kernel(const float* __restrict__ Wh, float* gates, const float*
         if (lastt) {
           if (dhT) dh += dhT[e];
         } else {
-          for (int p = 0; p < NP; ++p) dh += __ldcg(parts + (int64_t)p * total + e);   // written by other blocks
+          // partials written by other blocks: four loads in flight at a time, added in a fixed order
+          const float* pe = parts + e;
+          int p = 0;
+          for (; p + 4 <= NP; p += 4) {
+            const float q0 = __ldcg(pe + (int64_t)p * total), q1 = __ldcg(pe + (int64_t)(p + 1) * total);
+            const float q2 = __ldcg(pe + (int64_t)(p + 2) * total), q3 = __ldcg(pe + (int64_t)(p + 3) * total);
+            dh += (q0 + q1) + (q2 + q3);
+          }
+          for (; p < NP; ++p) dh += __ldcg(pe + (int64_t)p * total);
         }
         const float d_o = dh * tc;
         const float dcc = dc[e] + dh * og * (1.0f - tc * tc);   // dc[e] is carried by this same thread
@@ -665,24 +680,26 @@ lstm_bwd_persist_kernel(const float* __restrict__ Wh, float* gates, const float*
     ++gen;
     if (!grid_barrier(counter, gen * gridDim.x, dev_err, 3003)) break;
     // ---- phase 2: partial sums of Wh' * dgates for step t - 1
-    if (threadIdx.x < 32) {
-      asm volatile("fence.proxy.async;" ::: "memory");   // the derivatives were written through the generic proxy
-      if (threadIdx.x == 0)
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(nrows * PB_R * 4)) : "memory");
-      __syncwarp();
-      for (int r = threadIdx.x; r < nrows; r += 32) {
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Ds + r * PB_LD);
-        const float* src = gates + (int64_t)t * 4 * H + (int64_t)(b0 + r) * ldg + r0;
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                     "r"((uint32_t)(PB_R * 4)), "r"(bar)
-                     : "memory");
+    {
+      // the 64 x 128 tile of derivatives (written by other blocks: read through L2), eight 128-bit loads in flight
+      // per thread
+      constexpr int PER = DH_U * (PB_R / 4) / RT;   // 8
+      float4 v[PER];
+      const float* base = gates + (int64_t)t * 4 * H + r0;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int e = threadIdx.x + i * RT;
+        const int row = e / (PB_R / 4), c4 = e % (PB_R / 4);
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < nrows) v[i] = __ldcg((const float4*)(base + (int64_t)(b0 + row) * ldg + 4 * c4));
       }
-    }
-    const int got = rnn_mbar_wait(bar, loads & 1u) ? 1 : 0;
-    ++loads;
-    if (!__syncthreads_and(got)) {
-      if (threadIdx.x == 0) atomicCAS(dev_err, 0, 3004);
-      break;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int e = threadIdx.x + i * RT;
+        const int row = e / (PB_R / 4), c4 = e % (PB_R / 4);
+        *(float4*)(Ds + row * PB_LD + 4 * c4) = v[i];
+      }
+      __syncthreads();
     }
     float acc[4][4];
 #pragma unroll
