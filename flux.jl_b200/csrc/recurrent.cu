@@ -530,6 +530,66 @@ lstm_fwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ 
   }
 }
 
+// GRU counterpart of lstm_fwd_persist_kernel: block u0/4 keeps its 12 rows of Wh in shared memory for all T steps.
+__global__ void __launch_bounds__(RT)
+gru_fwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, const float* __restrict__ h0, float* out,
+                       float* cch, float* __restrict__ hT, int H, int B, int T, unsigned* counter, int32_t* dev_err) {
+  extern __shared__ __align__(16) float sm[];
+  const int kp = (H + 15) & ~15;
+  float* Ws = sm;
+  float* hs = Ws + 12 * kp;
+  float* red = hs + BC * (kp + 4);
+  const int u0 = blockIdx.x * 4;
+  const int64_t ldrow = (int64_t)T * H, ldgx = (int64_t)T * 3 * H, ldc = (int64_t)T * 4 * H;
+  __shared__ __align__(8) uint64_t h_bar;
+  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&h_bar);
+  for (int e = threadIdx.x; e < BC * (kp + 4); e += RT) hs[e] = 0.0f;
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  uint32_t loads = 0;
+  bool alive = true;
+  for (int t = 0; t < T && alive; ++t) {
+    const float* hprev = t == 0 ? h0 : out + (int64_t)(t - 1) * H;
+    const int64_t ldh = t == 0 ? H : ldrow;
+    const float* gx_t = gx + (int64_t)t * 3 * H;
+    float* out_t = out + (int64_t)t * H;
+    float* c_t = cch ? cch + (int64_t)t * 4 * H : nullptr;
+    const bool lastt = (t == T - 1);
+    for (int b0 = 0; b0 < B; b0 += BC) {
+      if (b0 > 0) __syncthreads();
+      if (!fast_gate_preacts<3, true>(Wh, hprev, ldh, H, B, b0, u0, kp, Ws, hs, red, t == 0 && b0 == 0, bar, loads & 1u)) {
+        if (threadIdx.x == 0) atomicCAS(dev_err, 0, 3002);
+        alive = false;
+        break;
+      }
+      if (hprev != nullptr) ++loads;
+      const int bb = threadIdx.x >> 2, u = threadIdx.x & 3;
+      const int gb = b0 + bb, gu = u0 + u;
+      if (gb < B && gu < H) {
+        const float* pre = red + bb * 13;
+        const float* gxr = gx_t + (int64_t)gb * ldgx;   // includes the bias
+        const float gh3 = pre[8 + u];
+        const float r = 1.0f / (1.0f + expf(-(gxr[gu] + pre[u])));
+        const float z = 1.0f / (1.0f + expf(-(gxr[H + gu] + pre[4 + u])));
+        const float hc = tanhf(gxr[2 * H + gu] + r * gh3);
+        const float hp = hprev ? hs[bb * (kp + 4) + gu] : 0.0f;   // the staged row of h_{t-1}
+        const float hn = (1.0f - z) * hc + z * hp;
+        out_t[(int64_t)gb * ldrow + gu] = hn;
+        if (c_t) {
+          float* cr = c_t + (int64_t)gb * ldc;
+          cr[gu] = r; cr[H + gu] = z; cr[2 * H + gu] = hc; cr[3 * H + gu] = gh3;
+        }
+        if (lastt && hT) hT[(int64_t)gb * H + gu] = hn;
+      }
+    }
+    if (alive && !lastt && !grid_barrier(counter, (unsigned)(t + 1) * gridDim.x, dev_err, 3001)) break;
+  }
+}
+
 size_t fast_fwd_smem(int ng, int H) {
   const int kp = (H + 15) & ~15;
   return (size_t)(ng * 4 * kp + BC * (kp + 4) + 4 * BC * (ng * 4 + 1)) * sizeof(float);
@@ -1032,6 +1092,23 @@ FB_API int32_t fb_gru_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
   if (fast) FB_CUDA(cudaFuncSetAttribute(gru_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
+  if (fast && T > 1 && T * (int64_t)grid < 0x7fffffff && persistent_enabled()) {
+    // one cooperative launch for the whole sequence when every block can be resident at once
+    int per_sm = 0;
+    FB_CUDA(cudaFuncSetAttribute(gru_fwd_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gru_fwd_persist_kernel, RT, smem));
+    if ((int64_t)per_sm * ctx->sm_count >= (int64_t)grid) {
+      unsigned* counter = (unsigned*)(ctx->dev_error + 16);
+      FB_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned), stream));
+      int Hi = H, Bi = B, Ti = (int)T;
+      int32_t* dev_err = ctx->dev_error;
+      void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&out, (void*)&cch, (void*)&hT, (void*)&Hi, (void*)&Bi, (void*)&Ti,
+                      (void*)&counter, (void*)&dev_err};
+      FB_CUDA(cudaLaunchCooperativeKernel((const void*)gru_fwd_persist_kernel, dim3(grid), dim3(RT), args, smem, stream));
+      FB_LAUNCH_CHECK();
+      return FB_OK;
+    }
+  }
   for (int64_t t = 0; t < T; ++t) {
     const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
     const int64_t ldh = t == 0 ? H : ldrow;
