@@ -440,6 +440,9 @@ FB_API int32_t fb_attn_fwd(fb_ctx* ctx, void* stream_, const float* q, const flo
   if (st != FB_OK) return st;
   if (lq == 0 || batch == 0) return FB_OK;
   FB_REQUIRE(q && k && v && o && lse, FB_ERR_INVALID_ARG, "fb_attn_fwd: NULL pointer");
+  // head size 64 without an explicit mask runs on the tensor cores
+  st = fb_attn_fwd_tc(ctx, stream, q, k, v, mask, o, lse, e_dim, ev_dim, lq, lk, batch, nheads, causal);
+  if (st != FB_ERR_UNSUPPORTED) return st;
   const int nc = (D.d > 64 || D.dv > 64) ? 2 : 1;
   const size_t smem = (size_t)(3 * TS * (nc * 64 + 4) + TS * PLD) * sizeof(float);
   dim3 grid((unsigned)((lq + TS - 1) / TS), (unsigned)nheads, (unsigned)batch);

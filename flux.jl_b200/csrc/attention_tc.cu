@@ -1,0 +1,331 @@
+// Flash-style attention forward on the tensor cores for Float32 data (head size 64): S = Q K' and O += P V are
+// tcgen05 TF32 MMAs with the error-compensated 3-pass split (hi / lo operands), the online softmax runs on the
+// accumulator read back from tensor memory, and no L x L array ever exists in HBM.
+//
+// One CTA owns 128 queries of one (batch, head) and walks the keys in blocks of 64:
+//   warp 0      TMA producer: the Q tile once, then a K and a V tile per block (single-buffered; a tile is reloaded
+//               as soon as the MMAs that read it have completed)
+//   warp 1      owns tensor memory (128 columns: S in 0..63, P V in 64..127) and issues the MMAs
+//   warps 2-5   softmax: thread = one query row (its TMEM lane).  Reads S, keeps the running maximum and sum,
+//               writes P (raw value = hi operand, and lo = p - tf32(p)) to shared memory in the K-major 64-byte
+//               swizzled layout the MMA descriptor names, then adds P V (read back from tensor memory) to its
+//               64 output accumulators with round-to-nearest adds
+//   warps 6-9   split warps: write the lo = x - tf32(x) twin of every Q / K / V tile beside the raw tile
+//
+// Shared-memory tiles use the layouts already proven by the GEMM: K-major chunks of 16 floats with the 64-byte
+// swizzle for Q, K and P; the 128-byte swizzle with 32-byte atoms for the MN-major V tile (keys are its K rows).
+// Every mbarrier wait is bounded; when one runs out the kernel records 4001 in the context's device error word,
+// all roles leave their loops, tensor memory is released and the kernel returns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int QT = 128;   // queries per CTA
+constexpr int KT = 64;    // keys per block
+constexpr int HD = 64;    // head size (q/k features and v features per head)
+constexpr int ATC_THREADS = 320;
+
+// byte offsets inside the 1024-byte aligned dynamic shared memory
+constexpr int OFF_QHI = 0, OFF_QLO = 32768;              // 4 chunks x [128 rows][16 floats]
+constexpr int OFF_KHI = 65536, OFF_KLO = 81920;          // 4 chunks x [64 rows][16 floats]
+constexpr int OFF_VHI = 98304, OFF_VLO = 114688;         // 2 chunks x [64 key rows][32 floats]
+constexpr int OFF_PHI = 131072, OFF_PLO = 163840;        // 4 chunks x [128 rows][16 floats]
+constexpr int OFF_BAR = 196608;
+constexpr int ATC_SMEM = OFF_BAR + 256 + 1024;           // barriers + alignment slack
+
+enum { B_QFULL = 0, B_QREADY, B_KFULL, B_KREADY, B_KFREE, B_VFULL, B_VREADY, B_VFREE, B_SFULL, B_PREADY, B_OFULL, B_COUNT };
+
+struct AtcDims {
+  int64_t E, Ev, Lq, Lk;
+  int H, causal;
+  float scale_log2;   // log2(e) / sqrt(d)
+  float scale;        // 1 / sqrt(d)
+};
+
+__global__ void __launch_bounds__(ATC_THREADS, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, float* __restrict__ o, float* __restrict__ lse, AtcDims D,
+                   int32_t* __restrict__ dev_err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar0 = sb + OFF_BAR;
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  volatile uint32_t* s_tmem = (volatile uint32_t*)(smem + OFF_BAR + 8 * B_COUNT);
+  volatile int* s_abort = (volatile int*)(smem + OFF_BAR + 8 * B_COUNT + 8);
+  volatile int* s_skip = (volatile int*)(smem + OFF_BAR + 8 * B_COUNT + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t i0 = (int64_t)blockIdx.x * QT;
+  const int h = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  int64_t kv_end = D.Lk;
+  if (D.causal && i0 + QT < kv_end) kv_end = i0 + QT;
+  const int nkb = (int)((kv_end + KT - 1) / KT);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(B_QFULL), 1);
+    mbar_init(bar(B_QREADY), 4);
+    mbar_init(bar(B_KFULL), 1);
+    mbar_init(bar(B_KREADY), 4);
+    mbar_init(bar(B_KFREE), 1);
+    mbar_init(bar(B_VFULL), 1);
+    mbar_init(bar(B_VREADY), 4);
+    mbar_init(bar(B_VFREE), 1);
+    mbar_init(bar(B_SFULL), 1);
+    mbar_init(bar(B_PREADY), 4);
+    mbar_init(bar(B_OFULL), 1);
+    *s_abort = 0;
+    *s_skip = (*(volatile int32_t*)dev_err != 0) ? 1 : 0;   // an error word left set means: do not start
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (*s_skip != 0) return;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)), "r"(128u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer ---
+    if (lane == 0) {
+      const int qrow = (int)(b * D.Lq + i0), krow0 = (int)(b * D.Lk);
+      mbar_arrive_expect_tx(bar(B_QFULL), 32768u);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tma_load_2d(sb + OFF_QHI + c * 8192, &tmQ, h * HD + 16 * c, qrow, bar(B_QFULL));
+      for (int j = 0; j < nkb; ++j) {
+        if (j > 0 && !mbar_wait(bar(B_KFREE), (uint32_t)(j - 1) & 1u, s_abort)) break;
+        mbar_arrive_expect_tx(bar(B_KFULL), 16384u);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tma_load_2d(sb + OFF_KHI + c * 4096, &tmK, h * HD + 16 * c, krow0 + j * KT, bar(B_KFULL));
+        if (j > 0 && !mbar_wait(bar(B_VFREE), (uint32_t)(j - 1) & 1u, s_abort)) break;
+        mbar_arrive_expect_tx(bar(B_VFULL), 16384u);
+        tma_load_3d(sb + OFF_VHI, &tmV, 0, krow0 + j * KT, 2 * h, bar(B_VFULL));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer ---
+    if (lane == 0) {
+      const uint32_t idesc_qk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(KT >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
+      const uint32_t idesc_pv = idesc_qk | (1u << 16);   // B = V is MN-major; N = 64 value features
+      bool ok = mbar_wait(bar(B_QREADY), 0u, s_abort);
+      for (int j = 0; j < nkb && ok; ++j) {
+        const uint32_t ph = (uint32_t)j & 1u;
+        ok = mbar_wait(bar(B_KREADY), ph, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        // S = Q K' (contraction over the 64 features: 4 chunks x 2 k-steps of 8)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t qo = (uint32_t)((ks >> 1) * 8192 + (ks & 1) * 32), ko = (uint32_t)((ks >> 1) * 4096 + (ks & 1) * 32);
+          const uint64_t q_hi = make_smem_desc(sb + OFF_QHI + qo, 16, 512, LAYOUT_SW64);
+          const uint64_t q_lo = make_smem_desc(sb + OFF_QLO + qo, 16, 512, LAYOUT_SW64);
+          const uint64_t k_hi = make_smem_desc(sb + OFF_KHI + ko, 16, 512, LAYOUT_SW64);
+          const uint64_t k_lo = make_smem_desc(sb + OFF_KLO + ko, 16, 512, LAYOUT_SW64);
+          tc_mma_tf32(tmem_base, q_lo, k_hi, idesc_qk, ks > 0 ? 1u : 0u);
+          tc_mma_tf32(tmem_base, q_hi, k_lo, idesc_qk, 1u);
+          tc_mma_tf32(tmem_base, q_hi, k_hi, idesc_qk, 1u);
+        }
+        tc_commit(bar(B_SFULL));
+        tc_commit(bar(B_KFREE));
+        ok = mbar_wait(bar(B_PREADY), ph, s_abort) && mbar_wait(bar(B_VREADY), ph, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        // P V (contraction over the 64 keys: 8 k-steps of 8; P chunk = 16 keys)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t po = (uint32_t)((ks >> 1) * 8192 + (ks & 1) * 32), vo = (uint32_t)(ks * 1024);
+          const uint64_t p_hi = make_smem_desc(sb + OFF_PHI + po, 16, 512, LAYOUT_SW64);
+          const uint64_t p_lo = make_smem_desc(sb + OFF_PLO + po, 16, 512, LAYOUT_SW64);
+          const uint64_t v_hi = make_smem_desc(sb + OFF_VHI + vo, KT * 128, 512, LAYOUT_SW128_32B);
+          const uint64_t v_lo = make_smem_desc(sb + OFF_VLO + vo, KT * 128, 512, LAYOUT_SW128_32B);
+          tc_mma_tf32(tmem_base + 64u, p_lo, v_hi, idesc_pv, ks > 0 ? 1u : 0u);
+          tc_mma_tf32(tmem_base + 64u, p_hi, v_lo, idesc_pv, 1u);
+          tc_mma_tf32(tmem_base + 64u, p_hi, v_hi, idesc_pv, 1u);
+        }
+        tc_commit(bar(B_OFULL));
+        tc_commit(bar(B_VFREE));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ softmax warps ---
+    const int q = warp & 3;                  // TMEM lane quadrant of this warp
+    const int row = 32 * q + lane;           // query row inside the tile = TMEM lane
+    const int64_t gi = i0 + row;
+    const uint32_t t_row = tmem_base + ((uint32_t)(32 * q) << 16);
+    float m = -INFINITY, l = 0.0f;
+    float acc[HD];
+#pragma unroll
+    for (int c = 0; c < HD; ++c) acc[c] = 0.0f;
+    const uint32_t sw = (uint32_t)((row >> 1) & 3);
+    bool ok = true;
+    for (int j = 0; j < nkb && ok; ++j) {
+      const uint32_t ph = (uint32_t)j & 1u;
+      const int64_t j0 = (int64_t)j * KT;
+      ok = mbar_wait(bar(B_SFULL), ph, s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s0[32], s1[32];
+      tc_ld_32x32b_x32(t_row, s0);
+      tc_ld_32x32b_x32(t_row + 32u, s1);
+      tc_wait_ld();
+      // keys this query may see in this block: key < Lk, and key <= query when causal
+      int64_t lim = D.Lk - j0;
+      if (D.causal && gi - j0 + 1 < lim) lim = gi - j0 + 1;
+      const int nvalid = lim < 0 ? 0 : (lim > KT ? KT : (int)lim);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        if (c < nvalid) mx = fmaxf(mx, __uint_as_float(s0[c]));
+        if (c + 32 < nvalid) mx = fmaxf(mx, __uint_as_float(s1[c]));
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = exp2f((m - m_use) * D.scale_log2);   // m = -inf gives 0
+      float rs = 0.0f;
+      // P in the K-major 64-byte swizzled layout: chunk = key / 16, 16-byte piece (key % 16) / 4 XOR (row / 2) % 4
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        float p[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = 4 * g + e;
+          const float sv = __uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]);
+          p[e] = (c < nvalid) ? exp2f((sv - m_use) * D.scale_log2) : 0.0f;
+          rs += p[e];
+        }
+        const uint32_t off = (uint32_t)((g >> 2) * 8192 + row * 64) + ((((uint32_t)g & 3u) ^ sw) << 4);
+        *(float4*)(smem + OFF_PHI + off) = make_float4(p[0], p[1], p[2], p[3]);
+        *(float4*)(smem + OFF_PLO + off) = make_float4(tf32_lo(p[0]), tf32_lo(p[1]), tf32_lo(p[2]), tf32_lo(p[3]));
+      }
+      fence_proxy_async();   // P becomes visible to the tensor core's async-proxy reads
+      tc_fence_before();     // the reads of S (and of the previous block's P V) precede the arrive
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PREADY));
+      l = l * alpha + rs;
+      m = m_new;
+#pragma unroll
+      for (int c = 0; c < HD; ++c) acc[c] *= alpha;
+      ok = mbar_wait(bar(B_OFULL), ph, s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      tc_ld_32x32b_x32(t_row + 64u, s0);
+      tc_ld_32x32b_x32(t_row + 96u, s1);
+      tc_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        acc[c] += __uint_as_float(s0[c]);
+        acc[c + 32] += __uint_as_float(s1[c]);
+      }
+    }
+    if (ok && gi < D.Lq) {
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      float* orow = o + (b * D.Lq + gi) * D.Ev + (int64_t)h * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 4)
+        *(float4*)(orow + c) = make_float4(acc[c] * inv, acc[c + 1] * inv, acc[c + 2] * inv, acc[c + 3] * inv);
+      // the running maximum is of unscaled scores
+      lse[(b * D.H + h) * D.Lq + gi] = (l > 0.0f) ? m * D.scale + logf(l) : -INFINITY;
+    }
+  } else {
+    // --------------------------------------------- split warps: lo = x - tf32(x) twins ---
+    const int tt = (warp - 6) * 32 + lane;   // 0..127
+    auto split = [&](int off_hi, int off_lo, int n16) {   // n16 = 16-byte pieces per thread
+      const float4* hi = (const float4*)(smem + off_hi);
+      float4* lo = (float4*)(smem + off_lo);
+      for (int i = 0; i < n16; ++i) {
+        float4 v = hi[tt + i * 128];
+        v.x = tf32_lo(v.x); v.y = tf32_lo(v.y); v.z = tf32_lo(v.z); v.w = tf32_lo(v.w);
+        lo[tt + i * 128] = v;
+      }
+      fence_proxy_async();
+      __syncwarp();
+    };
+    bool ok = mbar_wait(bar(B_QFULL), 0u, s_abort);
+    if (ok) {
+      split(OFF_QHI, OFF_QLO, 16);
+      if (lane == 0) mbar_arrive(bar(B_QREADY));
+    }
+    for (int j = 0; j < nkb && ok; ++j) {
+      const uint32_t ph = (uint32_t)j & 1u;
+      ok = mbar_wait(bar(B_KFULL), ph, s_abort);
+      if (!ok) break;
+      split(OFF_KHI, OFF_KLO, 8);
+      if (lane == 0) mbar_arrive(bar(B_KREADY));
+      ok = mbar_wait(bar(B_VFULL), ph, s_abort);
+      if (!ok) break;
+      split(OFF_VHI, OFF_VLO, 8);
+      if (lane == 0) mbar_arrive(bar(B_VREADY));
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown ---
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+  }
+  if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4001);
+}
+
+// FLUXB200_ATTN_TC = 0 keeps attention on the Float32 FMA kernels.
+bool attn_tc_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUXB200_ATTN_TC");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+// 3-d view {32, rows, cols / 32} of a row-major [rows][cols] matrix whose rows are the K dimension of an MN-major
+// operand: box {32, box_rows, chunks}.
+bool encode_rows3d(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, uint32_t box_rows, uint32_t chunks) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn || cols % 32 != 0) return false;
+  cuuint64_t gdim[3] = {32, (cuuint64_t)rows, (cuuint64_t)(cols / 32)};
+  cuuint64_t gstride[2] = {(cuuint64_t)cols * sizeof(float), 128};
+  cuuint32_t box[3] = {32, box_rows, chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// Returns FB_ERR_UNSUPPORTED when the shape is not one this kernel takes (the caller then uses the FMA kernels).
+int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const float* k, const float* v, const uint8_t* mask,
+                       float* o, float* lse, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch, int nheads,
+                       int causal) {
+  if (!attn_tc_enabled() || mask != nullptr || nheads < 1) return FB_ERR_UNSUPPORTED;
+  if (e_dim != (int64_t)nheads * HD || ev_dim != (int64_t)nheads * HD) return FB_ERR_UNSUPPORTED;
+  if (lq < 1 || lk < 1 || batch < 1 || batch * lq > 0x7fffff00 || batch * lk > 0x7fffff00 || batch > 65535 || nheads > 65535)
+    return FB_ERR_UNSUPPORTED;
+  if (!fb_aligned16(q) || !fb_aligned16(k) || !fb_aligned16(v) || !fb_aligned16(o)) return FB_ERR_UNSUPPORTED;
+  CUtensorMap tmQ, tmK, tmV;
+  if (!encode_map(&tmQ, q, batch * lq, e_dim, e_dim, 16, QT, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      !encode_map(&tmK, k, batch * lk, e_dim, e_dim, 16, KT, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      !encode_rows3d(&tmV, v, batch * lk, ev_dim, KT, HD / 32))
+    return FB_ERR_UNSUPPORTED;
+  AtcDims D;
+  D.E = e_dim; D.Ev = ev_dim; D.Lq = lq; D.Lk = lk; D.H = nheads; D.causal = causal ? 1 : 0;
+  D.scale = 1.0f / sqrtf((float)HD);
+  D.scale_log2 = D.scale * 1.4426950408889634f;
+  FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+  dim3 grid((unsigned)((lq + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
+  attn_fwd_tc_kernel<<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}

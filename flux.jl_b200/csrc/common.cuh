@@ -184,6 +184,10 @@ int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& 
 bool fb_gemm_tc_supported(const fb_gemm_args& a);
 int32_t fb_gemm_dispatch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a, int precision);
 void fb_tmap_cache_destroy(fb_ctx* ctx);
+// attention_tc.cu: tensor-core attention forward; FB_ERR_UNSUPPORTED when the shape is not taken
+int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const float* k, const float* v, const uint8_t* mask,
+                       float* o, float* lse, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch, int nheads,
+                       int causal);
 int32_t fb_gemm_workspace_create(fb_ctx* ctx);
 void fb_gemm_workspace_reset(fb_ctx* ctx, cudaStream_t stream);
 
