@@ -39,6 +39,36 @@ constexpr int ATC_SMEM = OFF_BAR + 256 + 1024;           // barriers + alignment
 
 enum { B_QFULL = 0, B_QREADY, B_KFULL, B_KREADY, B_KFREE, B_VFULL, B_VREADY, B_VFREE, B_SFULL, B_PREADY, B_OFULL, B_COUNT };
 
+__device__ __forceinline__ void tc_st_32x32b_x32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+      "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A tile (128 rows x 8 TF32 values) sits in 8 consecutive TMEM columns
+__device__ __forceinline__ void tc_mma_tf32_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+
+// 2^x by the special-function unit (relative error ~2^-22, far inside the tolerance of a softmax weight)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AtcDims {
   int64_t E, Ev, Lq, Lk;
   int H, causal;
@@ -46,6 +76,9 @@ struct AtcDims {
   float scale;        // 1 / sqrt(d)
 };
 
+// P_TMEM: the softmax warps put P (hi in place of S, lo in columns 128..191) into tensor memory and P V takes its A
+// operand from there, instead of staging P in shared memory.
+template <bool P_TMEM>
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, float* __restrict__ o, float* __restrict__ lse, AtcDims D,
@@ -87,7 +120,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   if (*s_skip != 0) return;
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)), "r"(128u)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)),
+                 "r"(P_TMEM ? 256u : 128u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -149,9 +183,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const uint64_t p_lo = make_smem_desc(sb + OFF_PLO + po, 16, 512, LAYOUT_SW64);
           const uint64_t v_hi = make_smem_desc(sb + OFF_VHI + vo, KT * 128, 512, LAYOUT_SW128_32B);
           const uint64_t v_lo = make_smem_desc(sb + OFF_VLO + vo, KT * 128, 512, LAYOUT_SW128_32B);
-          tc_mma_tf32(tmem_base + 64u, p_lo, v_hi, idesc_pv, ks > 0 ? 1u : 0u);
-          tc_mma_tf32(tmem_base + 64u, p_hi, v_lo, idesc_pv, 1u);
-          tc_mma_tf32(tmem_base + 64u, p_hi, v_hi, idesc_pv, 1u);
+          if (P_TMEM) {
+            const uint32_t a_hi = tmem_base + (uint32_t)(8 * ks), a_lo = tmem_base + 128u + (uint32_t)(8 * ks);
+            tc_mma_tf32_ta(tmem_base + 64u, a_lo, v_hi, idesc_pv, ks > 0 ? 1u : 0u);
+            tc_mma_tf32_ta(tmem_base + 64u, a_hi, v_lo, idesc_pv, 1u);
+            tc_mma_tf32_ta(tmem_base + 64u, a_hi, v_hi, idesc_pv, 1u);
+          } else {
+            tc_mma_tf32(tmem_base + 64u, p_lo, v_hi, idesc_pv, ks > 0 ? 1u : 0u);
+            tc_mma_tf32(tmem_base + 64u, p_hi, v_lo, idesc_pv, 1u);
+            tc_mma_tf32(tmem_base + 64u, p_hi, v_hi, idesc_pv, 1u);
+          }
         }
         tc_commit(bar(B_OFULL));
         tc_commit(bar(B_VFREE));
@@ -193,6 +234,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = exp2f((m - m_use) * D.scale_log2);   // m = -inf gives 0
       float rs = 0.0f;
+      if (P_TMEM) {
+        // P over S in place (the raw value is the hi operand), its lo part in columns 128..191
+        uint32_t lo0[32], lo1[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p0 = (c < nvalid) ? exp2f((__uint_as_float(s0[c]) - m_use) * D.scale_log2) : 0.0f;
+          const float p1 = (c + 32 < nvalid) ? exp2f((__uint_as_float(s1[c]) - m_use) * D.scale_log2) : 0.0f;
+          rs += p0 + p1;
+          s0[c] = __float_as_uint(p0); s1[c] = __float_as_uint(p1);
+          lo0[c] = __float_as_uint(tf32_lo(p0)); lo1[c] = __float_as_uint(tf32_lo(p1));
+        }
+        tc_st_32x32b_x32(t_row, s0);
+        tc_st_32x32b_x32(t_row + 32u, s1);
+        tc_st_32x32b_x32(t_row + 128u, lo0);
+        tc_st_32x32b_x32(t_row + 160u, lo1);
+        tc_wait_st();
+      } else {
       // P in the K-major 64-byte swizzled layout: chunk = key / 16, 16-byte piece (key % 16) / 4 XOR (row / 2) % 4
 #pragma unroll
       for (int g = 0; g < 16; ++g) {
@@ -207,6 +265,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t off = (uint32_t)((g >> 2) * 8192 + row * 64) + ((((uint32_t)g & 3u) ^ sw) << 4);
         *(float4*)(smem + OFF_PHI + off) = make_float4(p[0], p[1], p[2], p[3]);
         *(float4*)(smem + OFF_PLO + off) = make_float4(tf32_lo(p[0]), tf32_lo(p[1]), tf32_lo(p[2]), tf32_lo(p[3]));
+      }
       }
       fence_proxy_async();   // P becomes visible to the tensor core's async-proxy reads
       tc_fence_before();     // the reads of S (and of the previous block's P V) precede the arrive
@@ -274,9 +333,295 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P_TMEM ? 256u : 128u) : "memory");
   }
   if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4001);
+}
+
+// Pipelined variant: two K / V stages in shared memory and, in tensor memory, two S buffers (P hi overwrites S in
+// place), two P lo buffers and two P V buffers.  The MMA warp issues Q K' of block j + 1 before P V of block j, so the
+// tensor pipe works on the next scores while the softmax warps are busy with the current ones; the softmax warps add
+// P V of block j - 1 after they have handed P of block j to the tensor core.
+//   TMEM columns: S/P_hi 0..63, 64..127; P_lo 128..191, 192..255; P V 256..319, 320..383 (512 allocated)
+constexpr int P2_QHI = 0, P2_QLO = 32768;
+constexpr int P2_STAGE0 = 65536, P2_STAGE_BYTES = 65536;      // per stage: K hi, K lo, V hi, V lo (16 KB each)
+constexpr int P2_BAR = P2_STAGE0 + 2 * P2_STAGE_BYTES;        // 196608
+constexpr int ATC2_SMEM = P2_BAR + 256 + 1024;
+enum { C_QFULL = 0, C_QREADY, C_KFULL, C_KREADY = C_KFULL + 2, C_KFREE = C_KREADY + 2, C_VFULL = C_KFREE + 2, C_VREADY = C_VFULL + 2,
+       C_VFREE = C_VREADY + 2, C_SFULL = C_VFREE + 2, C_PREADY = C_SFULL + 2, C_OFULL = C_PREADY + 2, C_COUNT = C_OFULL + 2 };
+
+__global__ void __launch_bounds__(ATC_THREADS, 1)
+attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, float* __restrict__ o, float* __restrict__ lse, AtcDims D,
+                    int32_t* __restrict__ dev_err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar0 = sb + P2_BAR;
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  volatile uint32_t* s_tmem = (volatile uint32_t*)(smem + P2_BAR + 8 * C_COUNT);
+  volatile int* s_abort = (volatile int*)(smem + P2_BAR + 8 * C_COUNT + 8);
+  volatile int* s_skip = (volatile int*)(smem + P2_BAR + 8 * C_COUNT + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t i0 = (int64_t)blockIdx.x * QT;
+  const int h = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  int64_t kv_end = D.Lk;
+  if (D.causal && i0 + QT < kv_end) kv_end = i0 + QT;
+  const int nkb = (int)((kv_end + KT - 1) / KT);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(C_QFULL), 1);
+    mbar_init(bar(C_QREADY), 4);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(bar(C_KFULL + st), 1);
+      mbar_init(bar(C_KREADY + st), 4);
+      mbar_init(bar(C_KFREE + st), 1);
+      mbar_init(bar(C_VFULL + st), 1);
+      mbar_init(bar(C_VREADY + st), 4);
+      mbar_init(bar(C_VFREE + st), 1);
+      mbar_init(bar(C_SFULL + st), 1);
+      mbar_init(bar(C_PREADY + st), 4);
+      mbar_init(bar(C_OFULL + st), 1);
+    }
+    *s_abort = 0;
+    *s_skip = (*(volatile int32_t*)dev_err != 0) ? 1 : 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (*s_skip != 0) return;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+  // block j uses stage / buffer j & 1 for the (j >> 1)-th time: barrier parity (j >> 1) & 1
+  auto par = [](int j) { return (uint32_t)(j >> 1) & 1u; };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer ---
+    if (lane == 0) {
+      const int qrow = (int)(b * D.Lq + i0), krow0 = (int)(b * D.Lk);
+      mbar_arrive_expect_tx(bar(C_QFULL), 32768u);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tma_load_2d(sb + P2_QHI + c * 8192, &tmQ, h * HD + 16 * c, qrow, bar(C_QFULL));
+      for (int j = 0; j < nkb; ++j) {
+        const int st = j & 1;
+        const uint32_t base = sb + P2_STAGE0 + (uint32_t)(st * P2_STAGE_BYTES);
+        if (j >= 2 && !mbar_wait(bar(C_KFREE + st), par(j - 2), s_abort)) break;
+        mbar_arrive_expect_tx(bar(C_KFULL + st), 16384u);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tma_load_2d(base + c * 4096, &tmK, h * HD + 16 * c, krow0 + j * KT, bar(C_KFULL + st));
+        if (j >= 2 && !mbar_wait(bar(C_VFREE + st), par(j - 2), s_abort)) break;
+        mbar_arrive_expect_tx(bar(C_VFULL + st), 16384u);
+        tma_load_3d(base + 32768, &tmV, 0, krow0 + j * KT, 2 * h, bar(C_VFULL + st));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer ---
+    if (lane == 0) {
+      const uint32_t idesc_qk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(KT >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
+      const uint32_t idesc_pv = idesc_qk | (1u << 16);
+      // descriptors differ only in their 14-bit start-address field (units of 16 bytes): build one per tile and add
+      // the per-k-step offsets, so that issuing an MMA costs a couple of integer adds
+      const uint64_t dq_hi = make_smem_desc(sb + P2_QHI, 16, 512, LAYOUT_SW64), dq_lo = make_smem_desc(sb + P2_QLO, 16, 512, LAYOUT_SW64);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(bar(C_KREADY + st), par(j), s_abort)) return false;
+        tc_fence_after();
+        const uint32_t kb = sb + P2_STAGE0 + (uint32_t)(st * P2_STAGE_BYTES);
+        const uint64_t dk_hi = make_smem_desc(kb, 16, 512, LAYOUT_SW64), dk_lo = make_smem_desc(kb + 16384, 16, 512, LAYOUT_SW64);
+        const uint32_t d = tmem_base + (uint32_t)(64 * st);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t qo = (uint64_t)(((ks >> 1) * 8192 + (ks & 1) * 32) >> 4), ko = (uint64_t)(((ks >> 1) * 4096 + (ks & 1) * 32) >> 4);
+          tc_mma_tf32(d, dq_lo + qo, dk_hi + ko, idesc_qk, ks > 0 ? 1u : 0u);
+          tc_mma_tf32(d, dq_hi + qo, dk_lo + ko, idesc_qk, 1u);
+          tc_mma_tf32(d, dq_hi + qo, dk_hi + ko, idesc_qk, 1u);
+        }
+        tc_commit(bar(C_SFULL + st));
+        tc_commit(bar(C_KFREE + st));
+        return true;
+      };
+      bool ok = mbar_wait(bar(C_QREADY), 0u, s_abort);
+      ok = ok && issue_qk(0);
+      for (int j = 0; j < nkb && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < nkb) {
+          ok = issue_qk(j + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(bar(C_PREADY + st), par(j), s_abort) && mbar_wait(bar(C_VREADY + st), par(j), s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t vb = sb + P2_STAGE0 + (uint32_t)(st * P2_STAGE_BYTES) + 32768;
+        const uint32_t d = tmem_base + 256u + (uint32_t)(64 * st);
+        const uint64_t dv_hi = make_smem_desc(vb, KT * 128, 512, LAYOUT_SW128_32B);
+        const uint64_t dv_lo = make_smem_desc(vb + 16384, KT * 128, 512, LAYOUT_SW128_32B);
+        const uint32_t a_hi0 = tmem_base + (uint32_t)(64 * st), a_lo0 = a_hi0 + 128u;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t vo = (uint64_t)((ks * 1024) >> 4);
+          tc_mma_tf32_ta(d, a_lo0 + (uint32_t)(8 * ks), dv_hi + vo, idesc_pv, ks > 0 ? 1u : 0u);
+          tc_mma_tf32_ta(d, a_hi0 + (uint32_t)(8 * ks), dv_lo + vo, idesc_pv, 1u);
+          tc_mma_tf32_ta(d, a_hi0 + (uint32_t)(8 * ks), dv_hi + vo, idesc_pv, 1u);
+        }
+        tc_commit(bar(C_OFULL + st));
+        tc_commit(bar(C_VFREE + st));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ softmax warps ---
+    const int q = warp & 3;
+    const int row = 32 * q + lane;
+    const int64_t gi = i0 + row;
+    const uint32_t t_row = tmem_base + ((uint32_t)(32 * q) << 16);
+    float m = -INFINITY, l = 0.0f;
+    float acc[HD];
+#pragma unroll
+    for (int c = 0; c < HD; ++c) acc[c] = 0.0f;
+    bool ok = true;
+    // adds P V of block jj to the accumulators (waits for its MMAs)
+    auto add_pv = [&](int jj) -> bool {
+      const int st = jj & 1;
+      if (!mbar_wait(bar(C_OFULL + st), par(jj), s_abort)) return false;
+      tc_fence_after();
+      uint32_t v0[32], v1[32];
+      tc_ld_32x32b_x32(t_row + 256u + (uint32_t)(64 * st), v0);
+      tc_ld_32x32b_x32(t_row + 288u + (uint32_t)(64 * st), v1);
+      tc_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        acc[c] += __uint_as_float(v0[c]);
+        acc[c + 32] += __uint_as_float(v1[c]);
+      }
+      return true;
+    };
+    for (int j = 0; j < nkb && ok; ++j) {
+      const int st = j & 1;
+      const int64_t j0 = (int64_t)j * KT;
+      ok = mbar_wait(bar(C_SFULL + st), par(j), s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s0[32], s1[32];
+      const uint32_t t_s = t_row + (uint32_t)(64 * st);
+      tc_ld_32x32b_x32(t_s, s0);
+      tc_ld_32x32b_x32(t_s + 32u, s1);
+      tc_wait_ld();
+      int64_t lim = D.Lk - j0;
+      if (D.causal && gi - j0 + 1 < lim) lim = gi - j0 + 1;
+      const int nvalid = lim < 0 ? 0 : (lim > KT ? KT : (int)lim);
+      // keys the query may not see get a score of -inf (whole blocks below the diagonal need no test)
+      if (nvalid < KT) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (c >= nvalid) s0[c] = 0xff800000u;
+          if (c + 32 >= nvalid) s1[c] = 0xff800000u;
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(s1[c]));
+      }
+      const float m_new = fmaxf(m, fmaxf(mx0, mx1));
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = fast_exp2((m - m_use) * D.scale_log2);   // m = -inf gives 0
+      const float mc = m_use * D.scale_log2;
+      float rs0 = 0.0f, rs1 = 0.0f;
+      {
+        // P = 2^(s c - m c) over S in place (the raw value is the hi operand) and its lo part, 32 columns at a time
+        uint32_t lo[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s0[c]), D.scale_log2, -mc));
+          rs0 += p0;
+          s0[c] = __float_as_uint(p0);
+          lo[c] = __float_as_uint(tf32_lo(p0));
+        }
+        tc_st_32x32b_x32(t_s, s0);
+        tc_st_32x32b_x32(t_s + 128u, lo);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s1[c]), D.scale_log2, -mc));
+          rs1 += p1;
+          s1[c] = __float_as_uint(p1);
+          lo[c] = __float_as_uint(tf32_lo(p1));
+        }
+        tc_st_32x32b_x32(t_s + 32u, s1);
+        tc_st_32x32b_x32(t_s + 160u, lo);
+        tc_wait_st();
+      }
+      const float rs = rs0 + rs1;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C_PREADY + st));
+      // the previous block's P V joins the accumulators before they are rescaled for this block
+      if (j > 0) {
+        ok = add_pv(j - 1);
+        if (!ok) break;
+      }
+      l = l * alpha + rs;
+      m = m_new;
+#pragma unroll
+      for (int c = 0; c < HD; ++c) acc[c] *= alpha;
+    }
+    if (ok) ok = add_pv(nkb - 1);
+    if (ok && gi < D.Lq) {
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      float* orow = o + (b * D.Lq + gi) * D.Ev + (int64_t)h * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 4)
+        *(float4*)(orow + c) = make_float4(acc[c] * inv, acc[c + 1] * inv, acc[c + 2] * inv, acc[c + 3] * inv);
+      lse[(b * D.H + h) * D.Lq + gi] = (l > 0.0f) ? m * D.scale + logf(l) : -INFINITY;
+    }
+  } else {
+    // --------------------------------------------- split warps: lo = x - tf32(x) twins ---
+    const int tt = (warp - 6) * 32 + lane;
+    auto split = [&](int off_hi, int off_lo, int n16) {
+      const float4* hi = (const float4*)(smem + off_hi);
+      float4* lo = (float4*)(smem + off_lo);
+      for (int i = 0; i < n16; ++i) {
+        float4 v = hi[tt + i * 128];
+        v.x = tf32_lo(v.x); v.y = tf32_lo(v.y); v.z = tf32_lo(v.z); v.w = tf32_lo(v.w);
+        lo[tt + i * 128] = v;
+      }
+      fence_proxy_async();
+      __syncwarp();
+    };
+    bool ok = mbar_wait(bar(C_QFULL), 0u, s_abort);
+    if (ok) {
+      split(P2_QHI, P2_QLO, 16);
+      if (lane == 0) mbar_arrive(bar(C_QREADY));
+    }
+    for (int j = 0; j < nkb && ok; ++j) {
+      const int st = j & 1;
+      const int base = P2_STAGE0 + st * P2_STAGE_BYTES;
+      ok = mbar_wait(bar(C_KFULL + st), par(j), s_abort);
+      if (!ok) break;
+      split(base, base + 16384, 8);
+      if (lane == 0) mbar_arrive(bar(C_KREADY + st));
+      ok = mbar_wait(bar(C_VFULL + st), par(j), s_abort);
+      if (!ok) break;
+      split(base + 32768, base + 49152, 8);
+      if (lane == 0) mbar_arrive(bar(C_VREADY + st));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4002);
 }
 
 // FLUXB200_ATTN_TC = 0 keeps attention on the Float32 FMA kernels.
@@ -285,6 +630,26 @@ bool attn_tc_enabled() {
   if (on < 0) {
     const char* e = getenv("FLUXB200_ATTN_TC");
     on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+// FLUXB200_ATTN_PIPE = 0 selects the unpipelined kernels (one S / P V buffer, one K / V stage).
+bool attn_pipelined() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUXB200_ATTN_PIPE");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+// FLUXB200_ATTN_PTMEM = 1: P travels through tensor memory instead of shared memory.
+bool attn_p_in_tmem() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUXB200_ATTN_PTMEM");
+    on = (e != nullptr && e[0] == '1') ? 1 : 0;
   }
   return on != 0;
 }
@@ -323,9 +688,17 @@ int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const f
   D.E = e_dim; D.Ev = ev_dim; D.Lq = lq; D.Lk = lk; D.H = nheads; D.causal = causal ? 1 : 0;
   D.scale = 1.0f / sqrtf((float)HD);
   D.scale_log2 = D.scale * 1.4426950408889634f;
-  FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
   dim3 grid((unsigned)((lq + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
-  attn_fwd_tc_kernel<<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
+  if (attn_pipelined()) {
+    FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC2_SMEM));
+    attn_fwd_tc2_kernel<<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
+  } else if (attn_p_in_tmem()) {
+    FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+    attn_fwd_tc_kernel<true><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
+  } else {
+    FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+    attn_fwd_tc_kernel<false><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
+  }
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
