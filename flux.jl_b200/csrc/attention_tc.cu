@@ -364,7 +364,8 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* s_skip = (volatile int*)(smem + P2_BAR + 8 * C_COUNT + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t i0 = (int64_t)blockIdx.x * QT;
+  // causal: the last query tiles have the most key blocks, so they are scheduled first
+  const int64_t i0 = (int64_t)(D.causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * QT;
   const int h = blockIdx.y;
   const int64_t b = blockIdx.z;
   int64_t kv_end = D.Lk;
@@ -570,8 +571,10 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       l = l * alpha + rs;
       m = m_new;
+      if (alpha != 1.0f) {   // the running maximum moved (rare after the first blocks)
 #pragma unroll
-      for (int c = 0; c < HD; ++c) acc[c] *= alpha;
+        for (int c = 0; c < HD; ++c) acc[c] *= alpha;
+      }
     }
     if (ok) ok = add_pv(nkb - 1);
     if (ok && gi < D.Lq) {
