@@ -485,6 +485,9 @@ FB_API int32_t fb_attn_bwd(fb_ctx* ctx, void* stream_, const float* q, const flo
     FB_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
     attn_bwd_dkdv_kernel<1><<<grid_kv, AT, smem_kv, stream>>>(q, k, v, mask, lse, dlt, dout, dk, dv, D);
     FB_LAUNCH_CHECK();
+    // dQ on the tensor cores where the shape allows (head size 64, no explicit mask, at most 2048 keys)
+    st = fb_attn_bwd_dq_tc(ctx, stream, q, k, v, mask, lse, dlt, dout, dq, e_dim, ev_dim, lq, lk, batch, nheads, causal);
+    if (st != FB_ERR_UNSUPPORTED) return st;
     attn_bwd_dq_kernel<1><<<grid_q, AT, smem_q, stream>>>(q, k, v, mask, lse, dlt, dout, dq, D);
   } else {
     FB_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));

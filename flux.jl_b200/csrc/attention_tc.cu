@@ -627,6 +627,248 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4002);
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// dQ of the attention backward pass on the tensor cores.  One CTA owns 128 queries of one (batch, head); Q and dO of
+// those queries live in tensor memory for the whole kernel (hi and lo parts, A operands of the MMAs).  For every
+// block of 64 keys: S = Q K' and dP = dO V' (B operands: K and V tiles, K-major), the compute warps turn them into
+// dS = P (dP - delta) with P = exp(S / sqrt(d) - lse) and hand dS back through tensor memory, and dQ += dS K (B
+// operand: the same K tile loaded a second time in the MN-major layout, keys being its K rows).  dQ accumulates in
+// tensor memory over at most 32 blocks (2048 keys, the accumulation length the GEMM also uses).
+//   TMEM columns: Q hi 0, Q lo 64, dO hi 128, dO lo 192, S -> dS hi 256, dS lo 320, dP 384, dQ 448
+constexpr int DQ_STAGE_BYTES = 98304;   // K k-major hi/lo (32 KB), K mn-major hi/lo (32 KB), V k-major hi/lo (32 KB)
+constexpr int DQ_BAR = 2 * DQ_STAGE_BYTES;
+constexpr int DQ_SMEM = DQ_BAR + 256 + 1024;
+constexpr int DQ_MAX_BLOCKS = 32;
+enum { E_QREADY = 0, E_FULL, E_READY = E_FULL + 2, E_FREE = E_READY + 2, E_SFULL = E_FREE + 2, E_DSREADY, E_DQFULL, E_COUNT };
+
+__global__ void __launch_bounds__(ATC_THREADS, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmKmn,
+                      const __grid_constant__ CUtensorMap tmV, const float* __restrict__ q, const float* __restrict__ dout,
+                      const float* __restrict__ lse, const float* __restrict__ dlt, float* __restrict__ dq, AtcDims D,
+                      int32_t* __restrict__ dev_err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar0 = sb + DQ_BAR;
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  volatile uint32_t* s_tmem = (volatile uint32_t*)(smem + DQ_BAR + 8 * E_COUNT);
+  volatile int* s_abort = (volatile int*)(smem + DQ_BAR + 8 * E_COUNT + 8);
+  volatile int* s_skip = (volatile int*)(smem + DQ_BAR + 8 * E_COUNT + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t i0 = (int64_t)(D.causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * QT;
+  const int h = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  int64_t kv_end = D.Lk;
+  if (D.causal && i0 + QT < kv_end) kv_end = i0 + QT;
+  const int nkb = (int)((kv_end + KT - 1) / KT);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(E_QREADY), 4);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(bar(E_FULL + st), 1);
+      mbar_init(bar(E_READY + st), 4);
+      mbar_init(bar(E_FREE + st), 1);
+    }
+    mbar_init(bar(E_SFULL), 1);
+    mbar_init(bar(E_DSREADY), 4);
+    mbar_init(bar(E_DQFULL), 1);
+    *s_abort = 0;
+    *s_skip = (*(volatile int32_t*)dev_err != 0) ? 1 : 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (*s_skip != 0) return;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+  auto par = [](int j) { return (uint32_t)(j >> 1) & 1u; };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer ---
+    if (lane == 0) {
+      const int krow0 = (int)(b * D.Lk);
+      for (int j = 0; j < nkb; ++j) {
+        const int st = j & 1;
+        const uint32_t base = sb + (uint32_t)(st * DQ_STAGE_BYTES);
+        if (j >= 2 && !mbar_wait(bar(E_FREE + st), par(j - 2), s_abort)) break;
+        mbar_arrive_expect_tx(bar(E_FULL + st), 49152u);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tma_load_2d(base + c * 4096, &tmK, h * HD + 16 * c, krow0 + j * KT, bar(E_FULL + st));
+        tma_load_3d(base + 32768, &tmKmn, 0, krow0 + j * KT, 2 * h, bar(E_FULL + st));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tma_load_2d(base + 65536 + c * 4096, &tmV, h * HD + 16 * c, krow0 + j * KT, bar(E_FULL + st));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer ---
+    if (lane == 0) {
+      const uint32_t idesc_kk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(KT >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
+      const uint32_t idesc_mn = idesc_kk | (1u << 16);   // N = 64 either way (keys, or features of dQ)
+      const uint32_t t_q = tmem_base, t_do = tmem_base + 128u, t_s = tmem_base + 256u, t_dp = tmem_base + 384u, t_dq = tmem_base + 448u;
+      bool ok = mbar_wait(bar(E_QREADY), 0u, s_abort);
+      for (int j = 0; j < nkb && ok; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(bar(E_READY + st), par(j), s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t base = sb + (uint32_t)(st * DQ_STAGE_BYTES);
+        const uint64_t dk_hi = make_smem_desc(base, 16, 512, LAYOUT_SW64), dk_lo = make_smem_desc(base + 16384, 16, 512, LAYOUT_SW64);
+        const uint64_t dv_hi = make_smem_desc(base + 65536, 16, 512, LAYOUT_SW64), dv_lo = make_smem_desc(base + 81920, 16, 512, LAYOUT_SW64);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {   // S = Q K' and dP = dO V' over the 64 features
+          const uint64_t bo = (uint64_t)(((ks >> 1) * 4096 + (ks & 1) * 32) >> 4);
+          const uint32_t ao = (uint32_t)(8 * ks);
+          tc_mma_tf32_ta(t_s, t_q + 64u + ao, dk_hi + bo, idesc_kk, ks > 0 ? 1u : 0u);
+          tc_mma_tf32_ta(t_s, t_q + ao, dk_lo + bo, idesc_kk, 1u);
+          tc_mma_tf32_ta(t_s, t_q + ao, dk_hi + bo, idesc_kk, 1u);
+          tc_mma_tf32_ta(t_dp, t_do + 64u + ao, dv_hi + bo, idesc_kk, ks > 0 ? 1u : 0u);
+          tc_mma_tf32_ta(t_dp, t_do + ao, dv_lo + bo, idesc_kk, 1u);
+          tc_mma_tf32_ta(t_dp, t_do + ao, dv_hi + bo, idesc_kk, 1u);
+        }
+        tc_commit(bar(E_SFULL));
+        ok = mbar_wait(bar(E_DSREADY), (uint32_t)j & 1u, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dm_hi = make_smem_desc(base + 32768, KT * 128, 512, LAYOUT_SW128_32B);
+        const uint64_t dm_lo = make_smem_desc(base + 49152, KT * 128, 512, LAYOUT_SW128_32B);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {   // dQ += dS K over the 64 keys
+          const uint64_t bo = (uint64_t)((ks * 1024) >> 4);
+          const uint32_t ao = (uint32_t)(8 * ks);
+          tc_mma_tf32_ta(t_dq, t_s + 64u + ao, dm_hi + bo, idesc_mn, (j > 0 || ks > 0) ? 1u : 0u);
+          tc_mma_tf32_ta(t_dq, t_s + ao, dm_lo + bo, idesc_mn, 1u);
+          tc_mma_tf32_ta(t_dq, t_s + ao, dm_hi + bo, idesc_mn, 1u);
+        }
+        tc_commit(bar(E_FREE + st));
+        if (j == nkb - 1) tc_commit(bar(E_DQFULL));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ compute warps ---
+    const int qd = warp & 3;
+    const int row = 32 * qd + lane;
+    const int64_t gi = i0 + row;
+    const bool live = gi < D.Lq;
+    const uint32_t t_row = tmem_base + ((uint32_t)(32 * qd) << 16);
+    // Q and dO rows of this thread into tensor memory: the raw value is the hi operand, lo = x - tf32(x)
+    {
+      const float* src[2] = {q + (b * D.Lq + gi) * D.E + (int64_t)h * HD, dout + (b * D.Lq + gi) * D.Ev + (int64_t)h * HD};
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4) {
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live) x = __ldg((const float4*)(src[w] + 32 * half + 4 * c4));
+            hi[4 * c4] = __float_as_uint(x.x); hi[4 * c4 + 1] = __float_as_uint(x.y);
+            hi[4 * c4 + 2] = __float_as_uint(x.z); hi[4 * c4 + 3] = __float_as_uint(x.w);
+            lo[4 * c4] = __float_as_uint(tf32_lo(x.x)); lo[4 * c4 + 1] = __float_as_uint(tf32_lo(x.y));
+            lo[4 * c4 + 2] = __float_as_uint(tf32_lo(x.z)); lo[4 * c4 + 3] = __float_as_uint(tf32_lo(x.w));
+          }
+          tc_st_32x32b_x32(t_row + (uint32_t)(128 * w + 32 * half), hi);
+          tc_st_32x32b_x32(t_row + (uint32_t)(128 * w + 64 + 32 * half), lo);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(E_QREADY));
+    }
+    const float l2 = live ? lse[(b * D.H + h) * D.Lq + gi] * 1.4426950408889634f : INFINITY;   // a dead row gets P = 0
+    const float dl = live ? dlt[(b * D.H + h) * D.Lq + gi] : 0.0f;
+    bool ok = true;
+    for (int j = 0; j < nkb && ok; ++j) {
+      const int64_t j0 = (int64_t)j * KT;
+      ok = mbar_wait(bar(E_SFULL), (uint32_t)j & 1u, s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      int64_t lim = D.Lk - j0;
+      if (D.causal && gi - j0 + 1 < lim) lim = gi - j0 + 1;
+      const int nvalid = lim < 0 ? 0 : (lim > KT ? KT : (int)lim);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32], dp[32];
+        tc_ld_32x32b_x32(t_row + 256u + (uint32_t)(32 * half), sv);
+        tc_ld_32x32b_x32(t_row + 384u + (uint32_t)(32 * half), dp);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float p = fast_exp2(fmaf(__uint_as_float(sv[c]), D.scale_log2, -l2));
+          if (c + 32 * half >= nvalid) p = 0.0f;
+          const float ds = p * (__uint_as_float(dp[c]) - dl);
+          sv[c] = __float_as_uint(ds);
+          dp[c] = __float_as_uint(tf32_lo(ds));
+        }
+        tc_st_32x32b_x32(t_row + 256u + (uint32_t)(32 * half), sv);
+        tc_st_32x32b_x32(t_row + 320u + (uint32_t)(32 * half), dp);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(E_DSREADY));
+    }
+    if (ok) ok = mbar_wait(bar(E_DQFULL), 0u, s_abort);
+    if (ok) {
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tc_ld_32x32b_x32(t_row + 448u, r0);
+      tc_ld_32x32b_x32(t_row + 480u, r1);
+      tc_wait_ld();
+      if (live) {
+        float* drow = dq + (b * D.Lq + gi) * D.E + (int64_t)h * HD;
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          *(float4*)(drow + c) = make_float4(__uint_as_float(r0[c]) * D.scale, __uint_as_float(r0[c + 1]) * D.scale,
+                                             __uint_as_float(r0[c + 2]) * D.scale, __uint_as_float(r0[c + 3]) * D.scale);
+          *(float4*)(drow + 32 + c) = make_float4(__uint_as_float(r1[c]) * D.scale, __uint_as_float(r1[c + 1]) * D.scale,
+                                                  __uint_as_float(r1[c + 2]) * D.scale, __uint_as_float(r1[c + 3]) * D.scale);
+        }
+      }
+    }
+  } else {
+    // --------------------------------------------- split warps: lo = x - tf32(x) twins ---
+    const int tt = (warp - 6) * 32 + lane;
+    bool ok = true;
+    for (int j = 0; j < nkb && ok; ++j) {
+      const int st = j & 1;
+      ok = mbar_wait(bar(E_FULL + st), par(j), s_abort);
+      if (!ok) break;
+#pragma unroll
+      for (int tile = 0; tile < 3; ++tile) {
+        const float4* hi = (const float4*)(smem + st * DQ_STAGE_BYTES + tile * 32768);
+        float4* lo = (float4*)(smem + st * DQ_STAGE_BYTES + tile * 32768 + 16384);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float4 v = hi[tt + i * 128];
+          v.x = tf32_lo(v.x); v.y = tf32_lo(v.y); v.z = tf32_lo(v.z); v.w = tf32_lo(v.w);
+          lo[tt + i * 128] = v;
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(E_READY + st));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4003);
+}
+
 // FLUXB200_ATTN_TC = 0 keeps attention on the Float32 FMA kernels.
 bool attn_tc_enabled() {
   static int on = -1;
@@ -642,6 +884,16 @@ bool attn_pipelined() {
   static int on = -1;
   if (on < 0) {
     const char* e = getenv("FLUXB200_ATTN_PIPE");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+// FLUXB200_ATTN_BWD_TC = 0 keeps the backward pass on the Float32 FMA kernels.
+bool attn_bwd_tc_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUXB200_ATTN_BWD_TC");
     on = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
   return on != 0;
@@ -702,6 +954,32 @@ int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const f
     FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
     attn_fwd_tc_kernel<false><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
   }
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}
+
+// dQ of the backward pass; FB_ERR_UNSUPPORTED when the shape is not one this kernel takes.
+int32_t fb_attn_bwd_dq_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const float* k, const float* v, const uint8_t* mask,
+                          const float* lse, const float* dlt, const float* dout, float* dq, int64_t e_dim, int64_t ev_dim,
+                          int64_t lq, int64_t lk, int64_t batch, int nheads, int causal) {
+  if (!attn_tc_enabled() || !attn_bwd_tc_enabled() || mask != nullptr || nheads < 1) return FB_ERR_UNSUPPORTED;
+  if (e_dim != (int64_t)nheads * HD || ev_dim != (int64_t)nheads * HD) return FB_ERR_UNSUPPORTED;
+  if (lq < 1 || lk < 1 || batch < 1 || batch * lq > 0x7fffff00 || batch * lk > 0x7fffff00 || batch > 65535 || nheads > 65535)
+    return FB_ERR_UNSUPPORTED;
+  if ((lk + KT - 1) / KT > DQ_MAX_BLOCKS) return FB_ERR_UNSUPPORTED;   // dQ accumulates in tensor memory over <= 2048 keys
+  if (!fb_aligned16(q) || !fb_aligned16(k) || !fb_aligned16(v) || !fb_aligned16(dout) || !fb_aligned16(dq)) return FB_ERR_UNSUPPORTED;
+  CUtensorMap tmK, tmKmn, tmV;
+  if (!encode_map(&tmK, k, batch * lk, e_dim, e_dim, 16, KT, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      !encode_rows3d(&tmKmn, k, batch * lk, e_dim, KT, HD / 32) ||
+      !encode_map(&tmV, v, batch * lk, ev_dim, ev_dim, 16, KT, CU_TENSOR_MAP_SWIZZLE_64B))
+    return FB_ERR_UNSUPPORTED;
+  AtcDims D;
+  D.E = e_dim; D.Ev = ev_dim; D.Lq = lq; D.Lk = lk; D.H = nheads; D.causal = causal ? 1 : 0;
+  D.scale = 1.0f / sqrtf((float)HD);
+  D.scale_log2 = D.scale * 1.4426950408889634f;
+  FB_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
+  dim3 grid((unsigned)((lq + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
+  attn_bwd_dq_tc_kernel<<<grid, ATC_THREADS, DQ_SMEM, stream>>>(tmK, tmKmn, tmV, q, dout, lse, dlt, dq, D, ctx->dev_error);
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
