@@ -478,7 +478,7 @@ def run_small_config(args):
         flops = 652.8e9
         lines.append(("mha: MultiHeadAttention(1024, nheads=16), causal, 1024x2048x8 Float32, forward + backward (loss on y)", 8, ms,
                       {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": tf32, "unit": "TFLOP/s", "frac": flops / ms / 1e9 / tf32, "traffic": None,
-                       "note": "projections on tcgen05 (3xTF32); the attention core is the fp32 FMA flash kernel in this version"},
+                       "note": "projections and the attention core (forward, dQ, dK/dV) on tcgen05 with 3xTF32; softmax and dS on TMEM read-back"},
                       (1 * (512 / 2048) ** 2 * 1.0) / cpu * 1.0, "1 of 8 samples at seq 512 (1/16 of a sample's attention work, 1/4 of its projections), 1 run"))
     if F.context().device_error() != 0:
         raise SystemExit("a kernel recorded a bounded-wait timeout; the numbers are invalid")

@@ -483,8 +483,14 @@ FB_API int32_t fb_attn_bwd(fb_ctx* ctx, void* stream_, const float* q, const flo
   if (nc == 1) {
     FB_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
     FB_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
-    attn_bwd_dkdv_kernel<1><<<grid_kv, AT, smem_kv, stream>>>(q, k, v, mask, lse, dlt, dout, dk, dv, D);
-    FB_LAUNCH_CHECK();
+    // dK / dV on the tensor cores where the shape allows (head size 64, no explicit mask, at most 2048 queries)
+    st = fb_attn_bwd_dkdv_tc(ctx, stream, q, k, v, mask, lse, dlt, dout, dk, dv, e_dim, ev_dim, lq, lk, batch, nheads, causal);
+    if (st == FB_ERR_UNSUPPORTED) {
+      attn_bwd_dkdv_kernel<1><<<grid_kv, AT, smem_kv, stream>>>(q, k, v, mask, lse, dlt, dout, dk, dv, D);
+      FB_LAUNCH_CHECK();
+    } else if (st != FB_OK) {
+      return st;
+    }
     // dQ on the tensor cores where the shape allows (head size 64, no explicit mask, at most 2048 keys)
     st = fb_attn_bwd_dq_tc(ctx, stream, q, k, v, mask, lse, dlt, dout, dq, e_dim, ev_dim, lq, lk, batch, nheads, causal);
     if (st != FB_ERR_UNSUPPORTED) return st;

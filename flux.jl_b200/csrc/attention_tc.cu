@@ -869,6 +869,318 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4003);
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// dK and dV of the attention backward pass on the tensor cores, in transposed form so that keys are the rows
+// (TMEM lanes) of every accumulator.  One CTA owns 128 keys of one (batch, head): K lives in tensor memory (A operand),
+// V in shared memory (A operand, K-major).  For every block of 64 queries:
+//   S' = K Q'  and  dP' = V dO'    (B operands: the Q and dO tiles, K-major)
+//   P' = exp(S' / sqrt(d) - lse_q),  dS' = P' (dP' - delta_q)     (compute warps; back through tensor memory)
+//   dV += P' dO  and  dK += dS' Q   (B operands: the same Q and dO tiles loaded a second time MN-major, queries
+//                                    being their K rows)
+// A tile's shared memory is reloaded as soon as the MMAs that read it have completed, so the loads of the next block
+// overlap the rest of the current one.  dK and dV accumulate in tensor memory over at most 32 query blocks.
+//   TMEM columns: K hi 0, K lo 64, S' -> P' hi 128, P' lo 192, dP' -> dS' hi 256, dS' lo 320, dV 384, dK 448
+constexpr int KV_VHI = 0, KV_VLO = 32768;                       // 4 chunks x [128 keys][16 floats]
+constexpr int KV_QK = 65536, KV_DOK = 98304, KV_DOM = 131072, KV_QM = 163840;   // 64-query tiles: hi 16 KB + lo 16 KB each
+constexpr int KV_ROWV = 196608;                                 // lse * log2(e) and delta of the block's 64 queries, two sets
+constexpr int KV_BAR = KV_ROWV + 1024;
+constexpr int KV_SMEM = KV_BAR + 256 + 1024;
+constexpr int KV_MAX_BLOCKS = 32;
+enum { F_KREADY = 0, F_VFULL, F_VREADY, F_FULL, F_READY = F_FULL + 4, F_FREE = F_READY + 4, F_SFULL = F_FREE + 4, F_PREADY, F_DONE, F_COUNT };
+
+__global__ void __launch_bounds__(ATC_THREADS, 1)
+attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmQmn,
+                        const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmDOmn,
+                        const __grid_constant__ CUtensorMap tmV, const float* __restrict__ k, const float* __restrict__ lse,
+                        const float* __restrict__ dlt, float* __restrict__ dk, float* __restrict__ dv, AtcDims D,
+                        int32_t* __restrict__ dev_err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar0 = sb + KV_BAR;
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  volatile uint32_t* s_tmem = (volatile uint32_t*)(smem + KV_BAR + 8 * F_COUNT);
+  volatile int* s_abort = (volatile int*)(smem + KV_BAR + 8 * F_COUNT + 8);
+  volatile int* s_skip = (volatile int*)(smem + KV_BAR + 8 * F_COUNT + 16);
+  float* rowv = (float*)(smem + KV_ROWV);   // [set][0: lse * log2e, 1: delta][64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t j0 = (int64_t)blockIdx.x * QT;   // first key of this CTA
+  const int h = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  // query blocks that see these keys: all of them, or under a causal mask those from the diagonal on
+  const int ib0 = D.causal ? (int)(j0 / KT) : 0;
+  const int nqb = (int)((D.Lq + KT - 1) / KT) - ib0;   // may be <= 0: nothing attends to these keys
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(F_KREADY), 4);
+    mbar_init(bar(F_VFULL), 1);
+    mbar_init(bar(F_VREADY), 4);
+    for (int t = 0; t < 4; ++t) {
+      mbar_init(bar(F_FULL + t), 1);
+      mbar_init(bar(F_READY + t), 4);
+      mbar_init(bar(F_FREE + t), 1);
+    }
+    mbar_init(bar(F_SFULL), 1);
+    mbar_init(bar(F_PREADY), 4);
+    mbar_init(bar(F_DONE), 1);
+    *s_abort = 0;
+    *s_skip = (*(volatile int32_t*)dev_err != 0) ? 1 : 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (*s_skip != 0) return;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+  // tile order: 0 = Q k-major, 1 = dO k-major, 2 = dO mn-major, 3 = Q mn-major
+  const int tile_off[4] = {KV_QK, KV_DOK, KV_DOM, KV_QM};
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer ---
+    if (lane == 0 && nqb > 0) {
+      mbar_arrive_expect_tx(bar(F_VFULL), 32768u);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tma_load_2d(sb + KV_VHI + c * 8192, &tmV, h * HD + 16 * c, (int)(b * D.Lk + j0), bar(F_VFULL));
+      bool ok = true;
+      for (int i = 0; i < nqb && ok; ++i) {
+        const int qrow = (int)(b * D.Lq + (int64_t)(ib0 + i) * KT);
+        const uint32_t ph = (uint32_t)(i - 1) & 1u;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          if (i > 0 && !mbar_wait(bar(F_FREE + t), ph, s_abort)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(F_FULL + t), 16384u);
+          const uint32_t dst = sb + (uint32_t)tile_off[t];
+          if (t == 0) {
+            for (int c = 0; c < 4; ++c) tma_load_2d(dst + c * 4096, &tmQ, h * HD + 16 * c, qrow, bar(F_FULL + t));
+          } else if (t == 1) {
+            for (int c = 0; c < 4; ++c) tma_load_2d(dst + c * 4096, &tmDO, h * HD + 16 * c, qrow, bar(F_FULL + t));
+          } else if (t == 2) {
+            tma_load_3d(dst, &tmDOmn, 0, qrow, 2 * h, bar(F_FULL + t));
+          } else {
+            tma_load_3d(dst, &tmQmn, 0, qrow, 2 * h, bar(F_FULL + t));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer ---
+    if (lane == 0 && nqb > 0) {
+      const uint32_t idesc_kk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(KT >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
+      const uint32_t idesc_mn = idesc_kk | (1u << 16);
+      const uint32_t t_k = tmem_base, t_p = tmem_base + 128u, t_ds = tmem_base + 256u, t_dv = tmem_base + 384u, t_dk = tmem_base + 448u;
+      const uint64_t dv_hi = make_smem_desc(sb + KV_VHI, 16, 512, LAYOUT_SW64), dv_lo = make_smem_desc(sb + KV_VLO, 16, 512, LAYOUT_SW64);
+      const uint64_t dqk_hi = make_smem_desc(sb + KV_QK, 16, 512, LAYOUT_SW64), dqk_lo = make_smem_desc(sb + KV_QK + 16384, 16, 512, LAYOUT_SW64);
+      const uint64_t dok_hi = make_smem_desc(sb + KV_DOK, 16, 512, LAYOUT_SW64), dok_lo = make_smem_desc(sb + KV_DOK + 16384, 16, 512, LAYOUT_SW64);
+      const uint64_t dom_hi = make_smem_desc(sb + KV_DOM, KT * 128, 512, LAYOUT_SW128_32B), dom_lo = make_smem_desc(sb + KV_DOM + 16384, KT * 128, 512, LAYOUT_SW128_32B);
+      const uint64_t dqm_hi = make_smem_desc(sb + KV_QM, KT * 128, 512, LAYOUT_SW128_32B), dqm_lo = make_smem_desc(sb + KV_QM + 16384, KT * 128, 512, LAYOUT_SW128_32B);
+      bool ok = mbar_wait(bar(F_KREADY), 0u, s_abort) && mbar_wait(bar(F_VREADY), 0u, s_abort);
+      for (int i = 0; i < nqb && ok; ++i) {
+        const uint32_t ph = (uint32_t)i & 1u;
+        ok = mbar_wait(bar(F_READY + 0), ph, s_abort) && mbar_wait(bar(F_READY + 1), ph, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {   // S' = K Q' over the 64 features
+          const uint64_t bo = (uint64_t)(((ks >> 1) * 4096 + (ks & 1) * 32) >> 4);
+          const uint32_t ao = (uint32_t)(8 * ks);
+          tc_mma_tf32_ta(t_p, t_k + 64u + ao, dqk_hi + bo, idesc_kk, ks > 0 ? 1u : 0u);
+          tc_mma_tf32_ta(t_p, t_k + ao, dqk_lo + bo, idesc_kk, 1u);
+          tc_mma_tf32_ta(t_p, t_k + ao, dqk_hi + bo, idesc_kk, 1u);
+        }
+        tc_commit(bar(F_FREE + 0));
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {   // dP' = V dO' over the 64 value features (A = V from shared memory)
+          const uint64_t ao = (uint64_t)(((ks >> 1) * 8192 + (ks & 1) * 32) >> 4), bo = (uint64_t)(((ks >> 1) * 4096 + (ks & 1) * 32) >> 4);
+          tc_mma_tf32(t_ds, dv_lo + ao, dok_hi + bo, idesc_kk, ks > 0 ? 1u : 0u);
+          tc_mma_tf32(t_ds, dv_hi + ao, dok_lo + bo, idesc_kk, 1u);
+          tc_mma_tf32(t_ds, dv_hi + ao, dok_hi + bo, idesc_kk, 1u);
+        }
+        tc_commit(bar(F_FREE + 1));
+        tc_commit(bar(F_SFULL));
+        ok = mbar_wait(bar(F_PREADY), ph, s_abort) && mbar_wait(bar(F_READY + 2), ph, s_abort) && mbar_wait(bar(F_READY + 3), ph, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {   // dV += P' dO over the 64 queries
+          const uint64_t bo = (uint64_t)((ks * 1024) >> 4);
+          const uint32_t ao = (uint32_t)(8 * ks);
+          tc_mma_tf32_ta(t_dv, t_p + 64u + ao, dom_hi + bo, idesc_mn, (i > 0 || ks > 0) ? 1u : 0u);
+          tc_mma_tf32_ta(t_dv, t_p + ao, dom_lo + bo, idesc_mn, 1u);
+          tc_mma_tf32_ta(t_dv, t_p + ao, dom_hi + bo, idesc_mn, 1u);
+        }
+        tc_commit(bar(F_FREE + 2));
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {   // dK += dS' Q over the 64 queries
+          const uint64_t bo = (uint64_t)((ks * 1024) >> 4);
+          const uint32_t ao = (uint32_t)(8 * ks);
+          tc_mma_tf32_ta(t_dk, t_ds + 64u + ao, dqm_hi + bo, idesc_mn, (i > 0 || ks > 0) ? 1u : 0u);
+          tc_mma_tf32_ta(t_dk, t_ds + ao, dqm_lo + bo, idesc_mn, 1u);
+          tc_mma_tf32_ta(t_dk, t_ds + ao, dqm_hi + bo, idesc_mn, 1u);
+        }
+        tc_commit(bar(F_FREE + 3));
+        if (i == nqb - 1) tc_commit(bar(F_DONE));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ compute warps ---
+    const int qd = warp & 3;
+    const int row = 32 * qd + lane;
+    const int64_t kj = j0 + row;             // this thread's key
+    const bool live = kj < D.Lk;
+    const uint32_t t_row = tmem_base + ((uint32_t)(32 * qd) << 16);
+    if (nqb > 0) {
+      // K row of this thread into tensor memory: the raw value is the hi operand, lo = x - tf32(x)
+      const float* src = k + (b * D.Lk + kj) * D.E + (int64_t)h * HD;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t hi[32], lo[32];
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (live) x = __ldg((const float4*)(src + 32 * half + 4 * c4));
+          hi[4 * c4] = __float_as_uint(x.x); hi[4 * c4 + 1] = __float_as_uint(x.y);
+          hi[4 * c4 + 2] = __float_as_uint(x.z); hi[4 * c4 + 3] = __float_as_uint(x.w);
+          lo[4 * c4] = __float_as_uint(tf32_lo(x.x)); lo[4 * c4 + 1] = __float_as_uint(tf32_lo(x.y));
+          lo[4 * c4 + 2] = __float_as_uint(tf32_lo(x.z)); lo[4 * c4 + 3] = __float_as_uint(tf32_lo(x.w));
+        }
+        tc_st_32x32b_x32(t_row + (uint32_t)(32 * half), hi);
+        tc_st_32x32b_x32(t_row + (uint32_t)(64 + 32 * half), lo);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(F_KREADY));
+    }
+    bool ok = true;
+    for (int i = 0; i < nqb && ok; ++i) {
+      const int64_t i0b = (int64_t)(ib0 + i) * KT;   // first query of the block
+      const float* rv = rowv + (i & 1) * 128;
+      ok = mbar_wait(bar(F_SFULL), (uint32_t)i & 1u, s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      // queries of the block this key is seen by: query < Lq (dead ones carry lse = +inf), and query >= key when causal
+      int clo = 0;
+      if (D.causal && kj - i0b > 0) clo = (kj - i0b) > KT ? KT : (int)(kj - i0b);
+      if (!live) clo = KT;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32], dp[32], lo[32];
+        tc_ld_32x32b_x32(t_row + 128u + (uint32_t)(32 * half), sv);
+        tc_ld_32x32b_x32(t_row + 256u + (uint32_t)(32 * half), dp);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int cq = c + 32 * half;
+          float p = fast_exp2(fmaf(__uint_as_float(sv[c]), D.scale_log2, -rv[cq]));
+          if (cq < clo) p = 0.0f;
+          const float ds = p * (__uint_as_float(dp[c]) - rv[64 + cq]);
+          sv[c] = __float_as_uint(p);
+          lo[c] = __float_as_uint(tf32_lo(p));
+          dp[c] = __float_as_uint(ds);
+        }
+        tc_st_32x32b_x32(t_row + 128u + (uint32_t)(32 * half), sv);
+        tc_st_32x32b_x32(t_row + 192u + (uint32_t)(32 * half), lo);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) lo[c] = __float_as_uint(tf32_lo(__uint_as_float(dp[c])));
+        tc_st_32x32b_x32(t_row + 256u + (uint32_t)(32 * half), dp);
+        tc_st_32x32b_x32(t_row + 320u + (uint32_t)(32 * half), lo);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(F_PREADY));
+    }
+    if (nqb > 0) {
+      if (ok) ok = mbar_wait(bar(F_DONE), 0u, s_abort);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {   // 0: dV, 1: dK (scaled by 1 / sqrt(d))
+          uint32_t r0[32], r1[32];
+          tc_ld_32x32b_x32(t_row + 384u + (uint32_t)(64 * w), r0);
+          tc_ld_32x32b_x32(t_row + 416u + (uint32_t)(64 * w), r1);
+          tc_wait_ld();
+          if (live) {
+            const float sc = w == 0 ? 1.0f : D.scale;
+            float* drow = (w == 0 ? dv + (b * D.Lk + kj) * D.Ev : dk + (b * D.Lk + kj) * D.E) + (int64_t)h * HD;
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              *(float4*)(drow + c) = make_float4(__uint_as_float(r0[c]) * sc, __uint_as_float(r0[c + 1]) * sc,
+                                                 __uint_as_float(r0[c + 2]) * sc, __uint_as_float(r0[c + 3]) * sc);
+              *(float4*)(drow + 32 + c) = make_float4(__uint_as_float(r1[c]) * sc, __uint_as_float(r1[c + 1]) * sc,
+                                                      __uint_as_float(r1[c + 2]) * sc, __uint_as_float(r1[c + 3]) * sc);
+            }
+          }
+        }
+      }
+    } else if (live) {
+      // no query sees these keys: their gradients are zero
+      float* r1 = dv + (b * D.Lk + kj) * D.Ev + (int64_t)h * HD;
+      float* r2 = dk + (b * D.Lk + kj) * D.E + (int64_t)h * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 4) {
+        *(float4*)(r1 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *(float4*)(r2 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  } else {
+    // --------------------------------- split warps: lo twins, and the per-query lse / delta of each block ---
+    const int tt = (warp - 6) * 32 + lane;
+    auto split = [&](int off, int n16) {
+      const float4* hi = (const float4*)(smem + off);
+      float4* lo = (float4*)(smem + off + (n16 == 16 ? 32768 : 16384));
+      for (int i = 0; i < n16; ++i) {
+        float4 v = hi[tt + i * 128];
+        v.x = tf32_lo(v.x); v.y = tf32_lo(v.y); v.z = tf32_lo(v.z); v.w = tf32_lo(v.w);
+        lo[tt + i * 128] = v;
+      }
+    };
+    bool ok = nqb > 0;
+    if (ok) ok = mbar_wait(bar(F_VFULL), 0u, s_abort);
+    if (ok) {
+      split(KV_VHI, 16);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(F_VREADY));
+    }
+    for (int i = 0; i < nqb && ok; ++i) {
+      const uint32_t ph = (uint32_t)i & 1u;
+      // lse * log2(e) and delta of the block's queries (set i & 1: the compute warps may still read the other set)
+      if (tt < KT) {
+        const int64_t gq = (int64_t)(ib0 + i) * KT + tt;
+        float* rv = rowv + (i & 1) * 128;
+        rv[tt] = gq < D.Lq ? lse[(b * D.H + h) * D.Lq + gq] * 1.4426950408889634f : INFINITY;
+        rv[64 + tt] = gq < D.Lq ? dlt[(b * D.H + h) * D.Lq + gq] : 0.0f;
+      }
+#pragma unroll 1
+      for (int t = 0; t < 4 && ok; ++t) {
+        ok = mbar_wait(bar(F_FULL + t), ph, s_abort);
+        if (!ok) break;
+        split(tile_off[t], 8);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(F_READY + t));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4004);
+}
+
 // FLUXB200_ATTN_TC = 0 keeps attention on the Float32 FMA kernels.
 bool attn_tc_enabled() {
   static int on = -1;
@@ -980,6 +1292,36 @@ int32_t fb_attn_bwd_dq_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, cons
   FB_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
   dim3 grid((unsigned)((lq + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
   attn_bwd_dq_tc_kernel<<<grid, ATC_THREADS, DQ_SMEM, stream>>>(tmK, tmKmn, tmV, q, dout, lse, dlt, dq, D, ctx->dev_error);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}
+
+// dK and dV of the backward pass; FB_ERR_UNSUPPORTED when the shape is not one this kernel takes.
+int32_t fb_attn_bwd_dkdv_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const float* k, const float* v, const uint8_t* mask,
+                            const float* lse, const float* dlt, const float* dout, float* dk, float* dv, int64_t e_dim,
+                            int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch, int nheads, int causal) {
+  if (!attn_tc_enabled() || !attn_bwd_tc_enabled() || mask != nullptr || nheads < 1) return FB_ERR_UNSUPPORTED;
+  if (e_dim != (int64_t)nheads * HD || ev_dim != (int64_t)nheads * HD) return FB_ERR_UNSUPPORTED;
+  if (lq < 1 || lk < 1 || batch < 1 || batch * lq > 0x7fffff00 || batch * lk > 0x7fffff00 || batch > 65535 || nheads > 65535)
+    return FB_ERR_UNSUPPORTED;
+  if ((lq + KT - 1) / KT > KV_MAX_BLOCKS) return FB_ERR_UNSUPPORTED;   // accumulation in tensor memory over <= 2048 queries
+  if (!fb_aligned16(q) || !fb_aligned16(k) || !fb_aligned16(v) || !fb_aligned16(dout) || !fb_aligned16(dk) || !fb_aligned16(dv))
+    return FB_ERR_UNSUPPORTED;
+  CUtensorMap tmQ, tmQmn, tmDO, tmDOmn, tmV;
+  if (!encode_map(&tmQ, q, batch * lq, e_dim, e_dim, 16, KT, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      !encode_rows3d(&tmQmn, q, batch * lq, e_dim, KT, HD / 32) ||
+      !encode_map(&tmDO, dout, batch * lq, ev_dim, ev_dim, 16, KT, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      !encode_rows3d(&tmDOmn, dout, batch * lq, ev_dim, KT, HD / 32) ||
+      !encode_map(&tmV, v, batch * lk, ev_dim, ev_dim, 16, QT, CU_TENSOR_MAP_SWIZZLE_64B))
+    return FB_ERR_UNSUPPORTED;
+  AtcDims D;
+  D.E = e_dim; D.Ev = ev_dim; D.Lq = lq; D.Lk = lk; D.H = nheads; D.causal = causal ? 1 : 0;
+  D.scale = 1.0f / sqrtf((float)HD);
+  D.scale_log2 = D.scale * 1.4426950408889634f;
+  FB_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM));
+  dim3 grid((unsigned)((lk + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
+  attn_bwd_dkdv_tc_kernel<<<grid, ATC_THREADS, KV_SMEM, stream>>>(tmQ, tmQmn, tmDO, tmDOmn, tmV, k, lse, dlt, dk, dv, D,
+                                                                   ctx->dev_error);
   FB_LAUNCH_CHECK();
   return FB_OK;
 }

@@ -191,6 +191,9 @@ int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const f
 int32_t fb_attn_bwd_dq_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const float* k, const float* v, const uint8_t* mask,
                           const float* lse, const float* dlt, const float* dout, float* dq, int64_t e_dim, int64_t ev_dim,
                           int64_t lq, int64_t lk, int64_t batch, int nheads, int causal);
+int32_t fb_attn_bwd_dkdv_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const float* k, const float* v, const uint8_t* mask,
+                            const float* lse, const float* dlt, const float* dout, float* dk, float* dv, int64_t e_dim,
+                            int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch, int nheads, int causal);
 int32_t fb_gemm_workspace_create(fb_ctx* ctx);
 void fb_gemm_workspace_reset(fb_ctx* ctx, cudaStream_t stream);
 
