@@ -471,7 +471,10 @@ def test_gru_fwd_bwd(fb, I, H, T, B, bias):
 
 # --------------------------------------------------------------------------------- attention ---
 @pytest.mark.parametrize("E,Ev,heads,Lq,Lk,B", [(4, 4, 2, 3, 3, 5), (64, 64, 1, 70, 70, 2), (128, 64, 2, 65, 130, 3),
-                                               (256, 256, 2, 33, 33, 1), (96, 96, 4, 128, 128, 2)])
+                                               (256, 256, 2, 33, 33, 1), (96, 96, 4, 128, 128, 2),
+                                               # head size 64: the tensor-core kernels (several key / query blocks, ragged
+                                               # tails, Lq != Lk); with an explicit mask the same shapes run on the FMA kernels
+                                               (128, 128, 2, 200, 200, 2), (64, 64, 1, 130, 300, 1), (256, 256, 4, 520, 520, 1)])
 @pytest.mark.parametrize("mode", ["none", "causal", "mask"])
 def test_attention_fwd_bwd_scores(fb, E, Ev, heads, Lq, Lk, B, mode):
     if mode == "causal" and Lq != Lk:
