@@ -205,6 +205,30 @@ def test_recurrence_lstm_gru(F):
         assert y2.size == (H, T)
 
 
+def test_multiheadattention_head_size_64_runs_the_tensor_core_kernels(F):
+    """Same checks as the small layer test at a head size the tcgen05 attention kernels take (forward, dQ, dK / dV),
+    over several key / query blocks with a ragged tail."""
+    rng = np.random.default_rng(14)
+    dim, nheads, L, B = 128, 2, 210, 2
+    Ws = [O.glorot_uniform(rng, dim, dim) for _ in range(4)]
+    mha = F.MultiHeadAttention(*Ws, nheads=nheads)
+    q = rng.normal(size=(dim, L, B)).astype(np.float32)
+    qg = F.gpu(q)
+    W64 = [w.astype(np.float64) for w in Ws]
+    for causal in (False, True):
+        mk = (lambda: F.make_causal_mask(qg)) if causal else (lambda: None)
+        omask = O.make_causal_mask(L) if causal else None
+        y, a = mha(qg, mask=mk())
+        yref, aref = O.mha_fwd(*W64, q.astype(np.float64), nheads=nheads, mask=omask)
+        np.testing.assert_allclose(F.cpu(y), yref, atol=1e-4)
+        np.testing.assert_allclose(F.cpu(a.materialize()), aref, atol=1e-4)
+        val, (g,) = F.withgradient(lambda m: F.sum_abs2(m(qg, mask=mk())[0]), mha)
+        dWq, dWk, dWv, dWo, _ = O.mha_bwd(*W64, q.astype(np.float64), O.sum_abs2_bwd(yref), nheads=nheads, mask=omask)
+        for name, ref in [("q_proj", dWq), ("k_proj", dWk), ("v_proj", dWv), ("out_proj", dWo)]:
+            close(F.cpu(g[name]["weight"]), ref, rtol=2e-4, atol_scale=2e-4, name=name)
+    assert F.context().device_error() == 0
+
+
 def test_multiheadattention_layer(F):
     """test/layers/attention.jl:3-63 and test/ext_cuda/layers.jl:343-363 (y and alpha, atol 1e-4)."""
     rng = np.random.default_rng(4)
