@@ -187,3 +187,157 @@ FB_API int32_t fb_comm_async_error(fb_comm* comm, int32_t* out_host) {
   *out_host = err;
   return FB_OK;
 }
+
+// ------------------------------------------------------------------------------------------- gradient buckets ---
+// The native form of the bucketed, overlapped gradient averaging: a flat gradient buffer cut into buckets; every
+// gradient leaf is a slice of it.  The reverse sweep marks a leaf ready when its gradient has been written (stream
+// order); when the last leaf of a bucket is ready the bucket's mean all-reduce starts on the communication stream
+// while the compute stream goes on.  fb_bucket_wait makes the compute stream wait for every bucket.
+struct fb_bucket_set {
+  fb_comm* comm;
+  float* flat;
+  int64_t total;
+  int nbuckets;
+  int64_t* start;        // [nbuckets + 1]
+  int* leaves_in;        // leaves registered per bucket
+  int* pending;          // leaves not yet ready in this step
+  int* launched;
+  cudaEvent_t* ready_ev; // compute stream -> communication stream
+  cudaEvent_t* done_ev;  // communication stream -> compute stream
+  int nleaves, cap_leaves;
+  int* leaf_bucket;
+  unsigned char* leaf_ready;
+  cudaStream_t comm_stream;
+  int own_stream;
+};
+
+static int32_t bucket_launch(fb_bucket_set* b, int bi, cudaStream_t compute) {
+  b->launched[bi] = 1;
+  if (b->comm == nullptr || b->comm->nranks == 1) return FB_OK;   // one worker: the mean is the gradient itself
+  FB_CUDA(cudaEventRecord(b->ready_ev[bi], compute));
+  FB_CUDA(cudaStreamWaitEvent(b->comm_stream, b->ready_ev[bi], 0));
+  float* p = b->flat + b->start[bi];
+  const int32_t st = fb_allreduce(b->comm, (void*)b->comm_stream, p, p, b->start[bi + 1] - b->start[bi], FB_OP_AVG);
+  if (st != FB_OK) return st;
+  FB_CUDA(cudaEventRecord(b->done_ev[bi], b->comm_stream));
+  return FB_OK;
+}
+
+FB_API int32_t fb_bucket_create(fb_ctx* ctx, fb_comm* comm, float* flat, int64_t total, int32_t nbuckets,
+                                const int64_t* bucket_ends_host, void* comm_stream, fb_bucket_set** out) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(out != nullptr, FB_ERR_INVALID_ARG, "fb_bucket_create: out is NULL");
+  *out = nullptr;
+  FB_REQUIRE(flat != nullptr && total >= 1 && nbuckets >= 1 && bucket_ends_host != nullptr, FB_ERR_INVALID_ARG,
+             "fb_bucket_create: bad arguments");
+  int64_t prev = 0;
+  for (int i = 0; i < nbuckets; ++i) {
+    FB_REQUIRE(bucket_ends_host[i] > prev && bucket_ends_host[i] <= total, FB_ERR_INVALID_ARG,
+               "fb_bucket_create: bucket ends must increase and stay inside the buffer");
+    prev = bucket_ends_host[i];
+  }
+  FB_REQUIRE(prev == total, FB_ERR_INVALID_ARG, "fb_bucket_create: the last bucket must end at %lld", (long long)total);
+  FB_CUDA(cudaSetDevice(ctx->device));
+  fb_bucket_set* b = new fb_bucket_set();
+  b->comm = comm; b->flat = flat; b->total = total; b->nbuckets = nbuckets;
+  b->start = new int64_t[nbuckets + 1];
+  b->start[0] = 0;
+  for (int i = 0; i < nbuckets; ++i) b->start[i + 1] = bucket_ends_host[i];
+  b->leaves_in = new int[nbuckets]();
+  b->pending = new int[nbuckets]();
+  b->launched = new int[nbuckets]();
+  b->ready_ev = new cudaEvent_t[nbuckets];
+  b->done_ev = new cudaEvent_t[nbuckets];
+  for (int i = 0; i < nbuckets; ++i) {
+    cudaEventCreateWithFlags(&b->ready_ev[i], cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&b->done_ev[i], cudaEventDisableTiming);
+  }
+  b->nleaves = 0; b->cap_leaves = 64;
+  b->leaf_bucket = new int[b->cap_leaves];
+  b->leaf_ready = new unsigned char[b->cap_leaves];
+  b->comm_stream = (cudaStream_t)comm_stream;
+  b->own_stream = 0;
+  if (b->comm_stream == nullptr) {
+    int lo = 0, hi = 0;
+    cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    if (cudaStreamCreateWithPriority(&b->comm_stream, cudaStreamNonBlocking, hi) != cudaSuccess) {
+      cudaGetLastError();
+      fb_bucket_destroy(b);
+      return fb_fail(FB_ERR_CUDA, "fb_bucket_create: could not create the communication stream");
+    }
+    b->own_stream = 1;
+  }
+  *out = b;
+  return FB_OK;
+}
+
+FB_API int32_t fb_bucket_destroy(fb_bucket_set* b) {
+  if (b == nullptr) return FB_OK;
+  if (b->own_stream && b->comm_stream) {
+    cudaStreamSynchronize(b->comm_stream);
+    cudaStreamDestroy(b->comm_stream);
+  }
+  for (int i = 0; i < b->nbuckets; ++i) {
+    cudaEventDestroy(b->ready_ev[i]);
+    cudaEventDestroy(b->done_ev[i]);
+  }
+  delete[] b->start; delete[] b->leaves_in; delete[] b->pending; delete[] b->launched;
+  delete[] b->ready_ev; delete[] b->done_ev; delete[] b->leaf_bucket; delete[] b->leaf_ready;
+  delete b;
+  return FB_OK;
+}
+
+FB_API int32_t fb_bucket_register(fb_bucket_set* b, int64_t offset, int64_t count, int32_t* leaf_id) {
+  FB_REQUIRE(b != nullptr && leaf_id != nullptr, FB_ERR_INVALID_ARG, "fb_bucket_register: NULL pointer");
+  FB_REQUIRE(offset >= 0 && count >= 1 && offset + count <= b->total, FB_ERR_INVALID_ARG,
+             "fb_bucket_register: slice [%lld, %lld) is outside the buffer", (long long)offset, (long long)(offset + count));
+  int bi = 0;
+  while (bi < b->nbuckets && offset >= b->start[bi + 1]) ++bi;
+  FB_REQUIRE(offset + count <= b->start[bi + 1], FB_ERR_INVALID_ARG, "fb_bucket_register: a leaf must lie inside one bucket");
+  if (b->nleaves == b->cap_leaves) {
+    const int cap = 2 * b->cap_leaves;
+    int* lb = new int[cap];
+    unsigned char* lr = new unsigned char[cap];
+    memcpy(lb, b->leaf_bucket, sizeof(int) * b->nleaves);
+    memcpy(lr, b->leaf_ready, b->nleaves);
+    delete[] b->leaf_bucket; delete[] b->leaf_ready;
+    b->leaf_bucket = lb; b->leaf_ready = lr; b->cap_leaves = cap;
+  }
+  b->leaf_bucket[b->nleaves] = bi;
+  b->leaf_ready[b->nleaves] = 0;
+  b->leaves_in[bi] += 1;
+  b->pending[bi] += 1;
+  *leaf_id = b->nleaves++;
+  return FB_OK;
+}
+
+FB_API int32_t fb_bucket_begin_step(fb_bucket_set* b) {
+  FB_REQUIRE(b != nullptr, FB_ERR_INVALID_ARG, "fb_bucket_begin_step: NULL pointer");
+  for (int i = 0; i < b->nbuckets; ++i) {
+    b->pending[i] = b->leaves_in[i];
+    b->launched[i] = 0;
+  }
+  memset(b->leaf_ready, 0, (size_t)b->nleaves);
+  return FB_OK;
+}
+
+FB_API int32_t fb_bucket_mark_ready(fb_bucket_set* b, int32_t leaf_id, void* compute_stream) {
+  FB_REQUIRE(b != nullptr && leaf_id >= 0 && leaf_id < b->nleaves, FB_ERR_INVALID_ARG, "fb_bucket_mark_ready: bad leaf id %d", leaf_id);
+  if (b->leaf_ready[leaf_id]) return FB_OK;
+  b->leaf_ready[leaf_id] = 1;
+  const int bi = b->leaf_bucket[leaf_id];
+  if (--b->pending[bi] == 0 && !b->launched[bi]) return bucket_launch(b, bi, (cudaStream_t)compute_stream);
+  return FB_OK;
+}
+
+FB_API int32_t fb_bucket_wait(fb_bucket_set* b, void* compute_stream) {
+  FB_REQUIRE(b != nullptr, FB_ERR_INVALID_ARG, "fb_bucket_wait: NULL pointer");
+  for (int i = 0; i < b->nbuckets; ++i)
+    if (!b->launched[i]) {
+      const int32_t st = bucket_launch(b, i, (cudaStream_t)compute_stream);
+      if (st != FB_OK) return st;
+    }
+  if (b->comm != nullptr && b->comm->nranks > 1)
+    for (int i = 0; i < b->nbuckets; ++i) FB_CUDA(cudaStreamWaitEvent((cudaStream_t)compute_stream, b->done_ev[i], 0));
+  return FB_OK;
+}

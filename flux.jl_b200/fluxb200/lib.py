@@ -96,6 +96,12 @@ PROTOTYPES = {
     "fb_allgather": (_i32, [_p, _p, _p, _p, _i64]),
     "fb_bcast": (_i32, [_p, _p, _p, _p, _i64, _i32]),
     "fb_reduce": (_i32, [_p, _p, _p, _p, _i64, _i32, _i32]),
+    "fb_bucket_create": (_i32, [_p, _p, _p, _i64, _i32, C.POINTER(_i64), _p, C.POINTER(_p)]),
+    "fb_bucket_destroy": (_i32, [_p]),
+    "fb_bucket_register": (_i32, [_p, _i64, _i64, C.POINTER(_i32)]),
+    "fb_bucket_begin_step": (_i32, [_p]),
+    "fb_bucket_mark_ready": (_i32, [_p, _i32, _p]),
+    "fb_bucket_wait": (_i32, [_p, _p]),
     "fb_comm_async_error": (_i32, [_p, C.POINTER(_i32)]),
 }
 

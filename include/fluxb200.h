@@ -322,6 +322,24 @@ int32_t fb_allgather(fb_comm* comm, void* stream, const float* send, float* recv
 int32_t fb_bcast(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t root);
 /* DistributedUtils.reduce! (NCCL.Reduce!, FluxMPINCCLExt.jl:86-102). */
 int32_t fb_reduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op, int32_t root);
+
+/* Bucketed, overlapped gradient averaging for DistributedOptimizer (src/distributed/public_api.jl:286-300, which
+ * all-reduces leaf by leaf with no overlap).  `flat` is one gradient buffer of `total` floats cut into `nbuckets`
+ * buckets ending at bucket_ends_host[i] (increasing, the last one == total); every gradient leaf is registered as a
+ * slice lying inside one bucket.  Per step: fb_bucket_begin_step; the reverse sweep calls fb_bucket_mark_ready for
+ * a leaf once the kernels that write its gradient are enqueued on `compute_stream`; when a bucket's last leaf is
+ * ready its mean all-reduce starts on the communication stream (the given one, or a high-priority stream the set
+ * creates when comm_stream is NULL) while the compute stream continues; fb_bucket_wait starts whatever has not
+ * started and makes `compute_stream` wait for all of it.  With one worker nothing is communicated.  Host-side
+ * bookkeeping only: call from the thread that enqueues the step. */
+typedef struct fb_bucket_set fb_bucket_set;
+int32_t fb_bucket_create(fb_ctx* ctx, fb_comm* comm, float* flat, int64_t total, int32_t nbuckets,
+                         const int64_t* bucket_ends_host, void* comm_stream, fb_bucket_set** out);
+int32_t fb_bucket_destroy(fb_bucket_set* set);
+int32_t fb_bucket_register(fb_bucket_set* set, int64_t offset, int64_t count, int32_t* leaf_id);
+int32_t fb_bucket_begin_step(fb_bucket_set* set);
+int32_t fb_bucket_mark_ready(fb_bucket_set* set, int32_t leaf_id, void* compute_stream);
+int32_t fb_bucket_wait(fb_bucket_set* set, void* compute_stream);
 /* Non-zero when NCCL reported an asynchronous error on this communicator (polled by the host between
  * steps; a dead rank otherwise hangs the next collective, as it does in the reference). */
 int32_t fb_comm_async_error(fb_comm* comm, int32_t* out_host);

@@ -45,6 +45,34 @@ def main():
     DU.reduce(backend, buf, "+", root=0)
     assert (F.cpu(buf) == (tot if rank == 0 else rank + 1)).all()
 
+    # native gradient buckets (fb_bucket_*): leaves marked ready out of order, every bucket averaged exactly once
+    import ctypes as C
+    from fluxb200 import lib
+    ctx = F.context()
+    flat = torch.full((1000,), float(rank + 1), device="cuda")
+    ends = (C.c_int64 * 3)(256, 640, 1000)
+    bset = C.c_void_p()
+    lib.call("fb_bucket_create", ctx.handle, backend.comm, C.c_void_p(flat.data_ptr()), 1000, 3, ends, None, C.byref(bset))
+    ids = []
+    for off, cnt in [(0, 100), (100, 156), (256, 384), (640, 200), (840, 160)]:
+        lid = C.c_int32(-1)
+        lib.call("fb_bucket_register", bset, off, cnt, C.byref(lid))
+        ids.append(lid.value)
+    try:
+        lib.call("fb_bucket_register", bset, 200, 100, C.byref(C.c_int32()))
+        raise AssertionError("a leaf that straddles two buckets must be rejected")
+    except lib.FluxB200Error:
+        pass
+    for step in range(2):
+        flat.fill_(float(rank + 1) * (step + 1))
+        lib.call("fb_bucket_begin_step", bset)
+        for lid in (ids[4], ids[2], ids[0], ids[4], ids[1]):     # the last bucket completes first; ids[3] is never marked
+            lib.call("fb_bucket_mark_ready", bset, lid, ctx.stream)
+        lib.call("fb_bucket_wait", bset, ctx.stream)              # starts the bucket that was still pending
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(flat.cpu().numpy(), (step + 1) * tot / world, rtol=1e-6)
+    lib.call("fb_bucket_destroy", bset)
+
     # data container: contiguous ceil(n/N) shards whose sizes add up
     data = np.arange(10 * 7, dtype=np.float32).reshape(7, 10)
     ddc = DU.DistributedDataContainer(backend, data)
