@@ -338,20 +338,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4001);
 }
 
-// Pipelined variant: two K / V stages in shared memory and, in tensor memory, two S buffers (P hi overwrites S in
-// place), two P lo buffers and two P V buffers.  The MMA warp issues Q K' of block j + 1 before P V of block j, so the
-// tensor pipe works on the next scores while the softmax warps are busy with the current ones; the softmax warps add
-// P V of block j - 1 after they have handed P of block j to the tensor core.
-//   TMEM columns: S/P_hi 0..63, 64..127; P_lo 128..191, 192..255; P V 256..319, 320..383 (512 allocated)
-constexpr int P2_QHI = 0, P2_QLO = 32768;
-constexpr int P2_STAGE0 = 65536, P2_STAGE_BYTES = 65536;      // per stage: K hi, K lo, V hi, V lo (16 KB each)
-constexpr int P2_BAR = P2_STAGE0 + 2 * P2_STAGE_BYTES;        // 196608
-constexpr int ATC2_SMEM = P2_BAR + 256 + 1024;
-enum { C_QFULL = 0, C_QREADY, C_KFULL, C_KREADY = C_KFULL + 2, C_KFREE = C_KREADY + 2, C_VFULL = C_KFREE + 2, C_VREADY = C_VFULL + 2,
-       C_VFREE = C_VREADY + 2, C_SFULL = C_VFREE + 2, C_PREADY = C_SFULL + 2, C_OFULL = C_PREADY + 2, C_COUNT = C_OFULL + 2 };
+// Pipelined variant: three K / V stages in shared memory (a K tile is reloaded three blocks ahead, which covers the
+// latency of its TMA load); Q lives in tensor memory as the A operand of Q K' (hi and lo parts, stored once by the
+// softmax warps), next to two S buffers (P hi overwrites S in place), two P lo buffers and two P V buffers.  The MMA
+// warp issues Q K' of block j + 1 before P V of block j, so the tensor pipe works on the next scores while the softmax
+// warps are busy with the current ones; the softmax warps add P V of block j - 1 after they have handed P of block j
+// to the tensor core.
+//   TMEM columns: Q hi 0..63, Q lo 64..127; S/P_hi 128.., 192..; P_lo 256.., 320..; P V 384.., 448..
+constexpr int P2_NSTAGE = 3;
+constexpr int P2_STAGE0 = 0, P2_STAGE_BYTES = 65536;          // per stage: K hi, K lo, V hi, V lo (16 KB each)
+constexpr int P2_BAR = P2_STAGE0 + P2_NSTAGE * P2_STAGE_BYTES;   // 196608
+constexpr int ATC2_SMEM = P2_BAR + 512 + 1024;
+enum { C_QREADY = 0, C_KFULL, C_KREADY = C_KFULL + 3, C_KFREE = C_KREADY + 3, C_VFULL = C_KFREE + 3, C_VREADY = C_VFULL + 3,
+       C_VFREE = C_VREADY + 3, C_SFULL = C_VFREE + 3, C_PREADY = C_SFULL + 2, C_OFULL = C_PREADY + 2, C_COUNT = C_OFULL + 2 };
 
 __global__ void __launch_bounds__(ATC_THREADS, 1)
-attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+attn_fwd_tc2_kernel(const float* __restrict__ qmat, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, float* __restrict__ o, float* __restrict__ lse, AtcDims D,
                     int32_t* __restrict__ dev_err) {
   extern __shared__ uint8_t smem_raw[];
@@ -373,15 +375,16 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int nkb = (int)((kv_end + KT - 1) / KT);
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(C_QFULL), 1);
     mbar_init(bar(C_QREADY), 4);
-    for (int st = 0; st < 2; ++st) {
+    for (int st = 0; st < P2_NSTAGE; ++st) {
       mbar_init(bar(C_KFULL + st), 1);
       mbar_init(bar(C_KREADY + st), 4);
       mbar_init(bar(C_KFREE + st), 1);
       mbar_init(bar(C_VFULL + st), 1);
       mbar_init(bar(C_VREADY + st), 4);
       mbar_init(bar(C_VFREE + st), 1);
+    }
+    for (int st = 0; st < 2; ++st) {
       mbar_init(bar(C_SFULL + st), 1);
       mbar_init(bar(C_PREADY + st), 4);
       mbar_init(bar(C_OFULL + st), 1);
@@ -402,24 +405,22 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
-  // block j uses stage / buffer j & 1 for the (j >> 1)-th time: barrier parity (j >> 1) & 1
+  // block j uses TMEM buffer j & 1 for the (j >> 1)-th time and shared-memory stage j % 3 for the (j / 3)-th time
   auto par = [](int j) { return (uint32_t)(j >> 1) & 1u; };
+  auto par3 = [](int j) { return (uint32_t)(j / P2_NSTAGE) & 1u; };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer ---
     if (lane == 0) {
-      const int qrow = (int)(b * D.Lq + i0), krow0 = (int)(b * D.Lk);
-      mbar_arrive_expect_tx(bar(C_QFULL), 32768u);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tma_load_2d(sb + P2_QHI + c * 8192, &tmQ, h * HD + 16 * c, qrow, bar(C_QFULL));
+      const int krow0 = (int)(b * D.Lk);
       for (int j = 0; j < nkb; ++j) {
-        const int st = j & 1;
+        const int st = j % P2_NSTAGE;
         const uint32_t base = sb + P2_STAGE0 + (uint32_t)(st * P2_STAGE_BYTES);
-        if (j >= 2 && !mbar_wait(bar(C_KFREE + st), par(j - 2), s_abort)) break;
+        if (j >= P2_NSTAGE && !mbar_wait(bar(C_KFREE + st), par3(j - P2_NSTAGE), s_abort)) break;
         mbar_arrive_expect_tx(bar(C_KFULL + st), 16384u);
 #pragma unroll
         for (int c = 0; c < 4; ++c) tma_load_2d(base + c * 4096, &tmK, h * HD + 16 * c, krow0 + j * KT, bar(C_KFULL + st));
-        if (j >= 2 && !mbar_wait(bar(C_VFREE + st), par(j - 2), s_abort)) break;
+        if (j >= P2_NSTAGE && !mbar_wait(bar(C_VFREE + st), par3(j - P2_NSTAGE), s_abort)) break;
         mbar_arrive_expect_tx(bar(C_VFULL + st), 16384u);
         tma_load_3d(base + 32768, &tmV, 0, krow0 + j * KT, 2 * h, bar(C_VFULL + st));
       }
@@ -431,41 +432,41 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t idesc_pv = idesc_qk | (1u << 16);
       // descriptors differ only in their 14-bit start-address field (units of 16 bytes): build one per tile and add
       // the per-k-step offsets, so that issuing an MMA costs a couple of integer adds
-      const uint64_t dq_hi = make_smem_desc(sb + P2_QHI, 16, 512, LAYOUT_SW64), dq_lo = make_smem_desc(sb + P2_QLO, 16, 512, LAYOUT_SW64);
       auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(bar(C_KREADY + st), par(j), s_abort)) return false;
+        const int st = j % P2_NSTAGE, buf = j & 1;
+        if (!mbar_wait(bar(C_KREADY + st), par3(j), s_abort)) return false;
         tc_fence_after();
         const uint32_t kb = sb + P2_STAGE0 + (uint32_t)(st * P2_STAGE_BYTES);
         const uint64_t dk_hi = make_smem_desc(kb, 16, 512, LAYOUT_SW64), dk_lo = make_smem_desc(kb + 16384, 16, 512, LAYOUT_SW64);
-        const uint32_t d = tmem_base + (uint32_t)(64 * st);
+        const uint32_t d = tmem_base + 128u + (uint32_t)(64 * buf);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t qo = (uint64_t)(((ks >> 1) * 8192 + (ks & 1) * 32) >> 4), ko = (uint64_t)(((ks >> 1) * 4096 + (ks & 1) * 32) >> 4);
-          tc_mma_tf32(d, dq_lo + qo, dk_hi + ko, idesc_qk, ks > 0 ? 1u : 0u);
-          tc_mma_tf32(d, dq_hi + qo, dk_lo + ko, idesc_qk, 1u);
-          tc_mma_tf32(d, dq_hi + qo, dk_hi + ko, idesc_qk, 1u);
+          const uint64_t ko = (uint64_t)(((ks >> 1) * 4096 + (ks & 1) * 32) >> 4);
+          const uint32_t ao = (uint32_t)(8 * ks);
+          tc_mma_tf32_ta(d, tmem_base + 64u + ao, dk_hi + ko, idesc_qk, ks > 0 ? 1u : 0u);
+          tc_mma_tf32_ta(d, tmem_base + ao, dk_lo + ko, idesc_qk, 1u);
+          tc_mma_tf32_ta(d, tmem_base + ao, dk_hi + ko, idesc_qk, 1u);
         }
-        tc_commit(bar(C_SFULL + st));
+        tc_commit(bar(C_SFULL + buf));
         tc_commit(bar(C_KFREE + st));
         return true;
       };
       bool ok = mbar_wait(bar(C_QREADY), 0u, s_abort);
       ok = ok && issue_qk(0);
       for (int j = 0; j < nkb && ok; ++j) {
-        const int st = j & 1;
+        const int st = j % P2_NSTAGE, buf = j & 1;
         if (j + 1 < nkb) {
           ok = issue_qk(j + 1);
           if (!ok) break;
         }
-        ok = mbar_wait(bar(C_PREADY + st), par(j), s_abort) && mbar_wait(bar(C_VREADY + st), par(j), s_abort);
+        ok = mbar_wait(bar(C_PREADY + buf), par(j), s_abort) && mbar_wait(bar(C_VREADY + st), par3(j), s_abort);
         if (!ok) break;
         tc_fence_after();
         const uint32_t vb = sb + P2_STAGE0 + (uint32_t)(st * P2_STAGE_BYTES) + 32768;
-        const uint32_t d = tmem_base + 256u + (uint32_t)(64 * st);
+        const uint32_t d = tmem_base + 384u + (uint32_t)(64 * buf);
         const uint64_t dv_hi = make_smem_desc(vb, KT * 128, 512, LAYOUT_SW128_32B);
         const uint64_t dv_lo = make_smem_desc(vb + 16384, KT * 128, 512, LAYOUT_SW128_32B);
-        const uint32_t a_hi0 = tmem_base + (uint32_t)(64 * st), a_lo0 = a_hi0 + 128u;
+        const uint32_t a_hi0 = tmem_base + 128u + (uint32_t)(64 * buf), a_lo0 = a_hi0 + 128u;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t vo = (uint64_t)((ks * 1024) >> 4);
@@ -473,7 +474,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_mma_tf32_ta(d, a_hi0 + (uint32_t)(8 * ks), dv_lo + vo, idesc_pv, 1u);
           tc_mma_tf32_ta(d, a_hi0 + (uint32_t)(8 * ks), dv_hi + vo, idesc_pv, 1u);
         }
-        tc_commit(bar(C_OFULL + st));
+        tc_commit(bar(C_OFULL + buf));
         tc_commit(bar(C_VFREE + st));
       }
     }
@@ -488,14 +489,37 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
     for (int c = 0; c < HD; ++c) acc[c] = 0.0f;
     bool ok = true;
+    {
+      // Q row of this thread into tensor memory: the raw value is the hi operand, lo = x - tf32(x)
+      const float* src = qmat + (b * D.Lq + gi) * D.E + (int64_t)h * HD;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t hi[32], lo[32];
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (gi < D.Lq) x = __ldg((const float4*)(src + 32 * hf + 4 * c4));
+          hi[4 * c4] = __float_as_uint(x.x); hi[4 * c4 + 1] = __float_as_uint(x.y);
+          hi[4 * c4 + 2] = __float_as_uint(x.z); hi[4 * c4 + 3] = __float_as_uint(x.w);
+          lo[4 * c4] = __float_as_uint(tf32_lo(x.x)); lo[4 * c4 + 1] = __float_as_uint(tf32_lo(x.y));
+          lo[4 * c4 + 2] = __float_as_uint(tf32_lo(x.z)); lo[4 * c4 + 3] = __float_as_uint(tf32_lo(x.w));
+        }
+        tc_st_32x32b_x32(t_row + (uint32_t)(32 * hf), hi);
+        tc_st_32x32b_x32(t_row + (uint32_t)(64 + 32 * hf), lo);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C_QREADY));
+    }
     // adds P V of block jj to the accumulators (waits for its MMAs)
     auto add_pv = [&](int jj) -> bool {
       const int st = jj & 1;
       if (!mbar_wait(bar(C_OFULL + st), par(jj), s_abort)) return false;
       tc_fence_after();
       uint32_t v0[32], v1[32];
-      tc_ld_32x32b_x32(t_row + 256u + (uint32_t)(64 * st), v0);
-      tc_ld_32x32b_x32(t_row + 288u + (uint32_t)(64 * st), v1);
+      tc_ld_32x32b_x32(t_row + 384u + (uint32_t)(64 * st), v0);
+      tc_ld_32x32b_x32(t_row + 416u + (uint32_t)(64 * st), v1);
       tc_wait_ld();
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
@@ -511,7 +535,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       uint32_t s0[32], s1[32];
-      const uint32_t t_s = t_row + (uint32_t)(64 * st);
+      const uint32_t t_s = t_row + 128u + (uint32_t)(64 * st);
       tc_ld_32x32b_x32(t_s, s0);
       tc_ld_32x32b_x32(t_s + 32u, s1);
       tc_wait_ld();
@@ -599,19 +623,15 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       fence_proxy_async();
       __syncwarp();
     };
-    bool ok = mbar_wait(bar(C_QFULL), 0u, s_abort);
-    if (ok) {
-      split(P2_QHI, P2_QLO, 16);
-      if (lane == 0) mbar_arrive(bar(C_QREADY));
-    }
+    bool ok = true;
     for (int j = 0; j < nkb && ok; ++j) {
-      const int st = j & 1;
+      const int st = j % P2_NSTAGE;
       const int base = P2_STAGE0 + st * P2_STAGE_BYTES;
-      ok = mbar_wait(bar(C_KFULL + st), par(j), s_abort);
+      ok = mbar_wait(bar(C_KFULL + st), par3(j), s_abort);
       if (!ok) break;
       split(base, base + 16384, 8);
       if (lane == 0) mbar_arrive(bar(C_KREADY + st));
-      ok = mbar_wait(bar(C_VFULL + st), par(j), s_abort);
+      ok = mbar_wait(bar(C_VFULL + st), par3(j), s_abort);
       if (!ok) break;
       split(base + 32768, base + 49152, 8);
       if (lane == 0) mbar_arrive(bar(C_VREADY + st));
@@ -1258,7 +1278,7 @@ int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const f
   dim3 grid((unsigned)((lq + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
   if (attn_pipelined()) {
     FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC2_SMEM));
-    attn_fwd_tc2_kernel<<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
+    attn_fwd_tc2_kernel<<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(q, tmK, tmV, o, lse, D, ctx->dev_error);
   } else if (attn_p_in_tmem()) {
     FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
     attn_fwd_tc_kernel<true><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
