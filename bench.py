@@ -391,6 +391,15 @@ def run_small_config(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / steps
 
+    def time_grad(fn, model, steps, warmup):
+        """ms per forward + gradient: one CUDA-graph replay per call where the step can be captured, else eager launches."""
+        try:
+            gg = F.GraphedGradient(fn, model)
+            return time_gpu(lambda: gg(), steps, warmup), "CUDA graph replay"
+        except Exception:
+            torch.cuda.synchronize()
+            return time_gpu(lambda: F.withgradient(fn, model), steps, warmup), "eager launches"
+
     def time_cpu(fn, reps=2):
         best = None
         for _ in range(reps):
@@ -425,7 +434,7 @@ def run_small_config(args):
         xb = (rng.standard_normal((32, 32, 256, 128), dtype=np.float32) * 2 + 0.5)
         bn = F.trainmode(F.BatchNorm(256, "relu"))
         xg = F.gpu(xb)
-        ms = time_gpu(lambda: F.withgradient(lambda m: F.sum_abs2(m(xg)), bn), args.steps, args.warmup)
+        ms, how = time_grad(lambda m: F.sum_abs2(m(xg)), bn, args.steps, args.warmup)
         E = xb.size
         xs = xb[:, :, :, :8]
         cpu = time_cpu(lambda: (O.batchnorm_fwd_train(xs, np.ones(256, np.float32), np.zeros(256, np.float32), np.zeros(256, np.float32), np.ones(256, np.float32), sigma="relu"),
@@ -433,19 +442,19 @@ def run_small_config(args):
         by = 11.0 * E * 4
         lines.append(("batchnorm: BatchNorm(256,relu) train, 32x32x256x128 Float32, forward + gradient of sum(abs2,y)", 128, ms,
                       {"bound": "hbm", "achieved": by / ms / 1e6, "peak": hbm, "unit": "GB/s", "frac": by / ms / 1e6 / hbm, "traffic": None,
-                       "note": "11 passes x 134.2 MB: layer (8) + sum(abs2) read (1) + cotangent 2y read+write (2)"},
+                       "note": "11 passes x 134.2 MB: layer (8) + sum(abs2) read (1) + cotangent 2y read+write (2); " + how},
                       8 / cpu, "8 of 128 samples, best of 2"))
         xl = rng.standard_normal((4096, 16384), dtype=np.float32)
         ln = F.LayerNorm(4096)
         xlg = F.gpu(xl)
-        ms = time_gpu(lambda: F.withgradient(lambda m: F.sum_abs2(m(xlg)), ln), args.steps, args.warmup)
+        ms, how = time_grad(lambda m: F.sum_abs2(m(xlg)), ln, args.steps, args.warmup)
         xls = xl[:, :1024]
         g1, b1 = np.ones(4096, np.float32), np.zeros(4096, np.float32)
         cpu = time_cpu(lambda: (O.layernorm_fwd(xls, g1, b1), O.layernorm_bwd(xls, g1, b1, 2 * xls)))
         by = 8.0 * xl.size * 4
         lines.append(("layernorm: LayerNorm(4096) on 4096x16384 Float32, forward + gradient of sum(abs2,y)", 16384, ms,
                       {"bound": "hbm", "achieved": by / ms / 1e6, "peak": hbm, "unit": "GB/s", "frac": by / ms / 1e6 / hbm, "traffic": None,
-                       "note": "8 passes x 268.4 MB: layer (5) + sum(abs2) read (1) + cotangent 2y read+write (2)"},
+                       "note": "8 passes x 268.4 MB: layer (5) + sum(abs2) read (1) + cotangent 2y read+write (2); " + how},
                       1024 / cpu, "1024 of 16384 samples, best of 2"))
     elif args.config == 3:
         Hh, T, B = 512, 256, 64
@@ -469,7 +478,7 @@ def run_small_config(args):
         x = rng.standard_normal((E, S, B), dtype=np.float32)
         mha = F.MultiHeadAttention(*Ws, nheads=Hn)
         xg = F.gpu(x)
-        ms = time_gpu(lambda: F.withgradient(lambda m: F.sum_abs2(m(xg, mask=F.make_causal_mask())[0]), mha), args.steps, args.warmup)
+        ms, how = time_grad(lambda m: F.sum_abs2(m(xg, mask=F.make_causal_mask())[0]), mha, args.steps, args.warmup)
         xs = x[:, :512, :1]
         def cpu_fn():
             y, _ = O.mha_fwd(*Ws, xs, nheads=Hn, mask=O.make_causal_mask(512))
@@ -478,7 +487,7 @@ def run_small_config(args):
         flops = 652.8e9
         lines.append(("mha: MultiHeadAttention(1024, nheads=16), causal, 1024x2048x8 Float32, forward + backward (loss on y)", 8, ms,
                       {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": tf32, "unit": "TFLOP/s", "frac": flops / ms / 1e9 / tf32, "traffic": None,
-                       "note": "projections and the attention core (forward, dQ, dK/dV) on tcgen05 with 3xTF32; softmax and dS on TMEM read-back"},
+                       "note": "projections and the attention core (forward, dQ, dK/dV) on tcgen05 with 3xTF32; softmax and dS on TMEM read-back; " + how},
                       (1 * (512 / 2048) ** 2 * 1.0) / cpu * 1.0, "1 of 8 samples at seq 512 (1/16 of a sample's attention work, 1/4 of its projections), 1 run"))
     if F.context().device_error() != 0:
         raise SystemExit("a kernel recorded a bounded-wait timeout; the numbers are invalid")

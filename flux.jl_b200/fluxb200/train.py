@@ -359,6 +359,31 @@ def _copy_into(dst, src):
         dst.labels.t.copy_(t, non_blocking=True)
 
 
+class GraphedGradient:
+    """`withgradient(f, model)` for fixed input buffers as ONE CUDA-graph launch (forward + reverse sweep).
+
+    `f(model)` must close over device arrays that are updated in place between calls.  `graph()` replays the captured
+    launch sequence and returns the loss array (device scalar) and the gradient tree, whose arrays are the same
+    buffers on every call.  BatchNorm running statistics advance on every replay, as they would in eager calls.
+    Kernels that need a cooperative launch (the persistent recurrent kernels) cannot be captured: construction then
+    raises and the caller should stay with `withgradient`."""
+
+    def __init__(self, f, model):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            _withgradient_device(f, model)          # warm-up: grows the scratch arena and torch's pools
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss, _, self.tree = _withgradient_device(f, model)
+
+    def __call__(self):
+        self.graph.replay()
+        return self.loss, self.tree
+
+
 class GraphedTrainStep:
     """`trainstep!` for a fixed batch shape as ONE CUDA-graph launch: forward, reverse sweep, gradient averaging
     (when `opt_state` wraps a DistributedOptimizer) and the Adam update are captured once and replayed.
