@@ -367,6 +367,22 @@ FB_API int32_t fb_axpy(fb_ctx* ctx, void* stream, float alpha, const float* x, f
   return FB_OK;
 }
 
+__global__ void __launch_bounds__(EW_THREADS)
+round_bf16_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t count) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < count; i += stride) y[i] = __uint_as_float((uint32_t)f32_to_bf16_bits(x[i]) << 16);
+}
+
+FB_API int32_t fb_round_bf16(fb_ctx* ctx, void* stream, const float* x, float* y, int64_t count) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(count >= 0, FB_ERR_INVALID_ARG, "fb_round_bf16: negative count");
+  if (count == 0) return FB_OK;
+  FB_REQUIRE(x && y, FB_ERR_INVALID_ARG, "fb_round_bf16: NULL pointer");
+  round_bf16_kernel<<<ew_grid(ctx, count), EW_THREADS, 0, (cudaStream_t)stream>>>(x, y, count);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}
+
 FB_API int32_t fb_cast_f32_bf16(fb_ctx* ctx, void* stream, const float* x, uint16_t* y, int64_t count) {
   FB_CHECK_CTX(ctx);
   FB_REQUIRE(count >= 0, FB_ERR_INVALID_ARG, "fb_cast_f32_bf16: negative count");

@@ -8,7 +8,7 @@ from . import lib
 from .core import B200Array, Tape, context, cpu, empty, gpu, zeros
 from .layers import (ArgumentError, AttnScores, BatchNorm, CausalMask, Chain, Dense, DimensionMismatch, GRU, GRUCell,
                      LSTM, LSTMCell, Layer, LayerNorm, MultiHeadAttention, Recurrence, dot_product_attention,
-                     make_causal_mask, testmode, trainables, trainmode)
+                     make_causal_mask, testmode, trainables, trainmode, bf16, f32)
 from .train import (Adam, Descent, DomainError, GraphedGradient, GraphedTrainStep, OneHotLabels, gradient, logitcrossentropy, onehotbatch, setup, scale, sum_abs2, sum_all,
                     train, trainstep, update, withgradient)
 from . import distributed as DistributedUtils

@@ -98,6 +98,43 @@ class Chain(Layer):
         return "Chain(" + ", ".join(map(repr, self.layers)) + ")"
 
 
+def _round_bf16(a: B200Array) -> B200Array:
+    """In place: every element becomes Float32(BFloat16(element)) (round to nearest even, NaN -> canonical NaN)."""
+    ctx = context()
+    lib.call("fb_round_bf16", ctx.handle, ctx.stream, a.ptr, a.ptr, a.numel())
+    return a
+
+
+def bf16(m):
+    """Flux.bf16 (src/functor.jl:274, 137-183): the opt-in low-precision path.  For a model: every trainable array is
+    rounded to its BFloat16 value (kept in Float32 storage) and its Dense layers switch to the bf16 GEMM path
+    (single TF32 pass: exact products of bf16 values, Float32 accumulation, outputs and gradients rounded to bf16).
+    BatchNorm statistics and affine parameters stay Float32 (normalise.jl:513-519).  For an array: a rounded copy."""
+    if isinstance(m, B200Array):
+        out = empty(m.size)
+        ctx = context()
+        lib.call("fb_round_bf16", ctx.handle, ctx.stream, m.ptr, out.ptr, m.numel())
+        return out
+    for layer in _walk(m):
+        if isinstance(layer, BatchNorm):
+            continue
+        if isinstance(layer, Dense):
+            layer.precision = "bf16"
+        for name in layer.trainable_fields():
+            v = getattr(layer, name, None)
+            if isinstance(v, B200Array):
+                _round_bf16(v)
+    return m
+
+
+def f32(m):
+    """Flux.f32: back to the Float32 path (values are already Float32 storage; only the GEMM path changes)."""
+    for layer in _walk(m):
+        if isinstance(layer, Dense) and layer.precision == "bf16":
+            layer.precision = "default"
+    return m
+
+
 # ------------------------------------------------------------------------------------ Dense ---
 class Dense(Layer):
     """Dense(W, bias, sigma): y = sigma.(W*x .+ b) (basic.jl:179-205). `bias=False` means no bias."""
@@ -139,6 +176,9 @@ class Dense(Layer):
         z = empty(y.size) if (recording and self.σ in ("gelu", "gelu_tanh", "gelu_erf")) else None
         lib.call("fb_dense_fwd", ctx.handle, ctx.stream, act, prec, self.weight.ptr, _ptr(b), x.ptr, y.ptr, _ptr(z),
                  out_dim, in_dim, n)
+        lowp = self.precision == "bf16"
+        if lowp:
+            _round_bf16(y)
         if recording:
             W = self.weight
 
@@ -152,6 +192,10 @@ class Dense(Layer):
                 delta = empty(y.size) if act != 0 else None
                 lib.call("fb_dense_bwd", ctx.handle, ctx.stream, act, prec, W.ptr, x.ptr, y.ptr, _ptr(z), dy.ptr,
                          _ptr(delta), dW.ptr, _ptr(db), _ptr(dx), out_dim, in_dim, n)
+                if lowp:   # a bf16 model's gradients are bf16 values too
+                    for g in (dW, db, dx):
+                        if g is not None:
+                            _round_bf16(g)
                 res = [(W, dW)]
                 if b is not None:
                     res.append((b, db))

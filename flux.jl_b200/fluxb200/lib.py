@@ -17,7 +17,8 @@ ERR_NAMES = {-1: "FB_ERR_INVALID_ARG", -2: "FB_ERR_SHAPE", -3: "FB_ERR_ALLOC", -
              -5: "FB_ERR_NCCL", -6: "FB_ERR_TIMEOUT", -7: "FB_ERR_UNSUPPORTED"}
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "sigmoid": 3, "gelu_tanh": 4, "gelu": 4, "gelu_erf": 5}
-PREC = {"default": 0, "fp32_simt": 1, "3xtf32": 2, "tf32": 3, "3xtf32_pair": 4}
+# "bf16": operands hold bf16 values (see fluxb200.bf16); the GEMM is the single TF32 pass, exact for such operands
+PREC = {"default": 0, "fp32_simt": 1, "3xtf32": 2, "tf32": 3, "3xtf32_pair": 4, "bf16": 3}
 OP = {"+": 0, "sum": 0, "avg": 1}
 UNIQUE_ID_BYTES = 128
 
@@ -72,6 +73,7 @@ PROTOTYPES = {
     "fb_axpy": (_i32, [_p, _p, _f, _p, _p, _i64]),
     "fb_cast_f32_bf16": (_i32, [_p, _p, _p, _p, _i64]),
     "fb_cast_bf16_f32": (_i32, [_p, _p, _p, _p, _i64]),
+    "fb_round_bf16": (_i32, [_p, _p, _p, _p, _i64]),
     "fb_adam_step": (_i32, [_p, _p, _i32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_p),
                             C.POINTER(_i64), _f, _f, _f, _f, _f, _f, _f]),
     "fb_adam_step_dev": (_i32, [_p, _p, _i32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_p),

@@ -214,6 +214,11 @@ int32_t fb_axpy(fb_ctx* ctx, void* stream, float alpha, const float* x, float* y
  * with Flux._to_bf16 (src/functor.jl:161-166). */
 int32_t fb_cast_f32_bf16(fb_ctx* ctx, void* stream, const float* x, uint16_t* y, int64_t count);
 int32_t fb_cast_bf16_f32(fb_ctx* ctx, void* stream, const uint16_t* x, float* y, int64_t count);
+/* y[i] = Float32(BFloat16(x[i])): the value a bf16 model holds, kept in a Float32 container (in place when y == x).
+ * The opt-in bf16 path (Flux.bf16, src/functor.jl:274) keeps bf16-valued operands in Float32 storage: products of
+ * such values are exact on the single-pass TF32 tensor path and accumulate in Float32, which is the arithmetic of a
+ * bf16 tensor-core GEMM; results are rounded back with this call. */
+int32_t fb_round_bf16(fb_ctx* ctx, void* stream, const float* x, float* y, int64_t count);
 
 /* ------------------------------------------------------------------------------- Adam -- */
 

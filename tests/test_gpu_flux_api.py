@@ -205,6 +205,54 @@ def test_recurrence_lstm_gru(F):
         assert y2.size == (H, T)
 
 
+def test_bf16_model_runs_the_low_precision_dense_path(F):
+    """bf16(model) (src/functor.jl:274): parameters hold BFloat16 values, Dense multiplies them exactly and accumulates
+    in Float32, outputs and gradients are BFloat16 values; tolerance 2e-2 against the Float64 oracle on the same
+    rounded operands (in fact within a bf16 ulp)."""
+    rng = np.random.default_rng(21)
+    W1, W2 = O.glorot_uniform(rng, 96, 64), O.glorot_uniform(rng, 32, 96)
+    b1 = (rng.normal(size=96) * 0.1).astype(np.float32)
+    x = rng.normal(size=(64, 50)).astype(np.float32)
+    model = F.bf16(F.Chain(F.Dense(W1, b1, "relu"), F.Dense(W2, False)))
+    xb = F.bf16(F.gpu(x))
+    is_bf16 = lambda a: ((np.asarray(a, np.float32).view(np.uint32) & 0xFFFF) == 0).all()
+    assert is_bf16(F.cpu(model.layers[0].weight)) and is_bf16(F.cpu(model.layers[0].bias)) and is_bf16(F.cpu(xb))
+    np.testing.assert_array_equal(F.cpu(model.layers[0].weight), O.bf16_round(W1))
+    y = F.cpu(model(xb))
+    assert is_bf16(y)
+    W1r, W2r, b1r, xr = (O.bf16_round(a).astype(np.float64) for a in (W1, W2, b1, x))
+    h = O.bf16_round(O.dense_fwd(W1r, b1r, xr, "relu").astype(np.float32)).astype(np.float64)
+    yref = O.dense_fwd(W2r, None, h)
+    np.testing.assert_allclose(y, yref, rtol=2e-2, atol=2e-2 * np.abs(yref).max())
+    assert np.abs(y - yref).max() <= 2.0 ** -7 * np.abs(yref).max()
+    val, (g,) = F.withgradient(lambda m: F.sum_abs2(m(xb)), model)
+    assert is_bf16(F.cpu(g["layers"][0]["weight"])) and is_bf16(F.cpu(g["layers"][1]["weight"]))
+    dy = O.sum_abs2_bwd(yref)
+    dW2, _, dh = O.dense_bwd(W2r, None, h, dy)
+    np.testing.assert_allclose(F.cpu(g["layers"][1]["weight"]), dW2, rtol=2e-2, atol=2e-2 * np.abs(dW2).max())
+    dW1, _, _ = O.dense_bwd(W1r, b1r, xr, dh, "relu")
+    np.testing.assert_allclose(F.cpu(g["layers"][0]["weight"]), dW1, rtol=2e-2, atol=2e-2 * np.abs(dW1).max())
+    F.f32(model)
+    assert model.layers[0].precision == "default"
+
+
+def test_graphed_gradient_replays_withgradient(F):
+    rng = np.random.default_rng(22)
+    W = O.glorot_uniform(rng, 48, 32)
+    model = F.Chain(F.LayerNorm(32), F.Dense(W, True, "gelu"))
+    x0, x1 = (rng.normal(size=(32, 20)).astype(np.float32) for _ in range(2))
+    xg = F.gpu(x0)
+    fn = lambda m: F.sum_abs2(m(xg))
+    gg = F.GraphedGradient(fn, model)
+    for xv in (x0, x1, x0):
+        xg.t.copy_(F.gpu(xv).t)                 # new values in the same device buffer
+        loss, tree = gg()
+        val, (g,) = F.withgradient(fn, model)
+        assert abs(float(F.cpu(loss)) - val) <= 1e-6 * abs(val)
+        np.testing.assert_allclose(F.cpu(tree["layers"][1]["weight"]), F.cpu(g["layers"][1]["weight"]), rtol=1e-6, atol=1e-7)
+        np.testing.assert_allclose(F.cpu(tree["layers"][0]["diag"]["scale"]), F.cpu(g["layers"][0]["diag"]["scale"]), rtol=1e-6, atol=1e-7)
+
+
 def test_multiheadattention_head_size_64_runs_the_tensor_core_kernels(F):
     """Same checks as the small layer test at a head size the tcgen05 attention kernels take (forward, dQ, dK / dV),
     over several key / query blocks with a ragged tail."""
