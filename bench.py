@@ -279,7 +279,10 @@ def run_ours(args):
         gstep = F.GraphedTrainStep(loss_fn, model, opt, (x_dev, y_dev), grad_sink=buckets, shard_optimizer=not args.no_shard)
         launches_per_step = (lib.raw().fb_kernel_launches() - k0) // 2      # warm-up pass + captured pass
         step_resident = lambda: gstep(x_dev, y_dev)                          # inputs already in HBM
-        step_e2e = lambda: gstep(x_host, lab_host)                           # pinned host -> static device buffers
+        # end to end: every step copies one batch from pinned host memory (the batch of the FOLLOWING step, started
+        # right after this step's launch so that it travels beside the computation) and reads the loss back
+        gstep.prefetch(x_host, lab_host)
+        step_e2e = lambda: gstep(prefetch=(x_host, lab_host))
 
     for _ in range(max(args.warmup, 3)):
         step_resident()

@@ -406,6 +406,8 @@ class GraphedTrainStep:
             raise lib.FluxB200Error(-7, "GraphedTrainStep supports the Adam rule")
         self.model, self.opt_state, self.sink = model, opt_state, grad_sink
         self.static = tuple(_clone_static(b) for b in example_batch)
+        self._stage = self._copy_stream = self._staged_ev = self._consumed_ev = None
+        self._has_prefetch = False
         self.params = [p for p in opt_state.params]
         seen = set()
         self.params = [p for p in self.params if not (id(p) in seen or seen.add(id(p)))]
@@ -470,11 +472,42 @@ class GraphedTrainStep:
         self.loss_arr = loss_arr
         self._updated = ps
 
-    def __call__(self, *batch):
-        for dst, src in zip(self.static, batch):
-            if src is not dst:
+    def prefetch(self, *batch):
+        """Starts copying the NEXT step's inputs (pinned host tensors, or device arrays) into staging buffers on a copy
+        stream, so that the transfer runs beside the step that is executing; `step()` without arguments then uses them."""
+        if self._stage is None:
+            self._stage = tuple(_clone_static(b) for b in self.static)
+            self._copy_stream = torch.cuda.Stream()
+            self._staged_ev = torch.cuda.Event()
+        if self._consumed_ev is not None:
+            self._copy_stream.wait_event(self._consumed_ev)   # the previous batch must have left the staging buffers
+        with torch.cuda.stream(self._copy_stream):
+            for dst, src in zip(self._stage, batch):
                 _copy_into(dst, src)
+            self._staged_ev.record(self._copy_stream)
+        self._has_prefetch = True
+
+    def __call__(self, *batch, prefetch=None):
+        """One train step.  `step(x, y)` copies the batch into the step's static buffers first; `step()` takes the batch
+        handed to `prefetch` earlier; `prefetch=(x, y)` starts the transfer of the following batch right after this
+        step has been launched (before the loss is read back)."""
+        cur = torch.cuda.current_stream()
+        if not batch:
+            if not self._has_prefetch:
+                raise lib.FluxB200Error(-1, "GraphedTrainStep: step() without arguments needs a prefetched batch")
+            cur.wait_event(self._staged_ev)
+            for dst, src in zip(self.static, self._stage):
+                _copy_into(dst, src)
+            self._consumed_ev = torch.cuda.Event()
+            self._consumed_ev.record(cur)
+            self._has_prefetch = False
+        else:
+            for dst, src in zip(self.static, batch):
+                if src is not dst:
+                    _copy_into(dst, src)
         self.graph.replay()
+        if prefetch is not None:
+            self.prefetch(*prefetch)
         lv = float(self.loss_arr.t.item())
         if math.isfinite(lv):
             rule = self.opt_state.rule

@@ -376,3 +376,15 @@ def test_graphed_trainstep_equals_eager_and_skips_on_nan(F):
     # and the step keeps working afterwards
     l3 = gstep(xg, yg)
     assert np.isfinite(l3) and l3 < l2 + 1e-3
+    # prefetched batches (pinned host tensors copied beside the running step) give the same steps as direct ones
+    import torch
+    xh = torch.from_numpy(np.ascontiguousarray(x.T).reshape(-1)).pin_memory()          # memory order of x[in, N]
+    lh = torch.from_numpy(np.asarray(labels).astype(np.int32)).pin_memory()            # 1-based labels, as on the device
+    assert torch.equal(yg.labels.t.cpu(), lh)
+    gstep.prefetch(xh, lh)
+    l4 = F.trainstep(loss, m1, (xg, yg), o1)          # m1 is one good step behind m2: bring it level first
+    l5a = gstep(prefetch=(xh, lh))
+    l5b = gstep()
+    l4b = F.trainstep(loss, m1, (xg, yg), o1)
+    l4c = F.trainstep(loss, m1, (xg, yg), o1)
+    assert l4 == l3 and l5a == l4b and l5b == l4c, (l3, l4, l5a, l4b, l5b, l4c)
