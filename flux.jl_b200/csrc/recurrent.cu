@@ -843,6 +843,18 @@ bool persistent_enabled() {
   return on != 0;
 }
 
+// A cooperative launch cannot be recorded into a CUDA graph: under stream capture the time loop stays one launch per
+// step (which a graph replays at no host cost anyway).
+bool persistent_allowed(cudaStream_t stream) {
+  if (!persistent_enabled()) return false;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return cs == cudaStreamCaptureStatusNone;
+}
+
 int32_t check_dims(const char* fn, int64_t in_dim, int64_t H, int64_t T, int64_t B) {
   FB_REQUIRE(in_dim >= 1 && H >= 1 && T >= 0 && B >= 0, FB_ERR_SHAPE, "%s: bad shape in=%lld H=%lld T=%lld B=%lld", fn,
              (long long)in_dim, (long long)H, (long long)T, (long long)B);
@@ -908,7 +920,7 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
   else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
   const int64_t ldrow = T * H;       // stride between batch rows of out / cached c at a fixed t
-  if (fast && T > 1 && T * (int64_t)grid < 0x7fffffff && persistent_enabled()) {
+  if (fast && T > 1 && T * (int64_t)grid < 0x7fffffff && persistent_allowed(stream)) {
     // one cooperative launch for the whole sequence when every block can be resident at once
     int per_sm = 0;
     FB_CUDA(cudaFuncSetAttribute(lstm_fwd_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -977,7 +989,7 @@ FB_API int32_t fb_lstm_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
   const int UBp = (H + DH_U - 1) / DH_U, NPp = R / PB_R, BZp = (B + BC - 1) / BC;
   const int64_t pgrid = (int64_t)UBp * NPp * BZp;
   bool persist = T > 1 && (H % 32 == 0) && fb_aligned16(Wh) && fb_aligned16(cache) && pgrid >= 1 && pgrid <= 4096 &&
-                 2 * T * pgrid < 0x7fffffff && persistent_enabled();
+                 2 * T * pgrid < 0x7fffffff && persistent_allowed(stream);
   if (persist) {
     int per_sm = 0;
     FB_CUDA(cudaFuncSetAttribute(lstm_bwd_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PB_SMEM));
@@ -1092,7 +1104,7 @@ FB_API int32_t fb_gru_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
   if (fast) FB_CUDA(cudaFuncSetAttribute(gru_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
-  if (fast && T > 1 && T * (int64_t)grid < 0x7fffffff && persistent_enabled()) {
+  if (fast && T > 1 && T * (int64_t)grid < 0x7fffffff && persistent_allowed(stream)) {
     // one cooperative launch for the whole sequence when every block can be resident at once
     int per_sm = 0;
     FB_CUDA(cudaFuncSetAttribute(gru_fwd_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

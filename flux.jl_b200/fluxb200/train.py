@@ -365,8 +365,7 @@ class GraphedGradient:
     `f(model)` must close over device arrays that are updated in place between calls.  `graph()` replays the captured
     launch sequence and returns the loss array (device scalar) and the gradient tree, whose arrays are the same
     buffers on every call.  BatchNorm running statistics advance on every replay, as they would in eager calls.
-    Kernels that need a cooperative launch (the persistent recurrent kernels) cannot be captured: construction then
-    raises and the caller should stay with `withgradient`."""
+    (Recurrent layers run one launch per time step inside a captured step: a cooperative launch cannot be recorded.)"""
 
     def __init__(self, f, model):
         side = torch.cuda.Stream()

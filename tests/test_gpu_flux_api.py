@@ -253,6 +253,29 @@ def test_graphed_gradient_replays_withgradient(F):
         np.testing.assert_allclose(F.cpu(tree["layers"][0]["diag"]["scale"]), F.cpu(g["layers"][0]["diag"]["scale"]), rtol=1e-6, atol=1e-7)
 
 
+def test_graphed_gradient_of_a_recurrent_layer_matches_eager(F):
+    """Eager calls run the persistent (cooperative) LSTM kernels, a captured step the per-step ones: same numbers."""
+    rng = np.random.default_rng(23)
+    H, I, T, B = 32, 16, 9, 5
+    rnn = F.LSTM(O.glorot_uniform(rng, 4 * H, I), O.glorot_uniform(rng, 4 * H, H))
+    xg = F.gpu(rng.normal(size=(I, T, B)).astype(np.float32))
+    fn = lambda m: F.sum_abs2(m(xg))
+    val, (g,) = F.withgradient(fn, rnn)
+    gg = F.GraphedGradient(fn, rnn)
+    loss, tree = gg()
+    assert abs(float(F.cpu(loss)) - val) <= 1e-5 * abs(val)
+
+    def leaves(t):
+        if isinstance(t, dict):
+            for v in t.values():
+                yield from leaves(v)
+        elif t is not None:
+            yield t
+    for a, b in zip(leaves(tree), leaves(g)):
+        np.testing.assert_allclose(F.cpu(a), F.cpu(b), rtol=1e-4, atol=1e-5 * float(np.abs(F.cpu(b)).max()))
+    assert F.context().device_error() == 0
+
+
 def test_multiheadattention_head_size_64_runs_the_tensor_core_kernels(F):
     """Same checks as the small layer test at a head size the tcgen05 attention kernels take (forward, dQ, dK / dV),
     over several key / query blocks with a ragged tail."""
