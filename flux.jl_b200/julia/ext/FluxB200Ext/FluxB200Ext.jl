@@ -179,4 +179,63 @@ function DU.__reduce!(::DU.NCCLBackend, buf::B200Array{F32}, op::F, ::B200Device
     return buf
 end
 
+# Bucketed, overlapped gradient averaging for DistributedOptimizer                  src/distributed/public_api.jl:286-300
+# Gradients of a model moved to the device live in ONE flat buffer (GradientArena); every leaf's gradient is a view
+# into it, registered with the native bucket set.  The rrules above write dW / db straight into those views and call
+# `mark_ready!`; a bucket's mean all-reduce starts on the library's communication stream as soon as its last leaf is
+# ready, while the reverse sweep goes on.  `apply!` of the wrapped rule then only waits for the buckets.
+mutable struct GradientArena
+    flat::B200Array{F32,1}
+    set::PV                          # fb_bucket_set*
+    leaf_id::IdDict{Any,Int32}       # parameter array => leaf id
+    view::IdDict{Any,B200Array}      # parameter array => its gradient view
+end
+const arena = Ref{Union{Nothing,GradientArena}}(nothing)
+
+function GradientArena(params::Vector; bucket_bytes::Int = 64 << 20)
+    pad(n) = cld(n, 64) * 64                               # every slice starts on a 256-byte boundary
+    total = sum(pad(length(p)) for p in params)
+    flat = B200Arrays.zeros(F32, total)
+    ends = Int64[]; off = 0; start = 0
+    offs = Dict{Any,Int}()
+    for p in reverse(params)                               # the order the reverse sweep produces gradients in
+        offs[p] = off; off += pad(length(p))
+        if (off - start) * 4 >= bucket_bytes; push!(ends, off); start = off; end
+    end
+    (isempty(ends) || ends[end] != total) && push!(ends, total)
+    set = Ref{PV}(C_NULL)
+    check(ccall(sym(:fb_bucket_create), Int32, (PV, PV, PV, Int64, Int32, Ptr{Int64}, PV, Ptr{PV}),
+                fbctx(), comm[], ptr(flat), total, Int32(length(ends)), ends, C_NULL, set))
+    a = GradientArena(flat, set[], IdDict{Any,Int32}(), IdDict{Any,B200Array}())
+    for p in params
+        id = Ref{Int32}(-1)
+        check(ccall(sym(:fb_bucket_register), Int32, (PV, Int64, Int64, Ptr{Int32}), a.set, offs[p], length(p), id))
+        a.leaf_id[p] = id[]
+        a.view[p] = B200Arrays.view1d(flat, offs[p], size(p))
+    end
+    return a
+end
+begin_step!(a::GradientArena) = check(ccall(sym(:fb_bucket_begin_step), Int32, (PV,), a.set))
+mark_ready!(a::GradientArena, p) = check(ccall(sym(:fb_bucket_mark_ready), Int32, (PV, Int32, PV), a.set, a.leaf_id[p], fbstream()))
+wait_all!(a::GradientArena) = check(ccall(sym(:fb_bucket_wait), Int32, (PV, PV), a.set, fbstream()))
+
+function Optimisers.apply!(o::DU.DistributedOptimizer{<:DU.NCCLBackend}, state, x::B200Array{F32}, dx::B200Array{F32})
+    a = arena[]
+    if a !== nothing && haskey(a.view, x) && ptr(a.view[x]) == ptr(dx)
+        wait_all!(a)                                       # averaged in its bucket already: do not reduce twice
+    else
+        DU.allreduce!(o.backend, dx, DU.avg)
+    end
+    return Optimisers.apply!(o.opt, state, x, dx)
+end
+
+# --------------------------------------------------------------------------------------------- bf16 ---
+# Flux.bf16 on the device: parameters keep BFloat16 VALUES in Float32 storage (rounding bit-exact with _to_bf16,
+# src/functor.jl:161-166); Dense then multiplies with the single TF32 pass (exact products, Float32 accumulation).
+function Flux._to_bf16(x::B200Array{F32})
+    y = similar(x)
+    check(ccall(sym(:fb_round_bf16), Int32, (PV, PV, PV, PV, Int64), fbctx(), fbstream(), ptr(x), ptr(y), length(x)))
+    return y
+end
+
 end # module
