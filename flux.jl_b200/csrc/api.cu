@@ -53,7 +53,7 @@ FB_API int32_t fb_ctx_create(int32_t device, fb_ctx** out) {
   c->scratch_bytes = 0;
   c->retired_count = 0;
   c->dev_error = nullptr;
-  c->tmap_cache = nullptr;
+  c->gemm_ws = nullptr;
   e = cudaMalloc(&c->dev_error, 256);
   if (e != cudaSuccess) {
     delete c;
@@ -85,7 +85,7 @@ FB_API int32_t fb_ctx_destroy(fb_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   for (int i = 0; i < ctx->retired_count; ++i) cudaFree(ctx->retired[i]);
   if (ctx->dev_error) cudaFree(ctx->dev_error);
-  fb_tmap_cache_destroy(ctx);
+  fb_gemm_workspace_destroy(ctx);
   delete ctx;
   return FB_OK;
 }

@@ -23,7 +23,7 @@ struct fb_ctx {
   void* retired[FB_MAX_RETIRED];   // outgrown arena blocks, released with the context
   int retired_count;
   int32_t* dev_error;    // device error word written by kernels whose bounded waits ran out
-  void* tmap_cache;      // opaque (gemm_tc.cu): workspace of the split-tile GEMM schedule
+  void* gemm_ws;      // opaque (gemm_tc.cu): workspace of the split-tile GEMM schedule
 };
 
 // thread-local last-error message
@@ -183,7 +183,7 @@ int32_t fb_gemm_simt_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args
 int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a, int passes);
 bool fb_gemm_tc_supported(const fb_gemm_args& a);
 int32_t fb_gemm_dispatch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a, int precision);
-void fb_tmap_cache_destroy(fb_ctx* ctx);
+void fb_gemm_workspace_destroy(fb_ctx* ctx);
 // attention_tc.cu: tensor-core attention forward; FB_ERR_UNSUPPORTED when the shape is not taken
 int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const float* k, const float* v, const uint8_t* mask,
                        float* o, float* lse, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch, int nheads,

@@ -658,7 +658,7 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   // A last wave that fills less than 3/4 of the machine is cut along K and spread over all CTAs.  (Fuller waves
   // gain nothing: the kernel runs at the power limit, where idle SMs let the busy ones clock higher.)
   const int64_t rest = num_tiles % Gmax;
-  const GemmWorkspace* gw = (const GemmWorkspace*)ctx->tmap_cache;
+  const GemmWorkspace* gw = (const GemmWorkspace*)ctx->gemm_ws;
   if (rest != 0 && 4 * rest < 3 * Gmax && sch.nu > 1 && rest * sch.nu < 0x40000000 && gw != nullptr && stream_k_enabled()) {
     sch.dp_tiles = (int)(num_tiles - rest);
     sch.U = (int)(rest * sch.nu);
@@ -767,20 +767,20 @@ int32_t fb_gemm_workspace_create(fb_ctx* ctx) {
     return fb_fail(FB_ERR_ALLOC, "fb_ctx_create: GEMM workspace allocation failed");
   }
   cudaMemset(gw->tickets, 0, tickets * sizeof(int));
-  ctx->tmap_cache = gw;
+  ctx->gemm_ws = gw;
   return FB_OK;
 }
 
 void fb_gemm_workspace_reset(fb_ctx* ctx, cudaStream_t stream) {
-  GemmWorkspace* gw = (GemmWorkspace*)ctx->tmap_cache;
+  GemmWorkspace* gw = (GemmWorkspace*)ctx->gemm_ws;
   if (gw != nullptr && gw->tickets != nullptr) cudaMemsetAsync(gw->tickets, 0, (size_t)ctx->sm_count * 4 * sizeof(int), stream);
 }
 
-void fb_tmap_cache_destroy(fb_ctx* ctx) {
-  GemmWorkspace* gw = (GemmWorkspace*)ctx->tmap_cache;
+void fb_gemm_workspace_destroy(fb_ctx* ctx) {
+  GemmWorkspace* gw = (GemmWorkspace*)ctx->gemm_ws;
   if (gw == nullptr) return;
   if (gw->ws) cudaFree(gw->ws);
   if (gw->tickets) cudaFree(gw->tickets);
   delete gw;
-  ctx->tmap_cache = nullptr;
+  ctx->gemm_ws = nullptr;
 }
