@@ -352,9 +352,6 @@ constexpr int ATC2_SMEM = P2_BAR + 512 + 1024;
 enum { C_QREADY = 0, C_KFULL, C_KREADY = C_KFULL + 3, C_KFREE = C_KREADY + 3, C_VFULL = C_KFREE + 3, C_VREADY = C_VFULL + 3,
        C_VFREE = C_VREADY + 3, C_SFULL = C_VFREE + 3, C_PREADY = C_SFULL + 2, C_OFULL = C_PREADY + 2, C_COUNT = C_OFULL + 2 };
 
-// SPF: the softmax warps fetch the scores of block j + 1 from tensor memory while the stores of block j's P drain, so
-// that one of the three tensor-memory round trips of a block is off the critical path.
-template <bool SPF>
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attn_fwd_tc2_kernel(const float* __restrict__ qmat, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, float* __restrict__ o, float* __restrict__ lse, AtcDims D,
@@ -531,28 +528,17 @@ attn_fwd_tc2_kernel(const float* __restrict__ qmat, const __grid_constant__ CUte
       }
       return true;
     };
-    uint32_t s0[32], s1[32];
-    if (SPF) {
-      ok = mbar_wait(bar(C_SFULL + 0), 0u, s_abort);
-      if (ok) {
-        tc_fence_after();
-        tc_ld_32x32b_x32(t_row + 128u, s0);
-        tc_ld_32x32b_x32(t_row + 160u, s1);
-        tc_wait_ld();
-      }
-    }
     for (int j = 0; j < nkb && ok; ++j) {
       const int st = j & 1;
       const int64_t j0 = (int64_t)j * KT;
+      ok = mbar_wait(bar(C_SFULL + st), par(j), s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s0[32], s1[32];
       const uint32_t t_s = t_row + 128u + (uint32_t)(64 * st);
-      if (!SPF) {
-        ok = mbar_wait(bar(C_SFULL + st), par(j), s_abort);
-        if (!ok) break;
-        tc_fence_after();
-        tc_ld_32x32b_x32(t_s, s0);
-        tc_ld_32x32b_x32(t_s + 32u, s1);
-        tc_wait_ld();
-      }
+      tc_ld_32x32b_x32(t_s, s0);
+      tc_ld_32x32b_x32(t_s + 32u, s1);
+      tc_wait_ld();
       int64_t lim = D.Lk - j0;
       if (D.causal && gi - j0 + 1 < lim) lim = gi - j0 + 1;
       const int nvalid = lim < 0 ? 0 : (lim > KT ? KT : (int)lim);
@@ -596,20 +582,8 @@ attn_fwd_tc2_kernel(const float* __restrict__ qmat, const __grid_constant__ CUte
         }
         tc_st_32x32b_x32(t_s + 32u, s1);
         tc_st_32x32b_x32(t_s + 160u, lo);
-        if (SPF && j + 1 < nkb) {
-          // the next block's scores (their MMAs were issued before this block's P V is): the loads travel while the
-          // stores above drain; the wait for them is the one in add_pv below (or the explicit one for block 0)
-          ok = mbar_wait(bar(C_SFULL + (st ^ 1)), par(j + 1), s_abort);
-          if (ok) {
-            tc_fence_after();
-            const uint32_t t_n = t_row + 128u + (uint32_t)(64 * (st ^ 1));
-            tc_ld_32x32b_x32(t_n, s0);
-            tc_ld_32x32b_x32(t_n + 32u, s1);
-          }
-        }
         tc_wait_st();
       }
-      if (!ok) break;
       const float rs = rs0 + rs1;
       tc_fence_before();
       __syncwarp();
@@ -618,8 +592,6 @@ attn_fwd_tc2_kernel(const float* __restrict__ qmat, const __grid_constant__ CUte
       if (j > 0) {
         ok = add_pv(j - 1);
         if (!ok) break;
-      } else if (SPF) {
-        tc_wait_ld();
       }
       l = l * alpha + rs;
       m = m_new;
@@ -1239,16 +1211,6 @@ bool attn_tc_enabled() {
   return on != 0;
 }
 
-// FLUXB200_ATTN_SPF = 1: the forward kernel's softmax warps prefetch the next block's scores (see SPF).
-bool attn_score_prefetch() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("FLUXB200_ATTN_SPF");
-    on = (e != nullptr && e[0] == '1') ? 1 : 0;
-  }
-  return on != 0;
-}
-
 // FLUXB200_ATTN_PIPE = 0 selects the unpipelined kernels (one S / P V buffer, one K / V stage).
 bool attn_pipelined() {
   static int on = -1;
@@ -1315,13 +1277,8 @@ int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const f
   D.scale_log2 = D.scale * 1.4426950408889634f;
   dim3 grid((unsigned)((lq + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
   if (attn_pipelined()) {
-    if (attn_score_prefetch()) {
-      FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC2_SMEM));
-      attn_fwd_tc2_kernel<true><<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(q, tmK, tmV, o, lse, D, ctx->dev_error);
-    } else {
-      FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC2_SMEM));
-      attn_fwd_tc2_kernel<false><<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(q, tmK, tmV, o, lse, D, ctx->dev_error);
-    }
+    FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC2_SMEM));
+    attn_fwd_tc2_kernel<<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(q, tmK, tmV, o, lse, D, ctx->dev_error);
   } else if (attn_p_in_tmem()) {
     FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
     attn_fwd_tc_kernel<true><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
