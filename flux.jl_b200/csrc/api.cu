@@ -185,3 +185,33 @@ FB_API int32_t fb_device_error(fb_ctx* ctx, void* stream, int32_t* out_host) {
   }
   return FB_OK;
 }
+
+// ------------------------------------------------------------------ bounded-wait self test ---
+// A one-block kernel that waits, with an iteration limit, on an mbarrier nobody ever arrives on: the wait runs
+// out, the kernel records code 9001 in the context's device error word and returns.  It exists so that the host
+// side of the failure path (the error word is read, reported and cleared; launches that follow work again) can be
+// exercised without any kernel misbehaving.
+__global__ void fb_selftest_wait_kernel(int32_t* dev_err, uint32_t polls) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = (uint32_t)__cvta_generic_to_shared(&bar);
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t ok = 0;
+    for (uint32_t it = 0; it < polls && !ok; ++it)
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(ok) : "r"(b), "r"(0u) : "memory");
+    if (!ok) atomicExch(dev_err, 9001);
+  }
+}
+
+FB_API int32_t fb_selftest_bounded_wait(fb_ctx* ctx, void* stream, int32_t polls) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(polls >= 1 && polls <= 4096, FB_ERR_INVALID_ARG, "fb_selftest_bounded_wait: polls must be in [1, 4096]");
+  fb_selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->dev_error, (uint32_t)polls);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}

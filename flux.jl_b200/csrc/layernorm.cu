@@ -424,7 +424,7 @@ FB_API int32_t fb_layernorm_fwd(fb_ctx* ctx, void* stream_, const float* x, cons
 int32_t fb_layernorm_bwd_impl(cudaStream_t stream, int sm_count, float* part, int64_t groups, const float* x,
                               const float* gamma, const float* beta, const float* mean, const float* rstd,
                               const float* dy, float* dx, float* dgamma, float* dbeta, int64_t d, int64_t n,
-                              int32_t act, int32_t* dev_err) {
+                              int32_t act, int32_t* dev_err, bool allow_ring = true) {
   (void)sm_count;
   const bool want_param = (dgamma != nullptr);
   float* part_dg = want_param ? part : nullptr;
@@ -444,7 +444,7 @@ int32_t fb_layernorm_bwd_impl(cudaStream_t stream, int sm_count, float* part, in
     const size_t stage_bytes = (size_t)2 * d * sizeof(float);
     int nst = (int)((size_t)100 * 1024 / stage_bytes);
     if (nst > LN_PIPE_MAX) nst = LN_PIPE_MAX;
-    if (nst >= 2 && v >= 2) {
+    if (nst >= 2 && v >= 2 && allow_ring) {
       const size_t smem = (size_t)nst * stage_bytes;
       switch (v) {
         case 2:
@@ -582,6 +582,8 @@ FB_API int32_t fb_layernorm_bwd_noalloc(void* stream_, const float* x, const flo
   }
   // Every block overwrites all d columns of its own partial rows before the reduction reads exactly
   // groups * d of them, so nothing left behind by an earlier call is ever read.
+  // This entry point has no context and therefore no device error word to report a timed-out wait through, so it
+  // keeps to the kernels that hold their rows in registers and wait on nothing (no shared-memory ring).
   return fb_layernorm_bwd_impl(stream, sd.sm_count, sd.scratch, groups, x, gamma, beta, mean, rstd, dy, dx, dgamma, dbeta,
-                               d, n, act, nullptr);
+                               d, n, act, nullptr, /*allow_ring=*/false);
 }

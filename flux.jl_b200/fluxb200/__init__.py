@@ -11,6 +11,7 @@ from .layers import (ArgumentError, AttnScores, BatchNorm, CausalMask, Chain, De
                      make_causal_mask, testmode, trainables, trainmode, bf16, f32)
 from .train import (Adam, Descent, DomainError, GraphedGradient, GraphedTrainStep, OneHotLabels, gradient, logitcrossentropy, onehotbatch, setup, scale, sum_abs2, sum_all,
                     train, trainstep, update, withgradient)
+from .init import create_bias, glorot_uniform, nfan, ones32, rand32, randn32, seed, zeros32
 from . import distributed as DistributedUtils
 
 __all__ = [n for n in dir() if not n.startswith("_")]

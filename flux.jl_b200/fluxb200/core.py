@@ -95,7 +95,7 @@ class B200Array:
             size[i] = total // max(rest, 1)
         out = B200Array(self.t, size)
         if Tape.needs(self):
-            Tape.record(out, [self], lambda g, src=self: [(src, B200Array(g.t, src.size))])
+            Tape.record(out, [self], lambda gs, src=self: [(src, B200Array(gs[0].t, src.size))])
         return out
 
     def __repr__(self):

@@ -144,6 +144,69 @@ def reduce(backend, sendrecvbuf: B200Array, op_or_recv="+", op=None, root: int =
     return dst
 
 
+class WorkerLost(lib.FluxB200Error):
+    """A worker did not report for a step in time, or reported a different gradient-bucket layout."""
+
+    def __init__(self, msg):
+        super().__init__(-6, msg)
+
+
+class Heartbeat:
+    """Host-side failure detection between steps.  Before a step is launched every worker adds itself to a counter
+    of that step in the rendezvous store and waits (with a limit) until all have; a worker that died, hung or left
+    is noticed here, on the host, instead of inside the next collective, which would wait for it for ever (as it does
+    in the reference: NCCL.Allreduce! has no timeout, ext/FluxMPINCCLExt/FluxMPINCCLExt.jl:61-66).
+
+    `store` is any object with torch.distributed.Store's `add(key, n) -> int` (TCPStore, FileStore, HashStore)."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 30.0, poll_s: float = 0.005, prefix: str = "fluxb200/hb"):
+        self.store, self.rank, self.world = store, int(rank), int(world)
+        self.timeout_s, self.poll_s, self.prefix = float(timeout_s), float(poll_s), prefix
+        self.step = 0
+
+    def beat(self):
+        """Call once per step on every worker, before the step's first launch.  Raises WorkerLost when fewer than
+        `world` workers have reported within the limit."""
+        import time
+        key = f"{self.prefix}/{self.step}"
+        seen = self.store.add(key, 1)
+        t0 = time.monotonic()
+        while seen < self.world:
+            if time.monotonic() - t0 > self.timeout_s:
+                raise WorkerLost(f"step {self.step}: only {seen} of {self.world} workers reported within {self.timeout_s:g} s "
+                                 f"(seen from rank {self.rank}); not launching the step")
+            time.sleep(self.poll_s)
+            seen = self.store.add(key, 0)
+        self.step += 1
+
+
+def verify_layout(store, rank: int, world: int, layout, timeout_s: float = 30.0, prefix: str = "fluxb200/layout"):
+    """Every worker publishes a digest of its gradient-bucket layout (bucket boundaries and leaf sizes) and compares it
+    with the others' before the first collective: a worker built with a different model or bucket size would otherwise
+    exchange buffers of different lengths, which NCCL answers with a hang or silent corruption."""
+    import hashlib
+    import time
+    digest = hashlib.sha256(repr(layout).encode()).hexdigest()
+    store.set(f"{prefix}/{rank}", digest)
+    t0 = time.monotonic()
+    for r in range(world):
+        key = f"{prefix}/{r}"
+        while True:
+            try:
+                if hasattr(store, "check") and not store.check([key]):
+                    raise KeyError(key)
+                other = store.get(key)
+                break
+            except Exception:
+                if time.monotonic() - t0 > timeout_s:
+                    raise WorkerLost(f"worker {r} did not publish its gradient-bucket layout within {timeout_s:g} s")
+                time.sleep(0.005)
+        other = other.decode() if isinstance(other, (bytes, bytearray)) else str(other)
+        if other != digest:
+            raise WorkerLost(f"worker {r} has a different gradient-bucket layout than worker {rank}: the workers were not "
+                             "built with the same model / bucket size")
+
+
 class FluxDistributedModel:
     def __init__(self, model):
         self.model = model
@@ -224,6 +287,9 @@ class GradBuckets:
         self.adam = None
         self.armed = False
         self.loss = None
+        self.guard = None            # device scalar the update kernels test for finiteness (see set_loss)
+        self._guard_buf = None
+        self.guard_event = None
         # optional timeline: device time marks (fb_timestamp) placed on both streams; see enable_timeline
         self.marks = None
         self.mark_names = []
@@ -247,6 +313,10 @@ class GradBuckets:
         self.events = [torch.cuda.Event() for _ in self.buckets]
         self.launched = [False] * len(self.buckets)
         self.begin_step()
+
+    def layout(self):
+        """What has to agree on every worker: bucket boundaries and the size of every gradient slice, in order."""
+        return (tuple((b[0], b[1]) for b in self.buckets), tuple(p.numel() for p in self.params), self.backend.size)
 
     def enable_timeline(self, slots: int = 256):
         """Time marks on the compute and communication streams (they are captured with the step when it is a
@@ -273,17 +343,37 @@ class GradBuckets:
         for b in self.buckets:
             b[2] = set(b[3])
         self.launched = [False] * len(self.buckets)
+        self.handed = set()     # parameters whose slice a pullback of this step already writes
+        self.uses = {}          # parameter id -> gradient contributions still to come (set by expect_uses)
         if self.marks is not None:
             self.mark_names = []
             self._mark("step start")
 
     def buffer_for(self, param):
-        return self.views.get(id(param)) if param is not None else None
+        """The slice of the flat gradient buffer a pullback may OVERWRITE with this parameter's gradient: handed out
+        once per step.  A parameter applied twice in one model (tied weights, a layer called twice) gets None for its
+        later contributions, which then go to a temporary that `accumulate` adds to the slice."""
+        if param is None:
+            return None
+        k = id(param)
+        if k not in self.views or k in self.handed:
+            return None
+        self.handed.add(k)
+        return self.views[k]
+
+    def expect_uses(self, counts: dict):
+        """counts[id(param)] = number of recorded layer calls that will contribute a gradient to the parameter in this
+        reverse sweep; `ready` starts a bucket only after the last contribution of each of its parameters."""
+        self.uses = dict(counts)
 
     def ready(self, param):
         k = id(param)
         bi = self.bucket_of.get(k)
         if bi is None:
+            return
+        left = self.uses.get(k, 1) - 1
+        self.uses[k] = left
+        if left > 0:
             return
         b = self.buckets[bi]
         b[2].discard(k)
@@ -317,8 +407,23 @@ class GradBuckets:
         return True
 
     def set_loss(self, loss):
-        """The step's loss (device scalar): the captured update kernels skip themselves when it is not finite."""
+        """The step's loss (device scalar): the captured update kernels skip themselves when it is not finite.  With
+        several workers the guard is the SUM of the workers' losses (NaN and Inf survive a sum), so that every rank
+        takes the same decision: either all update, or none does (src/train.jl:377 decides per process, which would
+        let replicas diverge)."""
         self.loss = loss
+        self.guard = loss
+        be = self.backend
+        if be.size > 1 and be.comm is not None:
+            if self._guard_buf is None:
+                self._guard_buf = B200Array(torch.zeros(1, dtype=torch.float32, device=loss.t.device), ())
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            be.stream.wait_event(ev)
+            lib.call("fb_allreduce", be.comm, C.c_void_p(be.stream.cuda_stream), loss.ptr, self._guard_buf.ptr, 1, lib.OP["+"])
+            self.guard = self._guard_buf
+            self.guard_event = torch.cuda.Event()
+            self.guard_event.record(be.stream)
         self._mark("forward end")
 
     def _launch(self, bi):
@@ -345,7 +450,7 @@ class GradBuckets:
             one = C.c_void_p * 1
             lib.call("fb_adam_step_dev", context().handle, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
                      one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
-                     rule.epsilon, C.c_void_p(bt.data_ptr()), self.loss.ptr, 1.0)
+                     rule.epsilon, C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
             self._mark(f"bucket {bi} adam end", be.stream)
             lib.call("fb_allgather", be.comm, cs, C.c_void_p(pp), C.c_void_p(self.pflat.data_ptr() + 4 * start), blk)
         else:
@@ -362,6 +467,8 @@ class GradBuckets:
         if self.backend.size > 1:
             for ev in self.events:
                 torch.cuda.current_stream().wait_event(ev)
+            if self.guard_event is not None:
+                torch.cuda.current_stream().wait_event(self.guard_event)
         self._mark("step end")
 
 
@@ -371,6 +478,26 @@ class DistributedOptimizer(DistributedOptimizerBase):
 
     def __init__(self, backend, opt, buckets: GradBuckets | None = None):
         self.backend, self.opt, self.buckets = backend, opt, buckets
+
+    def all_finite(self, loss_value: float) -> bool:
+        """True when the loss is finite on EVERY worker.  A worker that skipped its update alone would leave the
+        others waiting in the gradient collectives and let the replicas diverge, so the decision is taken together
+        (one scalar all-reduce)."""
+        ok = bool(np.isfinite(loss_value))
+        if self.backend.size == 1 or self.backend.comm is None:
+            return ok
+        flag = B200Array(torch.tensor([0.0 if ok else 1.0], dtype=torch.float32, device="cuda"), (1,))
+        allreduce(self.backend, flag, "+")
+        return float(flag.t.item()) == 0.0
+
+    def check_async_error(self):
+        """Raises when NCCL has reported an asynchronous error on the communicator (polled between steps)."""
+        if self.backend.comm is None:
+            return
+        code = C.c_int32(0)
+        lib.call("fb_comm_async_error", self.backend.comm, C.byref(code))
+        if code.value != 0:
+            raise WorkerLost(f"NCCL reported asynchronous error {code.value} on rank {self.backend.rank}")
 
     def average_gradients(self, opt_state, gmap: dict):
         if self.buckets is not None:

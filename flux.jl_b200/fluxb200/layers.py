@@ -13,6 +13,7 @@ import torch
 
 from . import lib
 from .core import B200Array, Tape, context, empty, gpu, zeros
+from .init import glorot_uniform
 
 
 class DimensionMismatch(ValueError):
@@ -137,12 +138,20 @@ def f32(m):
 
 # ------------------------------------------------------------------------------------ Dense ---
 class Dense(Layer):
-    """Dense(W, bias, sigma): y = sigma.(W*x .+ b) (basic.jl:179-205). `bias=False` means no bias."""
+    """Dense(W, bias, sigma): y = sigma.(W*x .+ b) (basic.jl:179-205). `bias=False` means no bias.
+
+    `Dense((in, out), sigma, bias=True, init=glorot_uniform)` is Flux's `Dense(in => out, σ; init, bias)`
+    (basic.jl:189-192): the weight is `init(out, in)`."""
 
     _fields = ("weight", "bias", "σ")
     _trainable = ("weight", "bias")
 
-    def __init__(self, weight, bias=True, sigma="identity", precision="default"):
+    def __init__(self, weight, bias=True, sigma="identity", precision="default", init=glorot_uniform):
+        if isinstance(weight, (tuple, list)) and len(weight) == 2 and all(isinstance(v, (int, np.integer)) for v in weight):
+            if isinstance(bias, str):      # Dense((in, out), "relu")
+                bias, sigma = True, bias
+            in_dim, out_dim = int(weight[0]), int(weight[1])
+            weight = init(out_dim, in_dim)
         self.weight = gpu(weight) if isinstance(weight, np.ndarray) else weight
         if self.weight.ndim != 2:
             raise TypeError("MethodError: Dense weight must be a matrix")
@@ -364,7 +373,10 @@ class LSTMCell(Layer):
     _fields = ("Wi", "Wh", "bias")
     NG = 4
 
-    def __init__(self, Wi, Wh, bias=True):
+    def __init__(self, Wi, Wh=None, bias=True, init_kernel=glorot_uniform, init_recurrent_kernel=glorot_uniform):
+        if isinstance(Wi, (tuple, list)) and len(Wi) == 2 and all(isinstance(v, (int, np.integer)) for v in Wi):
+            in_dim, out = int(Wi[0]), int(Wi[1])     # LSTMCell(in => out) (recurrent.jl:395-407)
+            Wi, Wh = init_kernel(out * 4, in_dim), init_recurrent_kernel(out * 4, out)
         self.Wi, self.Wh = gpu(Wi), gpu(Wh)
         rows = self.Wi.size[0]
         if bias is True:
@@ -390,7 +402,10 @@ class GRUCell(Layer):
     _fields = ("Wi", "Wh", "b")
     NG = 3
 
-    def __init__(self, Wi, Wh, b=True):
+    def __init__(self, Wi, Wh=None, b=True, init_kernel=glorot_uniform, init_recurrent_kernel=glorot_uniform):
+        if isinstance(Wi, (tuple, list)) and len(Wi) == 2 and all(isinstance(v, (int, np.integer)) for v in Wi):
+            in_dim, out = int(Wi[0]), int(Wi[1])     # GRUCell(in => out) (recurrent.jl:596-607)
+            Wi, Wh = init_kernel(out * 3, in_dim), init_recurrent_kernel(out * 3, out)
         self.Wi, self.Wh = gpu(Wi), gpu(Wh)
         rows = self.Wi.size[0]
         if b is True:
@@ -498,14 +513,14 @@ class Recurrence(Layer):
         return y
 
 
-def LSTM(Wi, Wh, bias=True, return_state=False):
-    """LSTM(in => out) == Recurrence(LSTMCell(in => out)) (recurrent.jl:491-524)."""
-    return Recurrence(LSTMCell(Wi, Wh, bias), return_state=return_state)
+def LSTM(Wi, Wh=None, bias=True, return_state=False, **init):
+    """LSTM(in => out) == Recurrence(LSTMCell(in => out)) (recurrent.jl:491-524); `LSTM((in, out))` or explicit arrays."""
+    return Recurrence(LSTMCell(Wi, Wh, bias, **init), return_state=return_state)
 
 
-def GRU(Wi, Wh, b=True, return_state=False):
-    """GRU(in => out) == Recurrence(GRUCell(in => out)) (recurrent.jl:685-718)."""
-    return Recurrence(GRUCell(Wi, Wh, b), return_state=return_state)
+def GRU(Wi, Wh=None, b=True, return_state=False, **init):
+    """GRU(in => out) == Recurrence(GRUCell(in => out)) (recurrent.jl:685-718); `GRU((in, out))` or explicit arrays."""
+    return Recurrence(GRUCell(Wi, Wh, b, **init), return_state=return_state)
 
 
 # ---------------------------------------------------------------------------------- attention ---
@@ -575,10 +590,27 @@ class MultiHeadAttention(Layer):
     _fields = ("nheads", "q_proj", "k_proj", "v_proj", "attn_drop", "out_proj")
     _trainable = ("q_proj", "k_proj", "v_proj", "out_proj")
 
-    def __init__(self, Wq, Wk, Wv, Wo, nheads=8, biases=None, precision="default"):
+    def __init__(self, Wq, Wk=None, Wv=None, Wo=None, nheads=8, biases=None, precision="default", bias=False,
+                 init=glorot_uniform):
         bq = bk = bv = bo = False
         if biases is not None:
             bq, bk, bv, bo = biases
+        if Wk is None:
+            # MultiHeadAttention(dims; nheads, bias, init) (attention.jl:79-94): dims is an Int or
+            # (in, (qkv, out)) with in = Int | (q_in, k_in, v_in) and qkv = Int | (qk, v)  (normalize_mha_dims :97-112)
+            d = Wq
+            if isinstance(d, (int, np.integer)):
+                q_in = k_in = v_in = qk = vd = out = int(d)
+            else:
+                inp, (qkv, out) = d
+                q_in, k_in, v_in = (inp, inp, inp) if isinstance(inp, (int, np.integer)) else inp
+                qk, vd = (qkv, qkv) if isinstance(qkv, (int, np.integer)) else qkv
+            if qk % nheads:
+                raise ArgumentError(f"qk_dim = {qk} should be divisible by nheads = {nheads}")
+            if vd % nheads:
+                raise ArgumentError(f"v_dim = {vd} should be divisible by nheads = {nheads}")
+            Wq, Wk, Wv, Wo = init(qk, q_in), init(qk, k_in), init(vd, v_in), init(out, vd)
+            bq = bk = bv = bo = bool(bias)
         self.nheads = int(nheads)
         self.q_proj = Dense(Wq, bq, precision=precision)
         self.k_proj = Dense(Wk, bk, precision=precision)

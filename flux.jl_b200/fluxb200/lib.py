@@ -54,6 +54,7 @@ PROTOTYPES = {
     "fb_memset": (_i32, [_p, _p, _p, _i32, _i64]),
     "fb_sync": (_i32, [_p, _p]),
     "fb_device_error": (_i32, [_p, _p, C.POINTER(_i32)]),
+    "fb_selftest_bounded_wait": (_i32, [_p, _p, _i32]),
     "fb_gemm_f32": (_i32, [_p, _p, _i32, _i32, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i64, _i32, _i32]),
     "fb_dense_fwd": (_i32, [_p, _p, _i32, _i32, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_dense_bwd": (_i32, [_p, _p, _i32, _i32, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64]),

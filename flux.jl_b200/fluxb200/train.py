@@ -157,6 +157,15 @@ def _withgradient_device(f, model, grad_sink=None):
             raise TypeError("withgradient: the function must return a scalar B200Array")
         if grad_sink is not None and hasattr(grad_sink, "set_loss"):
             grad_sink.set_loss(loss)
+        if grad_sink is not None and hasattr(grad_sink, "expect_uses"):
+            # a parameter used by several recorded calls receives several contributions (Zygote's `accum`)
+            pid = {id(p) for p in params}
+            counts: dict = {}
+            for _, inputs, _ in Tape.entries:
+                for a in inputs:
+                    if a is not None and id(a) in pid:
+                        counts[id(a)] = counts.get(id(a), 0) + 1
+            grad_sink.expect_uses(counts)
         grads: dict = {}
         keep: dict = {}
         grads[id(loss)] = _One(B200Array(torch.ones(1, device=loss.t.device), ()))
@@ -264,6 +273,10 @@ def setup(rule, model) -> OptState:
 class DistributedOptimizerBase:
     """Marker base so `setup` can unwrap DistributedUtils.DistributedOptimizer without a circular import."""
     opt = None
+    buckets = None
+
+    def all_finite(self, loss_value: float) -> bool:
+        return math.isfinite(loss_value)
 
 
 def _flat_grads(model, tree, out: dict):
@@ -322,11 +335,29 @@ def trainstep(loss, model, batch, opt_state):
     pre-update loss; a non-finite loss skips the update."""
     if not isinstance(batch, tuple):
         batch = (batch,)
-    l, gs = withgradient(lambda m: loss(m, *batch), model)
+    outer = getattr(opt_state, "outer", None)
+    sink = getattr(outer, "buckets", None)
+    if hasattr(outer, "check_async_error"):
+        outer.check_async_error()
+    if sink is not None:
+        sink.begin_step()
+    l, gs = withgradient(lambda m: loss(m, *batch), model, grad_sink=sink)
     lv = l[0] if isinstance(l, tuple) else l
-    if math.isfinite(lv):
+    finite = outer.all_finite(lv) if isinstance(outer, DistributedOptimizerBase) else math.isfinite(lv)
+    if finite:
         update(opt_state, model, gs[0])
+    elif sink is not None:
+        sink.finish()   # the collectives already started must be matched on every worker
+    _raise_on_device_error()
     return l
+
+
+def _raise_on_device_error():
+    """A kernel whose bounded wait ran out records a code in the context's device error word and leaves its work
+    undone; later persistent launches return early while the word is set.  Reading the word clears it."""
+    code = context().device_error()
+    if code != 0:
+        raise lib.FluxB200Error(-6, f"a kernel gave up waiting (device error code {code}); the results of this step are invalid")
 
 
 def train(loss, model, data, opt_state):
@@ -396,6 +427,8 @@ class GraphedTrainStep:
     step's static input buffers on the current stream).
     """
 
+    error_poll_every = 16   # the device error word is read back every this many steps (one 4-byte copy)
+
     def __init__(self, loss, model, opt_state, example_batch, grad_sink=None, shard_optimizer=False):
         from .layers import BatchNorm, _walk
         if not isinstance(example_batch, tuple):
@@ -463,12 +496,16 @@ class GraphedTrainStep:
                                 arr_t(*[opt_state.leaves[id(p)].state[0].t.data_ptr() for p in ps]),
                                 arr_t(*[opt_state.leaves[id(p)].state[1].t.data_ptr() for p in ps]),
                                 (C.c_int64 * k)(*[p.numel() for p in ps]))
+            # with several workers the guard is the sum of all workers' losses: every rank takes the same decision
+            guard = getattr(grad_sink, "guard", None) or loss_arr
+            if not self.sharded:
                 lib.call("fb_adam_step_dev", c.handle, c.stream, k, *self._tables, rule.eta, rule.beta[0], rule.beta[1],
-                         rule.epsilon, C.c_void_p(self.bt.data_ptr()), loss_arr.ptr, 1.0)
+                         rule.epsilon, C.c_void_p(self.bt.data_ptr()), guard.ptr, 1.0)
             lib.call("fb_adam_advance", c.handle, c.stream, C.c_void_p(self.bt.data_ptr()), rule.beta[0], rule.beta[1],
-                     loss_arr.ptr)
-            self._keep = (loss_arr, tree, gmap)
+                     guard.ptr)
+            self._keep = (loss_arr, tree, gmap, guard)
         self.loss_arr = loss_arr
+        self.guard_arr = guard
         self._updated = ps
 
     def prefetch(self, *batch):
@@ -508,7 +545,11 @@ class GraphedTrainStep:
         if prefetch is not None:
             self.prefetch(*prefetch)
         lv = float(self.loss_arr.t.item())
-        if math.isfinite(lv):
+        gv = lv if self.guard_arr is self.loss_arr else float(self.guard_arr.t.item())
+        self._calls = getattr(self, "_calls", 0) + 1
+        if self._calls % self.error_poll_every == 0:
+            _raise_on_device_error()
+        if math.isfinite(gv):
             rule = self.opt_state.rule
             f32 = np.float32
             for p in self._updated:

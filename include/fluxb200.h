@@ -99,6 +99,12 @@ int32_t fb_sync(fb_ctx* ctx, void* stream);
  * tensor-core kernels return without computing.  Reading it synchronises the stream and clears it. */
 int32_t fb_device_error(fb_ctx* ctx, void* stream, int32_t* out_host);
 
+/* Launches a one-block kernel whose only act is a bounded wait (at most `polls` <= 4096 polls) on a barrier
+ * that nothing signals: the wait runs out, code 9001 lands in the device error word, the kernel returns.  It lets
+ * a caller exercise its handling of that word (report, clear, carry on) without any real kernel misbehaving.
+ * Test aid; no counterpart in the reference. */
+int32_t fb_selftest_bounded_wait(fb_ctx* ctx, void* stream, int32_t polls);
+
 /* ------------------------------------------------------------------------------- matmul -- */
 
 /* C = op(A) * op(B) (+ C when accumulate != 0), column-major BLAS convention, Float32.
@@ -152,7 +158,8 @@ int32_t fb_layernorm_bwd(fb_ctx* ctx, void* stream, const float* x, const float*
  * (FB_ERR_UNSUPPORTED otherwise); the call allocates and frees nothing; all calls share the array, so two calls
  * that overlap on the GPU (different streams) race - serialise them.  The first call on each device also resolves
  * the array's device address (cudaGetSymbolAddress, with that device current); make that first call before any
- * stream capture begins.  Uses the current device. */
+ * stream capture begins.  Uses the current device.  Having no context, the call has no device error word either:
+ * it only launches kernels that wait on nothing (rows held in registers), so there is no timeout to report. */
 int32_t fb_layernorm_bwd_noalloc(void* stream, const float* x, const float* gamma, const float* beta,
                                  const float* mean, const float* rstd, const float* dy, float* dx,
                                  float* dgamma, float* dbeta, int64_t d, int64_t n, int32_t act);

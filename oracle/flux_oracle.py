@@ -427,6 +427,16 @@ def make_causal_mask(length):
     return np.triu(np.ones((length, length), dtype=bool))
 
 
+def _contract_c(a, b):
+    """out[j, i, h, n] = sum_c a[h, c, j, n] * b[h, c, i, n] (one matrix product per head and batch entry)."""
+    return np.matmul(a.transpose(3, 0, 2, 1), b.transpose(3, 0, 1, 2)).transpose(2, 3, 1, 0)
+
+
+def _apply_ji(a, w):
+    """out[h, c, i, n] = sum_j a[h, c, j, n] * w[j, i, h, n] (one matrix product per head and batch entry)."""
+    return np.matmul(a.transpose(3, 0, 1, 2), w.transpose(3, 2, 0, 1)).transpose(1, 2, 3, 0)
+
+
 def dot_product_attention(q, k, v, bias=None, nheads=1, mask=None, return_cache=False):
     """q (E, Lq, B), k (E, Lk, B), v (Ev, Lk, B) -> x (Ev, Lq, B), alpha (Lk, Lq, h, B).
 
@@ -443,7 +453,7 @@ def dot_product_attention(q, k, v, bias=None, nheads=1, mask=None, return_cache=
     vh = v.reshape(nheads, dv, Lk, B)
     scale = q.dtype.type(1.0 / math.sqrt(d))
     # logits[j, i, h, b] = sum_c k[h,c,j,b] q[h,c,i,b] * scale
-    logits = np.einsum("hcjb,hcib->jihb", kh, qh) * scale
+    logits = _contract_c(kh, qh) * scale
     if bias is not None:
         logits = logits + np.broadcast_to(bias.reshape(bias.shape + (1,) * (4 - bias.ndim)), logits.shape)
     if mask is not None:
@@ -452,7 +462,7 @@ def dot_product_attention(q, k, v, bias=None, nheads=1, mask=None, return_cache=
     mx = logits.max(axis=0, keepdims=True)
     e = np.exp(logits - mx)
     alpha = e / e.sum(axis=0, keepdims=True)
-    xh = np.einsum("hcjb,jihb->hcib", vh, alpha)
+    xh = _apply_ji(vh, alpha)
     x = xh.reshape(Ev, Lq, B)
     if return_cache:
         return x, alpha, (qh, kh, vh, scale)
@@ -468,13 +478,13 @@ def dot_product_attention_bwd(q, k, v, dx, bias=None, nheads=1, mask=None, dalph
     d = E // nheads
     dv = Ev // nheads
     dxh = dx.reshape(nheads, dv, Lq, B)
-    dvh = np.einsum("hcib,jihb->hcjb", dxh, alpha)
-    da = np.einsum("hcjb,hcib->jihb", vh, dxh)
+    dvh = _apply_ji(dxh, alpha.transpose(1, 0, 2, 3))
+    da = _contract_c(vh, dxh)
     if dalpha is not None:
         da = da + dalpha
     ds = alpha * (da - (alpha * da).sum(axis=0, keepdims=True))
-    dqh = np.einsum("hcjb,jihb->hcib", kh, ds) * scale
-    dkh = np.einsum("hcib,jihb->hcjb", qh, ds) * scale
+    dqh = _apply_ji(kh, ds) * scale
+    dkh = _apply_ji(qh, ds.transpose(1, 0, 2, 3)) * scale
     return dqh.reshape(E, Lq, B), dkh.reshape(E, Lk, B), dvh.reshape(Ev, Lk, B)
 
 

@@ -116,3 +116,65 @@ def test_shard_sizes_with_ragged_split():
         assert (np.concatenate(shards) == np.arange(n)).all()
     with pytest.raises(IndexError):
         shard_indices(4, 8, 7)
+
+
+# ------------------------------------------------ failure detection on the host (no GPU involved) ---
+def _heartbeat_worker(rank, world, port, out):
+    """Rank 1 leaves after two steps (between steps, nothing in flight); rank 0 must learn of it on the host, within
+    the heartbeat's limit, before it would launch step 3."""
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fluxb200.distributed import Heartbeat, WorkerLost
+        store = dist.distributed_c10d._get_default_store()
+        hb = Heartbeat(store, rank, world, timeout_s=1.5)
+        t = torch.ones(4)
+        for step in range(2):
+            hb.beat()
+            dist.all_reduce(t)
+        if rank == 1:
+            out.put((rank, "left"))
+            return
+        t0 = time.monotonic()
+        try:
+            hb.beat()
+            out.put((rank, "no error"))
+        except WorkerLost as e:
+            dt = time.monotonic() - t0
+            out.put((rank, "lost" if (1.4 < dt < 10 and "1 of 2 workers" in str(e) and e.code == -6) else f"bad: {dt} {e}"))
+    except Exception as e:  # noqa: BLE001
+        out.put((rank, repr(e)))
+    finally:
+        if rank == 1:
+            time.sleep(3.0)   # keep the store's peer alive while rank 0 polls it
+        dist.destroy_process_group()
+
+
+def test_a_worker_that_never_arrives_is_reported_on_the_host_in_time():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_heartbeat_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(0, "lost"), (1, "left")], res
+
+
+def test_mismatched_bucket_layout_is_reported_before_any_collective():
+    from fluxb200.distributed import WorkerLost, verify_layout
+    store = dist.HashStore()
+    layout_a = (((0, 1024), (1024, 4096)), (1024, 3072), 2)
+    layout_b = (((0, 2048), (2048, 4096)), (2048, 2048), 2)
+    store.set("fluxb200/layout/1", __import__("hashlib").sha256(repr(layout_a).encode()).hexdigest())
+    verify_layout(store, 0, 2, layout_a, timeout_s=1.0)                       # same layout: passes
+    store2 = dist.HashStore()
+    store2.set("fluxb200/layout/1", __import__("hashlib").sha256(repr(layout_b).encode()).hexdigest())
+    with pytest.raises(WorkerLost, match="different gradient-bucket layout"):
+        verify_layout(store2, 0, 2, layout_a, timeout_s=1.0)
+    store3 = dist.HashStore()                                                 # worker 1 never publishes
+    with pytest.raises(WorkerLost, match="did not publish"):
+        verify_layout(store3, 0, 2, layout_a, timeout_s=0.3)

@@ -411,3 +411,52 @@ def test_graphed_trainstep_equals_eager_and_skips_on_nan(F):
     l4b = F.trainstep(loss, m1, (xg, yg), o1)
     l4c = F.trainstep(loss, m1, (xg, yg), o1)
     assert l4 == l3 and l5a == l4b and l5b == l4c, (l3, l4, l5a, l4b, l5b, l4c)
+
+
+def test_pair_constructors_use_glorot_uniform(F):
+    """Dense(in => out, σ), LSTMCell(in => out), GRUCell(in => out), MultiHeadAttention(dims; nheads)
+    (basic.jl:189-192, recurrent.jl:395-407, 596-607, attention.jl:79-94): shapes, zero biases, init scale."""
+    F.seed(1)
+    d = F.Dense((10, 6), "relu")
+    assert d.weight.size == (6, 10) and d.bias.size == (6,) and d.σ == "relu" and (F.cpu(d.bias) == 0).all()
+    assert np.abs(F.cpu(d.weight)).max() <= 0.5 * np.sqrt(24 / 16) + 1e-6
+    assert F.Dense((10, 6), bias=False).bias is False
+    ones = F.Dense((10, 1), init=lambda o, i: np.ones((o, i), np.float32))       # test/layers/basic.jl:85
+    assert F.cpu(ones(F.gpu(np.ones((10, 1), np.float32)))).item() == 10
+    c = F.LSTMCell((3, 5))
+    assert c.Wi.size == (20, 3) and c.Wh.size == (20, 5) and c.bias.size == (20,)
+    g = F.GRUCell((3, 5))
+    assert g.Wi.size == (15, 3) and g.Wh.size == (15, 5) and g.b.size == (15,)
+    assert F.LSTM((3, 5))(F.gpu(np.zeros((3, 4, 2), np.float32))).size == (5, 4, 2)
+    m = F.MultiHeadAttention(16, nheads=2)
+    assert m.q_proj.weight.size == (16, 16) and m.q_proj.bias is False
+    m2 = F.MultiHeadAttention(((4, 6, 8), ((12, 10), 14)), nheads=2, bias=True)     # (q_in,k_in,v_in) => (qk, v) => out
+    assert (m2.q_proj.weight.size, m2.k_proj.weight.size, m2.v_proj.weight.size, m2.out_proj.weight.size) == \
+        ((12, 4), (12, 6), (10, 8), (14, 10))
+    with pytest.raises(F.ArgumentError):
+        F.MultiHeadAttention(10, nheads=3)
+
+
+def test_layer_applied_twice_accumulates_into_the_gradient_bucket(F):
+    """A Dense used twice in one model (tied weights): both contributions must reach the flat gradient buffer of a
+    GradBuckets sink, and the bucket may only start after the second one."""
+    DU = F.DistributedUtils
+    rng = np.random.default_rng(5)
+    W, b = O.glorot_uniform(rng, 32, 32), (rng.normal(size=32) * 0.1).astype(np.float32)
+    x = rng.normal(size=(32, 9)).astype(np.float32)
+    layer = F.Dense(W, b, "tanh")
+    model = F.Chain(layer, layer)
+    backend = DU.initialize(DU.NCCLBackend)
+    sink = DU.GradBuckets(backend, F.trainables(layer), bucket_mb=0.001)
+    xg = F.gpu(x)
+    val, (g,) = F.withgradient(lambda m: F.sum_abs2(m(xg)), model, grad_sink=sink)
+    W64, b64, x64 = W.astype(np.float64), b.astype(np.float64), x.astype(np.float64)
+    h = O.dense_fwd(W64, b64, x64, "tanh")
+    y = O.dense_fwd(W64, b64, h, "tanh")
+    dW2, db2, dh = O.dense_bwd(W64, b64, h, 2 * y, "tanh")
+    dW1, db1, _ = O.dense_bwd(W64, b64, x64, dh, "tanh")
+    close(val, (y * y).sum())
+    close(F.cpu(sink.views[id(layer.weight)]), dW1 + dW2, name="dW in the bucket", rtol=2e-4, atol_scale=2e-4)
+    close(F.cpu(sink.views[id(layer.bias)]), db1 + db2, name="db in the bucket", rtol=2e-4, atol_scale=2e-4)
+    close(F.cpu(g["layers"][0]["weight"]), dW1 + dW2, name="dW in the tree", rtol=2e-4, atol_scale=2e-4)
+    assert all(sink.launched)

@@ -613,3 +613,41 @@ def test_against_committed_golden_vectors(fb):
         bt = (bt[0] * np.float32(0.9), bt[1] * np.float32(0.999))
     np.testing.assert_allclose(host(w, (11,)), G["adam_w3"], rtol=1e-5, atol=1e-7)
     np.testing.assert_allclose(host(v, (11,)), G["adam_v3"], rtol=1e-5, atol=1e-10)
+
+
+# ------------------------------------------------------------- failure path of bounded waits ---
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_works():
+    """A wait that nothing satisfies (fb_selftest_bounded_wait: a barrier nobody signals, a few dozen polls) must end by
+    itself, leave its code in the device error word, and not poison the context: while the word is set the tensor-core
+    GEMM returns without computing; once the word has been read (which clears it) the same launch gives the right
+    result."""
+    from fluxb200 import lib
+    h = C.c_void_p()
+    lib.call("fb_ctx_create", 0, C.byref(h))
+    try:
+        def err():
+            out = C.c_int32(0)
+            lib.call("fb_device_error", h, stream(), C.byref(out))
+            return out.value
+
+        assert err() == 0
+        lib.call("fb_selftest_bounded_wait", h, stream(), 64)
+        assert err() == 9001          # reported ...
+        assert err() == 0             # ... and cleared by the read
+        rng = np.random.default_rng(0)
+        m = n = k = 256
+        A, B = rng.normal(size=(m, k)).astype(np.float32), rng.normal(size=(k, n)).astype(np.float32)
+        dA, dB = dev(A), dev(B)
+        dC = torch.full((m * n,), 7.0, device="cuda")
+        lib.call("fb_selftest_bounded_wait", h, stream(), 64)
+        lib.call("fb_gemm_f32", h, stream(), 0, 0, m, n, k, P(dA), m, P(dB), k, P(dC), m, 0, PREC["3xtf32"])
+        torch.cuda.synchronize()
+        assert (dC == 7.0).all()      # the GEMM saw the word and did not start
+        assert err() == 9001
+        lib.call("fb_gemm_f32", h, stream(), 0, 0, m, n, k, P(dA), m, P(dB), k, P(dC), m, 0, PREC["3xtf32"])
+        close(host(dC, (m, n)), A.astype(np.float64) @ B.astype(np.float64), name="gemm after the error was read")
+        assert err() == 0
+        st = lib.raw().fb_selftest_bounded_wait(h, stream(), 1 << 20)
+        assert st == -1               # the self test refuses long waits
+    finally:
+        lib.call("fb_ctx_destroy", h)
