@@ -588,14 +588,14 @@ struct GemmWorkspace {
   int* tickets;
 };
 
-// FLUXB200_STREAMK = 0 keeps every tile whole.
-bool stream_k_enabled() {
+// FLUXB200_STREAMK = 0 keeps every tile whole; 2 cuts every incomplete last wave, however full.
+int stream_k_mode() {
   static int on = -1;
   if (on < 0) {
     const char* e = getenv("FLUXB200_STREAMK");
-    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+    on = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
   }
-  return on != 0;
+  return on;
 }
 
 // 3-d view {32, K, MN / 32} of an MN-major matrix (row k holds MN contiguous floats): box {32, BK, chunks}.
@@ -659,7 +659,8 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   // gain nothing: the kernel runs at the power limit, where idle SMs let the busy ones clock higher.)
   const int64_t rest = num_tiles % Gmax;
   const GemmWorkspace* gw = (const GemmWorkspace*)ctx->gemm_ws;
-  if (rest != 0 && 4 * rest < 3 * Gmax && sch.nu > 1 && rest * sch.nu < 0x40000000 && gw != nullptr && stream_k_enabled()) {
+  const int skm = stream_k_mode();
+  if (rest != 0 && (4 * rest < 3 * Gmax || skm == 2) && sch.nu > 1 && rest * sch.nu < 0x40000000 && gw != nullptr && skm != 0) {
     sch.dp_tiles = (int)(num_tiles - rest);
     sch.U = (int)(rest * sch.nu);
     sch.ws = gw->ws;
@@ -739,6 +740,12 @@ int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& 
   // split / barrier round trip, so one 86 %-full wave of them beats two waves of 128 x 128 tiles
   const int64_t tiles256 = ((a.M + BM - 1) / BM) * ((a.N + 255) / 256);
   const bool narrow = (a.N <= 128) || (2 * tiles256 <= ctx->sm_count);
+  // FLUXB200_GEMM_TILE = one256 | one128 forces the one-CTA tile of that width (measurement aid)
+  static const char* tile_env = getenv("FLUXB200_GEMM_TILE");
+  if (passes == 3 && tile_env != nullptr && !passes_flag_pair) {
+    if (strcmp(tile_env, "one256") == 0) return launch_layout<256, 3, false>(ctx, stream, a);
+    if (strcmp(tile_env, "one128") == 0) return launch_layout<128, 3, false>(ctx, stream, a);
+  }
   if (passes == 3) {
     // two-CTA 256 x 256 tiles once there are enough of them to occupy a good part of the SM pairs
     const int64_t pair_tiles = ((a.M + 255) / 256) * ((a.N + 255) / 256);

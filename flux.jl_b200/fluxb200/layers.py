@@ -446,6 +446,8 @@ class Recurrence(Layer):
 
     def __call__(self, x: B200Array, state=None):
         cell = self.cell
+        if not isinstance(cell, (LSTMCell, GRUCell)):
+            return _scan_family(self, x, state)
         in_dim = cell.Wi.size[1]
         _size_check(cell, x, 1, in_dim)
         if x.ndim == 2:
@@ -634,3 +636,315 @@ class MultiHeadAttention(Layer):
         v = self.v_proj(v_in)
         x, alpha = dot_product_attention(q, k, v, bias, nheads=self.nheads, mask=mask)
         return self.out_proj(x), alpha
+
+
+# ------------------------------------------------------------- the rest of the layer family ---
+class GroupNorm(Layer):
+    """GroupNorm(chs, G, λ; affine=true, eps=1f-5) (normalise.jl:440-489): every group of chs/G consecutive channels of a
+    sample is normalised with its own mean and biased variance; per-channel scale γ and bias β."""
+
+    _fields = ("G", "λ", "β", "γ", "μ", "σ2", "ε", "momentum", "affine", "track_stats", "active", "chs")
+    _trainable = ("β", "γ")
+
+    def __init__(self, chs: int, G: int, sigma="identity", affine=True, active=None, eps=1e-5, momentum=0.1):
+        if chs % G != 0:
+            raise ArgumentError(f"The number of groups ({G}) must divide the number of channels ({chs})")
+        self.chs, self.G = int(chs), int(G)
+        self.λ = _act_name(sigma)
+        self.affine, self.track_stats, self.active = bool(affine), False, active
+        self.ε, self.momentum = float(eps), float(momentum)
+        self.β = gpu(np.zeros(chs, np.float32)) if affine else None
+        self.γ = gpu(np.ones(chs, np.float32)) if affine else None
+        self.μ = self.σ2 = None
+
+    def __repr__(self):
+        return f"GroupNorm({self.chs}, {self.G}, {self.λ})"
+
+    def _groups(self):
+        return self.G
+
+    def __call__(self, x: B200Array) -> B200Array:
+        N = x.ndim
+        if N < 2:
+            raise DimensionMismatch(f"layer {self} expects ndims(input) >= 2, but got {x}")
+        _size_check(self, x, N - 1, self.chs)
+        s = int(np.prod(x.size[:N - 2], dtype=np.int64)) if N > 2 else 1
+        c, n, G = self.chs, x.size[-1], self._groups()
+        ctx = context()
+        act = lib.ACT[self.λ]
+        y, mean, rstd = empty(x.size), empty((n * G,)), empty((n * G,))
+        lib.call("fb_groupnorm_fwd", ctx.handle, ctx.stream, x.ptr, _ptr(self.γ), _ptr(self.β), y.ptr, mean.ptr, rstd.ptr,
+                 s, c, n, G, self.ε, act)
+        self._after_forward(mean, rstd, s, c, n)
+        if Tape.active:
+            g, b = self.γ, self.β
+
+            def pullback(gs, x=x):
+                dy = gs[0]
+                dx = empty(x.size)
+                dg = empty((c,)) if g is not None else None
+                dbeta = empty((c,)) if b is not None else None
+                lib.call("fb_groupnorm_bwd", ctx.handle, ctx.stream, x.ptr, _ptr(g), _ptr(b), mean.ptr, rstd.ptr, dy.ptr, dx.ptr,
+                         _ptr(dg), _ptr(dbeta), s, c, n, G, act)
+                res = [(x, dx)] if Tape.needs(x) else []
+                if g is not None:
+                    res += [(g, dg), (b, dbeta)]
+                return res
+
+            Tape.record(y, [x, g, b], pullback)
+        return y
+
+    def _after_forward(self, mean, rstd, s, c, n):
+        pass
+
+
+class InstanceNorm(GroupNorm):
+    """InstanceNorm(chs, λ; affine=false, track_stats=false, eps=1f-5, momentum=0.1f0) (normalise.jl:330-393): every
+    (channel, sample) slice is normalised on its own; with track_stats the running statistics are updated while
+    training and used for inference."""
+
+    def __init__(self, chs: int, sigma="identity", affine=False, track_stats=False, active=None, eps=1e-5, momentum=0.1):
+        super().__init__(chs, chs, sigma, affine=affine, active=active, eps=eps, momentum=momentum)
+        self.track_stats = bool(track_stats)
+        self.μ = gpu(np.zeros(chs, np.float32)) if track_stats else None
+        self.σ2 = gpu(np.ones(chs, np.float32)) if track_stats else None
+
+    def __repr__(self):
+        return f"InstanceNorm({self.chs}, {self.λ})"
+
+    def _isactive(self):
+        return Tape.active if self.active is None else bool(self.active)
+
+    def __call__(self, x: B200Array) -> B200Array:
+        if self.track_stats and not self._isactive():
+            N = x.ndim
+            _size_check(self, x, N - 1, self.chs)
+            s = int(np.prod(x.size[:N - 2], dtype=np.int64)) if N > 2 else 1
+            ctx = context()
+            y = empty(x.size)
+            lib.call("fb_batchnorm_fwd_infer", ctx.handle, ctx.stream, x.ptr, _ptr(self.γ), _ptr(self.β), self.μ.ptr, self.σ2.ptr,
+                     y.ptr, s, self.chs, x.size[-1], self.ε, lib.ACT[self.λ])
+            return y
+        return super().__call__(x)
+
+    def _after_forward(self, mean, rstd, s, c, n):
+        if self.track_stats and self._isactive():
+            ctx = context()
+            lib.call("fb_instancenorm_update_stats", ctx.handle, ctx.stream, mean.ptr, rstd.ptr, self.μ.ptr, self.σ2.ptr, s, c, n,
+                     self.ε, self.momentum)
+
+
+class Embedding(Layer):
+    """Embedding(in => out; init=randn32, padding_idx=nothing) (basic.jl:778-800): a lookup table whose columns are
+    selected by 1-based integer indices of any shape; the padding column is zero and receives no gradient."""
+
+    _fields = ("weight", "padding_idx")
+    _trainable = ("weight",)
+
+    def __init__(self, weight, padding_idx=None, init=None):
+        if isinstance(weight, (tuple, list)) and len(weight) == 2 and all(isinstance(v, (int, np.integer)) for v in weight):
+            from .init import randn32
+            vocab, out = int(weight[0]), int(weight[1])
+            weight = (init or randn32)(out, vocab)
+            if padding_idx is not None:
+                if not (1 <= padding_idx <= vocab):
+                    raise ArgumentError(f"padding_idx={padding_idx} must be in 1:{vocab}")
+                weight[:, padding_idx - 1] = 0
+        self.weight = gpu(weight) if isinstance(weight, np.ndarray) else weight
+        self.padding_idx = None if padding_idx is None else int(padding_idx)
+
+    def __repr__(self):
+        return f"Embedding({self.weight.size[1]} => {self.weight.size[0]})"
+
+    def __call__(self, idx) -> B200Array:
+        if isinstance(idx, (int, np.integer)):
+            idx = np.array([idx], np.int32)
+            scalar = True
+        else:
+            scalar = False
+        if isinstance(idx, np.ndarray):
+            if idx.size and (idx.min() < 1 or idx.max() > self.weight.size[1]):
+                raise IndexError(f"BoundsError: attempt to access {self.weight.size[1]}-column embedding at index outside 1:{self.weight.size[1]}")
+            idx = gpu(idx.astype(np.int32))
+        out_dim, vocab = self.weight.size
+        n = idx.numel()
+        ctx = context()
+        pad = self.padding_idx or 0
+        y = empty((out_dim,) + (() if scalar else idx.size))
+        lib.call("fb_embedding_fwd", ctx.handle, ctx.stream, self.weight.ptr, idx.ptr, y.ptr, out_dim, vocab, n, pad)
+        if Tape.needs(self.weight):
+            W = self.weight
+
+            def pullback(gs):
+                dW = empty(W.size)
+                lib.call("fb_embedding_bwd", ctx.handle, ctx.stream, gs[0].ptr, idx.ptr, dW.ptr, out_dim, vocab, n, pad)
+                return [(W, dW)]
+
+            Tape.record(y, [W], pullback)
+        return y
+
+
+class Dropout(Layer):
+    """Dropout(p; active=nothing, seed) (normalise.jl:54-92): while active, every element is zeroed with probability p and
+    the rest scaled by 1 / (1 - p); inactive (test mode, or outside `withgradient` when active is None) it is the
+    identity.  The mask is a counter-based function of (seed, call number, element index), so the backward pass
+    regenerates it instead of storing it."""
+
+    _fields = ("p", "active", "seed")
+    _trainable = ()
+
+    def __init__(self, p: float, active=None, seed: int = 0):
+        if not (0 <= p <= 1):
+            raise ArgumentError(f"Dropout expects 0 ≤ p ≤ 1, got p = {p}")
+        self.p, self.active, self.seed = float(p), active, int(seed)
+        self.calls = 0
+
+    def _isactive(self):
+        return Tape.active if self.active is None else bool(self.active)
+
+    def next_offset(self, count: int) -> int:
+        """Counter offset of this call's mask; successive calls take disjoint counter ranges."""
+        off = self.calls
+        self.calls += (count + 3) // 4
+        return off
+
+    def __call__(self, x: B200Array) -> B200Array:
+        if not self._isactive() or self.p == 0.0:
+            return x
+        ctx = context()
+        y = empty(x.size)
+        off = self.next_offset(x.numel())
+        lib.call("fb_dropout", ctx.handle, ctx.stream, x.ptr, y.ptr, x.numel(), self.p, self.seed, off)
+        if Tape.needs(x):
+            def pullback(gs):
+                dx = empty(x.size)
+                lib.call("fb_dropout", ctx.handle, ctx.stream, gs[0].ptr, dx.ptr, x.numel(), self.p, self.seed, off)
+                return [(x, dx)]
+
+            Tape.record(y, [x], pullback)
+        return y
+
+
+class RNNCell(Layer):
+    """RNNCell(in => out, σ = tanh) (recurrent.jl:140-198): h' = σ.(Wi x + Wh h + b)."""
+
+    _fields = ("σ", "Wi", "Wh", "bias")
+    _trainable = ("Wi", "Wh", "bias")
+    NG = 1
+
+    def __init__(self, Wi, Wh=None, bias=True, sigma="tanh", init_kernel=glorot_uniform, init_recurrent_kernel=glorot_uniform):
+        if isinstance(Wi, (tuple, list)) and len(Wi) == 2 and all(isinstance(v, (int, np.integer)) for v in Wi):
+            in_dim, out = int(Wi[0]), int(Wi[1])
+            Wi, Wh = init_kernel(out, in_dim), init_recurrent_kernel(out, out)
+        self.Wi, self.Wh = gpu(Wi), gpu(Wh)
+        self.σ = _act_name(sigma)
+        if self.σ not in ("identity", "relu", "tanh", "sigmoid"):
+            raise lib.FluxB200Error(-7, f"RNNCell activation {self.σ!r} has no B200 kernel (identity, relu, tanh, sigmoid)")
+        rows = self.Wi.size[0]
+        self.bias = zeros((rows,)) if bias is True else (False if bias in (False, None) else gpu(bias))
+
+    @property
+    def hidden(self):
+        return self.Wh.size[1]
+
+    def initialstates(self):
+        return zeros((self.hidden,))
+
+
+class GRUv3Cell(Layer):
+    """GRUv3Cell(in => out) (recurrent.jl:765-809): like GRUCell, but the candidate state uses a separate matrix
+    Wh_h̃ applied to r .* h."""
+
+    _fields = ("Wi", "Wh", "b", "Wh_h̃")
+    NG = 3
+
+    def __init__(self, Wi, Wh=None, b=True, Wh_h=None, init_kernel=glorot_uniform, init_recurrent_kernel=glorot_uniform):
+        if isinstance(Wi, (tuple, list)) and len(Wi) == 2 and all(isinstance(v, (int, np.integer)) for v in Wi):
+            in_dim, out = int(Wi[0]), int(Wi[1])
+            Wi, Wh, Wh_h = init_kernel(out * 3, in_dim), init_recurrent_kernel(out * 3, out), init_recurrent_kernel(out, out)
+        self.Wi, self.Wh = gpu(Wi), gpu(Wh)
+        setattr(self, "Wh_h̃", gpu(Wh_h))
+        rows = self.Wi.size[0]
+        self.b = zeros((rows,)) if b is True else (False if b in (False, None) else gpu(b))
+
+    @property
+    def Wh_h(self):
+        return getattr(self, "Wh_h̃")
+
+    @property
+    def hidden(self):
+        return self.Wh.size[1]
+
+    def initialstates(self):
+        return zeros((self.hidden,))
+
+
+def _scan_family(rec, x: B200Array, state=None):
+    """scan(cell, x, state) for RNNCell and GRUv3Cell (recurrent.jl:1-8)."""
+    cell = rec.cell
+    in_dim = cell.Wi.size[1]
+    _size_check(cell, x, 1, in_dim)
+    if x.ndim == 2:
+        x3 = x.reshape(x.size[0], x.size[1], 1)
+    elif x.ndim == 3:
+        x3 = x
+    else:
+        raise DimensionMismatch(f"Recurrence expects a 2-d or 3-d input, got {x}")
+    _, T, B = x3.size
+    H = cell.hidden
+    ctx = context()
+    is_rnn = isinstance(cell, RNNCell)
+    bias = cell.bias if is_rnn else cell.b
+    bias = bias if bias is not False else None
+    h0 = _broadcast_state(state, H, B)
+    out, hT = empty((H, T, B)), empty((H, B))
+    recording = Tape.active
+    cache = None
+    if is_rnn:
+        act = lib.ACT[cell.σ]
+        lib.call("fb_rnn_fwd", ctx.handle, ctx.stream, act, cell.Wi.ptr, cell.Wh.ptr, _ptr(bias), x3.ptr, _ptr(h0), out.ptr, hT.ptr,
+                 in_dim, H, T, B)
+    else:
+        if recording:
+            cache = torch.empty(max(lib.raw().fb_gruv3_cache_bytes(in_dim, H, T, B) // 4, 1), dtype=torch.float32, device=x.t.device)
+        lib.call("fb_gruv3_fwd", ctx.handle, ctx.stream, cell.Wi.ptr, cell.Wh.ptr, _ptr(bias), cell.Wh_h.ptr, x3.ptr, _ptr(h0), out.ptr,
+                 hT.ptr, cache.data_ptr() if cache is not None else None, in_dim, H, T, B)
+    if recording:
+        def pullback(gs, x3=x3):
+            dout = gs[0] if gs[0] is not None else zeros(out.size)
+            dhT = gs[1]
+            dWi, dWh = empty(cell.Wi.size), empty(cell.Wh.size)
+            db = empty(bias.size) if bias is not None else None
+            dx = empty(x3.size) if Tape.needs(x3) else None
+            if is_rnn:
+                scratch = torch.empty(max(lib.raw().fb_rnn_cache_bytes(in_dim, H, T, B) // 4, 1), dtype=torch.float32, device=x.t.device)
+                lib.call("fb_rnn_bwd", ctx.handle, ctx.stream, act, cell.Wi.ptr, cell.Wh.ptr, x3.ptr, _ptr(h0), out.ptr,
+                         scratch.data_ptr(), dout.ptr, _ptr(dhT), dWi.ptr, dWh.ptr, _ptr(db), _ptr(dx), in_dim, H, T, B)
+                res = [(cell.Wi, dWi), (cell.Wh, dWh)]
+            else:
+                dWhh = empty(cell.Wh_h.size)
+                lib.call("fb_gruv3_bwd", ctx.handle, ctx.stream, cell.Wi.ptr, cell.Wh.ptr, cell.Wh_h.ptr, x3.ptr, _ptr(h0), out.ptr,
+                         cache.data_ptr(), dout.ptr, _ptr(dhT), dWi.ptr, dWh.ptr, _ptr(db), dWhh.ptr, _ptr(dx), in_dim, H, T, B)
+                res = [(cell.Wi, dWi), (cell.Wh, dWh), (cell.Wh_h, dWhh)]
+            if bias is not None:
+                res.append((bias, db))
+            if dx is not None:
+                res.append((x3, dx))
+            return res
+
+        ins = [x3, cell.Wi, cell.Wh, bias] + ([] if is_rnn else [cell.Wh_h])
+        Tape.record([out, hT], ins, pullback)
+    y = out if x.ndim == 3 else out.reshape(H, T)
+    if rec.return_state:
+        return y, hT
+    return y
+
+
+def RNN(Wi, Wh=None, bias=True, sigma="tanh", return_state=False, **init):
+    """RNN(in => out, σ) == Recurrence(RNNCell(in => out, σ)) (recurrent.jl:262-300)."""
+    return Recurrence(RNNCell(Wi, Wh, bias, sigma, **init), return_state=return_state)
+
+
+def GRUv3(Wi, Wh=None, b=True, Wh_h=None, return_state=False, **init):
+    """GRUv3(in => out) == Recurrence(GRUv3Cell(in => out)) (recurrent.jl:860-900)."""
+    return Recurrence(GRUv3Cell(Wi, Wh, b, Wh_h, **init), return_state=return_state)

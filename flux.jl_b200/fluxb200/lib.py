@@ -64,6 +64,12 @@ PROTOTYPES = {
     "fb_batchnorm_fwd_train": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _f, _i32, _i32]),
     "fb_batchnorm_fwd_infer": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _i32]),
     "fb_batchnorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i32]),
+    "fb_groupnorm_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i32]),
+    "fb_groupnorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32]),
+    "fb_instancenorm_update_stats": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _f]),
+    "fb_embedding_fwd": (_i32, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i32]),
+    "fb_embedding_bwd": (_i32, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i32]),
+    "fb_dropout": (_i32, [_p, _p, _p, _p, _i64, _f, C.c_uint64, C.c_uint64]),
     "fb_logitcrossentropy_labels": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f]),
     "fb_logitcrossentropy_dense": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f]),
     "fb_sumsq": (_i32, [_p, _p, _p, _i64, _p]),
@@ -86,6 +92,12 @@ PROTOTYPES = {
     "fb_lstm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),
     "fb_gru_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),
     "fb_gru_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),
+    "fb_rnn_cache_bytes": (_i64, [_i64, _i64, _i64, _i64]),
+    "fb_rnn_fwd": (_i32, [_p, _p, _i32, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),
+    "fb_rnn_bwd": (_i32, [_p, _p, _i32, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),
+    "fb_gruv3_cache_bytes": (_i64, [_i64, _i64, _i64, _i64]),
+    "fb_gruv3_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),
+    "fb_gruv3_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64]),
     "fb_attn_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i32]),
     "fb_attn_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i32]),
     "fb_attn_scores": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32]),

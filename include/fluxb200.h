@@ -190,6 +190,47 @@ int32_t fb_batchnorm_bwd(fb_ctx* ctx, void* stream, const float* x, const float*
                          const float* dy, float* dx, float* dgamma, float* dbeta, int64_t s, int64_t c,
                          int64_t n, int32_t act);
 
+/* ------------------------------------------------------------------- GroupNorm / InstanceNorm -- */
+
+/* GroupNorm on x viewed as [n][c][s]: every (sample, group of c/groups channels) is normalised with its own mean and
+ * biased variance over (c/groups)*s values, then y = act.(gamma[ch] * xhat + beta[ch]) per channel.  gamma/beta may be
+ * NULL (affine=false).  mean/rstd hold n*groups floats, saved for the backward pass.  groups must divide c.
+ * Replaces (gn::GroupNorm)(x) = gn.lambda.(NNlib.groupnorm(gamma, beta, x, G; eps)) (src/layers/normalise.jl:486-489).
+ * With groups == c this is InstanceNorm's training-mode arithmetic (normalise.jl:388-393 -> NNlib.instancenorm). */
+int32_t fb_groupnorm_fwd(fb_ctx* ctx, void* stream, const float* x, const float* gamma, const float* beta,
+                         float* y, float* mean, float* rstd, int64_t s, int64_t c, int64_t n, int64_t groups,
+                         float eps, int32_t act);
+/* Reverse of fb_groupnorm_fwd (external NNlib rrule): dx, dgamma[c], dbeta[c] (the last two may be NULL). */
+int32_t fb_groupnorm_bwd(fb_ctx* ctx, void* stream, const float* x, const float* gamma, const float* beta,
+                         const float* mean, const float* rstd, const float* dy, float* dx, float* dgamma,
+                         float* dbeta, int64_t s, int64_t c, int64_t n, int64_t groups, int32_t act);
+/* InstanceNorm with track_stats=true: running_mean <- (1-m) running_mean + m * mean over samples of the per-instance
+ * means, running_var likewise from the per-instance biased variances times s/(s-1), from the mean/rstd (n*c floats)
+ * that fb_groupnorm_fwd saved with groups == c (rule pinned by test/layers/normalisation.jl:262-275).  Inference with
+ * tracked statistics is fb_batchnorm_fwd_infer. */
+int32_t fb_instancenorm_update_stats(fb_ctx* ctx, void* stream, const float* mean, const float* rstd,
+                                     float* running_mean, float* running_var, int64_t s, int64_t c, int64_t n,
+                                     float eps, float momentum);
+
+/* ------------------------------------------------------------------------ Embedding / Dropout -- */
+
+/* y[:, i] = W[:, idx[i]] for 1-based int32 indices (NNlib.gather), zero columns where idx[i] == padding_idx
+ * (padding_idx 0 = none).  An index outside 1:vocab records code 5001 in the device error word (the reference throws
+ * a BoundsError) and yields a zero column.  Replaces (m::Embedding)(x) (src/layers/basic.jl:794-800). */
+int32_t fb_embedding_fwd(fb_ctx* ctx, void* stream, const float* W, const int32_t* idx, float* y, int64_t out_dim,
+                         int64_t vocab, int64_t n, int32_t padding_idx);
+/* Reverse of fb_embedding_fwd: dW[out, vocab] is zeroed and receives the scatter-add of dy's columns (the rrule of
+ * NNlib.gather); the padding column stays zero. */
+int32_t fb_embedding_bwd(fb_ctx* ctx, void* stream, const float* dy, const int32_t* idx, float* dW, int64_t out_dim,
+                         int64_t vocab, int64_t n, int32_t padding_idx);
+/* y[i] = x[i] / (1 - p) where the mask keeps element i, else 0 (NNlib.dropout, called at src/layers/normalise.jl:83).
+ * The mask is a pure function of (seed, offset + i): Philox4x32-10 keyed by `seed`, counter offset + i/4, word i%4,
+ * keep iff (word >> 8) * 2^-24 >= p.  Calling it again with the same seed and offset on the cotangent is the
+ * backward pass.  The reference draws from a Julia RNG whose stream cannot be reproduced; only the distribution
+ * matches. */
+int32_t fb_dropout(fb_ctx* ctx, void* stream, const float* x, float* y, int64_t count, float p, uint64_t seed,
+                   uint64_t offset);
+
 /* ----------------------------------------------------------------------- losses / helpers -- */
 
 /* loss = mean_n( -sum_c y[c,n] * logsoftmax(yhat)[c,n] ) with one-hot y given as 1-based int32 labels;
@@ -283,6 +324,31 @@ int32_t fb_gru_bwd(fb_ctx* ctx, void* stream, const float* Wi, const float* Wh, 
                    const float* h0, const float* out, const void* cache, const float* dout, const float* dhT, float* dWi,
                    float* dWh, float* db, float* dx, int64_t in_dim, int64_t hidden, int64_t seq_len,
                    int64_t batch);
+
+/* Recurrence(RNNCell)(x): h' = act.(Wi x + Wh h + b) (src/layers/recurrent.jl:193-198) over x[in,T,B] -> out[H,T,B],
+ * final state hT[H,B] (optional); act is identity, relu, tanh or sigmoid.  The input projection is one GEMM over all
+ * steps; every step is one GEMM with a fused accumulate + activation epilogue. */
+int64_t fb_rnn_cache_bytes(int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch);
+int32_t fb_rnn_fwd(fb_ctx* ctx, void* stream, int32_t act, const float* Wi, const float* Wh, const float* b,
+                   const float* x, const float* h0, float* out, float* hT, int64_t in_dim, int64_t hidden,
+                   int64_t seq_len, int64_t batch);
+/* Reverse (BPTT) of fb_rnn_fwd; `cache` is scratch of fb_rnn_cache_bytes. db and dx may be NULL. */
+int32_t fb_rnn_bwd(fb_ctx* ctx, void* stream, int32_t act, const float* Wi, const float* Wh, const float* x,
+                   const float* h0, const float* out, void* cache, const float* dout, const float* dhT, float* dWi,
+                   float* dWh, float* db, float* dx, int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch);
+
+/* Recurrence(GRUv3Cell)(x) (src/layers/recurrent.jl:795-809): r, z from the first two row blocks of Wi / Wh[3H,H],
+ * htilde = tanh(gx3 + Wh_h (r .* h) + b3) with the separate matrix Wh_h[H,H], h' = (1-z) htilde + z h.  The third row
+ * block of Wh is never read by the cell, so its gradient is zero.  `cache` (fb_gruv3_cache_bytes) is filled by the
+ * forward pass and consumed by the backward pass; it may be NULL when no backward pass follows. */
+int64_t fb_gruv3_cache_bytes(int64_t in_dim, int64_t hidden, int64_t seq_len, int64_t batch);
+int32_t fb_gruv3_fwd(fb_ctx* ctx, void* stream, const float* Wi, const float* Wh, const float* b, const float* Wh_h,
+                     const float* x, const float* h0, float* out, float* hT, void* cache, int64_t in_dim,
+                     int64_t hidden, int64_t seq_len, int64_t batch);
+int32_t fb_gruv3_bwd(fb_ctx* ctx, void* stream, const float* Wi, const float* Wh, const float* Wh_h, const float* x,
+                     const float* h0, const float* out, void* cache, const float* dout, const float* dhT, float* dWi,
+                     float* dWh, float* db, float* dWh_h, float* dx, int64_t in_dim, int64_t hidden, int64_t seq_len,
+                     int64_t batch);
 
 /* -------------------------------------------------------------------------- Attention -- */
 

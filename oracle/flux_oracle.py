@@ -294,6 +294,139 @@ def batchnorm_bwd(x, gamma, beta, dy, eps=1e-5, sigma="identity"):
 
 
 # --------------------------------------------------------------------------
+# GroupNorm / InstanceNorm (normalise.jl:388-393, 486-489 -> NNlib.groupnorm / instancenorm)
+# --------------------------------------------------------------------------
+def _group_view(x, G):
+    """x (..., C, N) -> (S, C/G, G, N) with S the product of the leading dims: what NNlib.groupnorm reshapes to."""
+    C, N = x.shape[-2], x.shape[-1]
+    S = x.size // (C * N)
+    # Julia memory order has the first index fastest and channel c = g * (C/G) + k (k fastest): in numpy's C-order
+    # view of the Julia-shaped array that is a split of the channel axis into (G, C/G)
+    return x.reshape(S, G, C // G, N), S
+
+
+def groupnorm_fwd(x, gamma, beta, G, eps=1e-5, sigma="identity", return_stats=False):
+    """(gn::GroupNorm)(x) (normalise.jl:486-489): per (group, sample) mean and biased variance over the spatial dims
+    and the C/G channels of the group, per-channel affine, activation.  Frozen outputs of the reference's test
+    (test/layers/normalisation.jl:410, 431) pin the grouping of consecutive channels and the biased variance."""
+    C = x.shape[-2]
+    if C % G:
+        raise ValueError(f"The number of groups ({G}) must divide the number of channels ({C})")
+    xv, S = _group_view(x, G)
+    mu = xv.mean(axis=(0, 2), keepdims=True)
+    var = ((xv - mu) ** 2).mean(axis=(0, 2), keepdims=True)
+    rstd = 1.0 / np.sqrt(var + x.dtype.type(eps))
+    xhat = ((xv - mu) * rstd).reshape(x.shape)
+    z = xhat
+    if gamma is not None:
+        shp = [1] * x.ndim
+        shp[-2] = C
+        z = gamma.reshape(shp) * xhat + beta.reshape(shp)
+    y = act(sigma, z)
+    if return_stats:
+        return y, mu.reshape(G, -1), rstd.reshape(G, -1)
+    return y
+
+
+def groupnorm_bwd(x, gamma, beta, dy, G, eps=1e-5, sigma="identity"):
+    """Reverse of groupnorm_fwd: (dx, dgamma, dbeta)."""
+    C = x.shape[-2]
+    xv, S = _group_view(x, G)
+    mu = xv.mean(axis=(0, 2), keepdims=True)
+    var = ((xv - mu) ** 2).mean(axis=(0, 2), keepdims=True)
+    rstd = 1.0 / np.sqrt(var + x.dtype.type(eps))
+    xhat = ((xv - mu) * rstd).reshape(x.shape)
+    shp = [1] * x.ndim
+    shp[-2] = C
+    if gamma is not None:
+        g_ = gamma.reshape(shp)
+        z = g_ * xhat + beta.reshape(shp)
+    else:
+        g_, z = 1.0, xhat
+    dz = dy * act_grad(sigma, z)
+    axes = tuple(i for i in range(x.ndim) if i != x.ndim - 2)
+    dgamma, dbeta = (dz * xhat).sum(axis=axes), dz.sum(axis=axes)
+    g = (dz * g_).reshape(xv.shape)
+    xh = xhat.reshape(xv.shape)
+    dx = (rstd * (g - g.mean(axis=(0, 2), keepdims=True) - xh * (g * xh).mean(axis=(0, 2), keepdims=True))).reshape(x.shape)
+    if gamma is None:
+        return dx, None, None
+    return dx, dgamma, dbeta
+
+
+def instancenorm_fwd_train(x, gamma, beta, run_mean, run_var, momentum=0.1, eps=1e-5, sigma="identity", track_stats=False):
+    """(l::InstanceNorm)(x) in training (normalise.jl:388-393): GroupNorm with one channel per group; with
+    track_stats the running statistics take the batch mean of the per-instance statistics, the variance corrected
+    by n/(n-1) with n the number of spatial positions (test/layers/normalisation.jl:262-275).
+    Returns (y, new_running_mean, new_running_var)."""
+    C, N = x.shape[-2], x.shape[-1]
+    y = groupnorm_fwd(x, gamma, beta, C, eps, sigma)
+    if not track_stats or run_mean is None:
+        return y, run_mean, run_var
+    S = x.size // (C * N)
+    xv = x.reshape(S, C, N)
+    mu = xv.mean(axis=0)                       # (C, N)
+    var = ((xv - mu) ** 2).mean(axis=0)
+    m = x.dtype.type(momentum)
+    corr = x.dtype.type(S / (S - 1)) if S > 1 else x.dtype.type(1)
+    return y, (1 - m) * run_mean + m * mu.mean(axis=1), (1 - m) * run_var + m * corr * var.mean(axis=1)
+
+
+# --------------------------------------------------------------------------
+# Embedding (basic.jl:794-800) and Dropout (normalise.jl:83 -> NNlib.dropout)
+# --------------------------------------------------------------------------
+def embedding_fwd(W, idx, padding_idx=None):
+    """(m::Embedding)(x): columns W[:, idx] for 1-based integer indices of any shape; padding columns are zero."""
+    idx = np.asarray(idx)
+    if idx.min() < 1 or idx.max() > W.shape[1]:
+        raise IndexError("BoundsError: embedding index outside 1:vocabulary")
+    y = W[:, idx.reshape(-1) - 1]
+    if padding_idx is not None:
+        y = y * (idx.reshape(1, -1) != padding_idx)
+    return y.reshape((W.shape[0],) + idx.shape)
+
+
+def embedding_bwd(W, idx, dy, padding_idx=None):
+    """Reverse of embedding_fwd: scatter-add of dy's columns (the rrule of NNlib.gather)."""
+    idx = np.asarray(idx).reshape(-1)
+    d = dy.reshape(W.shape[0], -1)
+    dW = np.zeros_like(W)
+    keep = np.ones(idx.shape, bool) if padding_idx is None else idx != padding_idx
+    np.add.at(dW.T, idx[keep] - 1, d[:, keep].T)
+    return dW
+
+
+def philox4x32_10(counter, seed):
+    """Philox4x32-10 (Salmon, Moraes, Dror, Shaw 2011) for uint64 counters and one uint64 key; returns (n, 4) uint32.
+    The dropout mask of the device library is defined in terms of this generator, so it is restated here bit for bit."""
+    counter = np.asarray(counter, dtype=np.uint64)
+    c = [(counter & np.uint64(0xFFFFFFFF)).astype(np.uint64), (counter >> np.uint64(32)).astype(np.uint64),
+         np.zeros_like(counter), np.zeros_like(counter)]
+    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64((seed >> 32) & 0xFFFFFFFF)
+    M0, M1, MASK = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0, p1 = M0 * c[0], M1 * c[2]
+        c = [((p1 >> np.uint64(32)) ^ c[1] ^ k0) & MASK, p1 & MASK, ((p0 >> np.uint64(32)) ^ c[3] ^ k1) & MASK, p0 & MASK]
+        k0 = (k0 + np.uint64(0x9E3779B9)) & MASK
+        k1 = (k1 + np.uint64(0xBB67AE85)) & MASK
+    return np.stack(c, axis=-1).astype(np.uint32)
+
+
+def dropout_mask(count, p, seed, offset=0):
+    """keep[i] for i in 0:count: word i % 4 of Philox(counter = offset + i // 4, key = seed); keep iff
+    (word >> 8) * 2^-24 >= p."""
+    quads = (count + 3) // 4
+    words = philox4x32_10(np.arange(quads, dtype=np.uint64) + np.uint64(offset), seed).reshape(-1)[:count]
+    u = (words >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / 16777216.0)
+    return u >= np.float32(p)
+
+
+def dropout_fwd(x, p, mask):
+    """NNlib.dropout with a given keep-mask: x .* mask ./ (1 - p) (Flux's Dropout, normalise.jl:83)."""
+    return x * mask.reshape(x.shape) / x.dtype.type(1 - p)
+
+
+# --------------------------------------------------------------------------
 # Recurrence: scan (recurrent.jl:1-8), LSTMCell (:411-419), GRUCell (:614-628)
 # --------------------------------------------------------------------------
 def _sigmoid(z):
@@ -416,6 +549,98 @@ def gru_scan_bwd(Wi, Wh, b, x, dout, dhT=None):
     if b is None or b is False:
         db = None
     return dWi, dWh, db, dx
+
+
+def rnn_scan_fwd(Wi, Wh, b, x, sigma="tanh", h0=None):
+    """Recurrence(RNNCell)(x) (recurrent.jl:193-198): h' = sigma.(Wi x + Wh h + b); returns (out, hT)."""
+    H = Wh.shape[1]
+    I, T, B = x.shape
+    dt = x.dtype
+    h = np.zeros((H, B), dt) if h0 is None else np.broadcast_to(h0.reshape(H, -1), (H, B)).astype(dt)
+    bb = np.zeros((H, 1), dt) if (b is None or b is False) else b.reshape(-1, 1)
+    out = np.empty((H, T, B), dt)
+    for t in range(T):
+        h = act(sigma, Wi @ x[:, t, :] + Wh @ h + bb)
+        out[:, t, :] = h
+    return out, h
+
+
+def rnn_scan_bwd(Wi, Wh, b, x, dout, sigma="tanh", h0=None, dhT=None):
+    """BPTT through rnn_scan_fwd.  Returns dWi, dWh, db, dx."""
+    H = Wh.shape[1]
+    I, T, B = x.shape
+    dt = x.dtype
+    out, _ = rnn_scan_fwd(Wi, Wh, b, x, sigma, h0)
+    h_init = np.zeros((H, B), dt) if h0 is None else np.broadcast_to(h0.reshape(H, -1), (H, B)).astype(dt)
+    bb = np.zeros((H, 1), dt) if (b is None or b is False) else b.reshape(-1, 1)
+    dWi, dWh, db, dx = np.zeros_like(Wi), np.zeros_like(Wh), np.zeros(H, dt), np.zeros_like(x)
+    dh = np.zeros((H, B), dt) if dhT is None else dhT.copy()
+    for t in range(T - 1, -1, -1):
+        h_prev = h_init if t == 0 else out[:, t - 1, :]
+        z = Wi @ x[:, t, :] + Wh @ h_prev + bb
+        dpre = (dh + dout[:, t, :]) * act_grad(sigma, z)
+        dWi += dpre @ x[:, t, :].T
+        dWh += dpre @ h_prev.T
+        db += dpre.sum(axis=1)
+        dx[:, t, :] = Wi.T @ dpre
+        dh = Wh.T @ dpre
+    if b is None or b is False:
+        db = None
+    return dWi, dWh, db, dx
+
+
+def gruv3_scan_fwd(Wi, Wh, b, Wh_h, x, h0=None, return_cache=False):
+    """Recurrence(GRUv3Cell)(x) (recurrent.jl:795-809): r, z use the first two row blocks of Wi, Wh, b;
+    h~ = tanh(gx3 + Wh_h (r .* h) + b3); the third row block of Wh is not read."""
+    H = Wh.shape[1]
+    I, T, B = x.shape
+    dt = x.dtype
+    h = np.zeros((H, B), dt) if h0 is None else np.broadcast_to(h0.reshape(H, -1), (H, B)).astype(dt)
+    bb = np.zeros((3 * H, 1), dt) if (b is None or b is False) else b.reshape(-1, 1)
+    out = np.empty((H, T, B), dt)
+    cache = []
+    for t in range(T):
+        gx = Wi @ x[:, t, :]
+        gh = Wh @ h
+        r = _sigmoid(gx[0:H] + gh[0:H] + bb[0:H])
+        z = _sigmoid(gx[H:2 * H] + gh[H:2 * H] + bb[H:2 * H])
+        hc = np.tanh(gx[2 * H:] + Wh_h @ (r * h) + bb[2 * H:])
+        h_new = (1 - z) * hc + z * h
+        if return_cache:
+            cache.append((h, r, z, hc))
+        h = h_new
+        out[:, t, :] = h
+    if return_cache:
+        return out, h, cache
+    return out, h
+
+
+def gruv3_scan_bwd(Wi, Wh, b, Wh_h, x, dout, dhT=None):
+    """BPTT through gruv3_scan_fwd with zero initial state.  Returns dWi, dWh, db, dWh_h, dx."""
+    H = Wh.shape[1]
+    I, T, B = x.shape
+    out, _, cache = gruv3_scan_fwd(Wi, Wh, b, Wh_h, x, return_cache=True)
+    dWi, dWh, dWhh = np.zeros_like(Wi), np.zeros_like(Wh), np.zeros_like(Wh_h)
+    db = np.zeros(3 * H, x.dtype)
+    dx = np.zeros_like(x)
+    dh = np.zeros((H, B), x.dtype) if dhT is None else dhT.copy()
+    for t in range(T - 1, -1, -1):
+        h_prev, r, z, hc = cache[t]
+        dh = dh + dout[:, t, :]
+        da3 = dh * (1 - z) * (1 - hc * hc)
+        da2 = dh * (h_prev - hc) * z * (1 - z)
+        drh = Wh_h.T @ da3
+        da1 = drh * h_prev * r * (1 - r)
+        dgx = np.concatenate([da1, da2, da3], axis=0)
+        dWi += dgx @ x[:, t, :].T
+        dWh[0:2 * H] += dgx[0:2 * H] @ h_prev.T
+        dWhh += da3 @ (r * h_prev).T
+        db += dgx.sum(axis=1)
+        dx[:, t, :] = Wi.T @ dgx
+        dh = dh * z + drh * r + Wh[0:2 * H].T @ dgx[0:2 * H]
+    if b is None or b is False:
+        db = None
+    return dWi, dWh, db, dWhh, dx
 
 
 # --------------------------------------------------------------------------

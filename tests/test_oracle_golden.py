@@ -276,3 +276,119 @@ def test_committed_golden_fixture_roundtrip():
     assert set(stored.files) == set(fresh.keys())
     for k in stored.files:
         np.testing.assert_allclose(stored[k], fresh[k], rtol=1e-12, atol=0, err_msg=k)
+
+
+# ---- GroupNorm / InstanceNorm: test/layers/normalisation.jl:236-300, 392-445 --------------------
+def test_groupnorm_frozen_literals():
+    """The reference's frozen outputs for GroupNorm(4, 2) on reshape(1:24, 3, 4, 2), plain and with sigmoid
+    (test/layers/normalisation.jl:410, 431)."""
+    x = np.arange(1, 25, dtype=np.float64).reshape((3, 4, 2), order="F")
+    y = O.groupnorm_fwd(x, np.ones(4), np.zeros(4), 2)
+    ref1 = np.array([[-1.4638476, 0.29276943, -1.4638476, 0.29276943], [-0.87830865, 0.87830853, -0.8783088, 0.8783083],
+                     [-0.29276967, 1.4638474, -0.2927699, 1.4638472]])
+    ref2 = np.array([[-1.4638476, 0.29276943, -1.4638472, 0.29276943], [-0.8783083, 0.8783083, -0.8783083, 0.8783083],
+                     [-0.29276943, 1.4638472, -0.29276943, 1.4638472]])
+    np.testing.assert_allclose(y[:, :, 0], ref1, atol=1e-5)
+    np.testing.assert_allclose(y[:, :, 1], ref2, atol=1e-5)
+    ys = O.groupnorm_fwd(x, np.ones(4), np.zeros(4), 2, sigma="sigmoid")
+    refs = np.array([[0.18787955, 0.57267404, 0.18787955, 0.57267404], [0.2935284, 0.70647156, 0.29352835, 0.70647156],
+                     [0.42732593, 0.81212044, 0.42732587, 0.8121204]])
+    np.testing.assert_allclose(ys[:, :, 0], refs, atol=1e-5)
+    with pytest.raises(ValueError):
+        O.groupnorm_fwd(x, np.ones(4), np.zeros(4), 3)
+
+
+def test_instancenorm_known_answers():
+    """test/layers/normalisation.jl:236-275: running mean [0.5, 0.8], running variance rule with n/(n-1); instance norm
+    equals group norm with one channel per group (:441-445) and batch norm with channel and batch squashed (:348-352)."""
+    x = np.arange(1, 13, dtype=np.float64).reshape((3, 2, 2), order="F")
+    y, mu, var = O.instancenorm_fwd_train(x, np.ones(2), np.zeros(2), np.zeros(2), np.ones(2), 0.1, 1e-5, track_stats=True)
+    np.testing.assert_allclose(mu, [0.5, 0.8])
+    s2 = x.var(axis=0)          # biased variance over the spatial dim, shape (C, N)
+    np.testing.assert_allclose(var, 0.1 * (3 / 2) * s2.mean(axis=1) + 0.9)
+    xin = np.arange(1, 2 * 2 * 3 * 4 * 5 + 1, dtype=np.float64).reshape((2, 2, 3, 4, 5), order="F")
+    a = O.instancenorm_fwd_train(xin, np.ones(4), np.zeros(4), None, None)[0]
+    np.testing.assert_allclose(a, O.groupnorm_fwd(xin, np.ones(4), np.zeros(4), 4), rtol=1e-12)
+    x6 = np.arange(1, 5 * 5 * 3 * 4 * 2 * 6 + 1, dtype=np.float64).reshape((5, 5, 3, 4, 2, 6), order="F")
+    b = O.instancenorm_fwd_train(x6, np.ones(2), np.zeros(2), None, None)[0]
+    xb = x6.reshape((5, 5, 3, 4, 12, 1), order="F")
+    bn = O.batchnorm_fwd_train(xb, np.ones(12), np.zeros(12), None, None, track_stats=False)[0]
+    np.testing.assert_allclose(b, bn.reshape(x6.shape, order="F"), rtol=1e-10, atol=1e-12)
+
+
+@pytest.mark.parametrize("sigma,G", [("identity", 2), ("tanh", 1), ("relu", 4)])
+def test_groupnorm_bwd_fd(sigma, G):
+    rng = np.random.default_rng(1)
+    x, g, b = rng.normal(size=(3, 2, 4, 2)), rng.normal(size=4) + 1.5, rng.normal(size=4)
+    dy = rng.normal(size=x.shape)
+    loss = lambda x_, g_, b_: (O.groupnorm_fwd(x_, g_, b_, G, sigma=sigma) * dy).sum()
+    dx, dg, db = O.groupnorm_bwd(x, g, b, dy, G, sigma=sigma)
+    fd_check(loss, (x, g, b), dx, 0, rtol=1e-4, atol=1e-6)
+    fd_check(loss, (x, g, b), dg, 1, rtol=1e-4, atol=1e-6)
+    fd_check(loss, (x, g, b), db, 2, rtol=1e-4, atol=1e-6)
+
+
+# ---- Embedding: src/layers/basic.jl:752-776 (doctest values) -------------------------------------
+def test_embedding_known_answers_and_gradient():
+    W = np.zeros((4, 26))
+    W[np.arange(4), np.arange(4)] = 22.0          # identity_init(gain = 22)
+    np.testing.assert_array_equal(O.embedding_fwd(W, 2), [0, 22, 0, 0])
+    y = O.embedding_fwd(W, np.array([3, 1, 20, 14, 4, 15, 7]))
+    assert y.shape == (4, 7) and y[2, 0] == 22 and y[0, 1] == 22 and y[3, 4] == 22 and y.sum() == 66
+    assert O.embedding_fwd(W, np.ones((10, 1, 12), int)).shape == (4, 10, 1, 12)
+    rng = np.random.default_rng(0)
+    W = rng.normal(size=(3, 5))
+    idx = np.array([[1, 2, 2], [5, 1, 2]])
+    assert (O.embedding_fwd(W, idx, padding_idx=1)[:, 0, 0] == 0).all()
+    dy = rng.normal(size=(3, 2, 3))
+    dW = O.embedding_bwd(W, idx, dy, padding_idx=1)
+    fd_check(lambda W_: (O.embedding_fwd(W_, idx, padding_idx=1) * dy).sum(), (W,), dW, 0)
+    assert (dW[:, 0] == 0).all() and (dW[:, 2] == 0).all()
+    with pytest.raises(IndexError):
+        O.embedding_fwd(W, np.array([6]))
+
+
+# ---- Dropout mask generator ------------------------------------------------------------------------
+def test_philox_known_answers_and_dropout_statistics():
+    """Philox4x32-10 known-answer vectors of the Random123 distribution (kat_vectors: all-zero and all-ones inputs do
+    not fit this generator's (64-bit counter, 64-bit key) form, so the zero vector and the round structure are pinned;
+    the keep rate is checked statistically like test/layers/normalisation.jl:10-30 does for Dropout)."""
+    out = O.philox4x32_10(np.array([0], dtype=np.uint64), 0)[0]
+    assert [hex(int(v)) for v in out] == ["0x6627e8d5", "0xe169c58d", "0xbc57ac4c", "0x9b00dbd8"]
+    m = O.dropout_mask(100000, 0.3, seed=7)
+    assert abs(m.mean() - 0.7) < 0.01
+    assert (O.dropout_mask(1000, 0.0, 1)).all() and not O.dropout_mask(1000, 1.0, 1).any()
+    # disjoint counter ranges give independent masks; the same (seed, offset) reproduces the mask
+    assert (O.dropout_mask(64, 0.5, 3, offset=16) == O.dropout_mask(128, 0.5, 3)[64:]).all()
+    x = np.ones(10)
+    y = O.dropout_fwd(x, 0.5, O.dropout_mask(10, 0.5, 1))
+    assert set(np.unique(y)) <= {0.0, 2.0}
+
+
+# ---- RNNCell / GRUv3Cell: recurrent.jl:193-198, 795-809 -------------------------------------------
+@pytest.mark.parametrize("sigma", ["tanh", "relu"])
+def test_rnn_bwd_fd(sigma):
+    rng = np.random.default_rng(2)
+    I, H, T, B = 3, 4, 5, 2
+    Wi, Wh, b, x = rng.normal(size=(H, I)) * .5, rng.normal(size=(H, H)) * .5, rng.normal(size=H) * .1, rng.normal(size=(I, T, B))
+    dout = rng.normal(size=(H, T, B))
+    loss = lambda Wi_, Wh_, b_, x_: (O.rnn_scan_fwd(Wi_, Wh_, b_, x_, sigma)[0] * dout).sum()
+    dWi, dWh, db, dx = O.rnn_scan_bwd(Wi, Wh, b, x, dout, sigma)
+    for i, g in enumerate((dWi, dWh, db, dx)):
+        fd_check(loss, (Wi, Wh, b, x), g, i, rtol=1e-4, atol=1e-6)
+    # zero initial state and cell(x) == cell(x, zeros) (test/layers/recurrent.jl:24-40)
+    o1, _ = O.rnn_scan_fwd(Wi, Wh, b, x, sigma)
+    o2, _ = O.rnn_scan_fwd(Wi, Wh, b, x, sigma, h0=np.zeros(H))
+    assert (o1 == o2).all()
+
+
+def test_gruv3_bwd_fd():
+    rng = np.random.default_rng(3)
+    I, H, T, B = 3, 4, 5, 2
+    Wi, Wh, b = rng.normal(size=(3 * H, I)) * .5, rng.normal(size=(3 * H, H)) * .5, rng.normal(size=3 * H) * .1
+    Whh, x, dout = rng.normal(size=(H, H)) * .5, rng.normal(size=(I, T, B)), rng.normal(size=(H, T, B))
+    loss = lambda Wi_, Wh_, b_, Whh_, x_: (O.gruv3_scan_fwd(Wi_, Wh_, b_, Whh_, x_)[0] * dout).sum()
+    grads = O.gruv3_scan_bwd(Wi, Wh, b, Whh, x, dout)
+    for i, g in enumerate(grads):
+        fd_check(loss, (Wi, Wh, b, Whh, x), g, i, rtol=1e-4, atol=1e-6)
+    assert (grads[1][2 * H:] == 0).all()      # the third row block of Wh is never read (recurrent.jl:804)
