@@ -177,6 +177,20 @@ struct fb_gemm_args {
   int act;
   int accumulate;
 };
+// bf16 operands (raw uint16 bit patterns), fp32 accumulation; C is bf16 (or fp32 when out_f32), Z / bias_n are bf16
+struct fb_gemm_bf16_args {
+  const uint16_t* A; int64_t lda; int a_mn_major;
+  const uint16_t* B; int64_t ldb; int b_mn_major;
+  void* C; int64_t ldc;
+  uint16_t* Z;
+  const uint16_t* bias_n;
+  int64_t M, N, K;
+  int act;
+  int accumulate;
+  int out_f32;
+};
+int32_t fb_gemm_bf16_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_bf16_args& a);
+bool fb_gemm_bf16_supported(const fb_gemm_bf16_args& a);
 int32_t fb_gemm_simt_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a);
 // tensor-core path; returns FB_ERR_UNSUPPORTED (without raising an error message) when the shape or
 // alignment is outside what the kernel handles, so the dispatcher can pick the FMA kernel.

@@ -58,6 +58,9 @@ PROTOTYPES = {
     "fb_gemm_f32": (_i32, [_p, _p, _i32, _i32, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i64, _i32, _i32]),
     "fb_dense_fwd": (_i32, [_p, _p, _i32, _i32, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_dense_bwd": (_i32, [_p, _p, _i32, _i32, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
+    "fb_gemm_bf16": (_i32, [_p, _p, _i32, _i32, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i64, _i32, _i32]),
+    "fb_dense_fwd_bf16": (_i32, [_p, _p, _i32, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
+    "fb_dense_bwd_bf16": (_i32, [_p, _p, _i32, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_layernorm_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i32]),
     "fb_layernorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32]),
     "fb_layernorm_bwd_noalloc": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32]),

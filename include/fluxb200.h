@@ -133,6 +133,20 @@ int32_t fb_dense_bwd(fb_ctx* ctx, void* stream, int32_t act, int32_t precision, 
                      const float* x, const float* y, const float* z, const float* dy, float* delta,
                      float* dW, float* db, float* dx, int64_t out_dim, int64_t in_dim, int64_t n);
 
+/* The same three calls for BFloat16 storage (raw bf16 bit patterns in uint16), the opt-in low-precision path of
+ * Flux.bf16 / Flux._to_bf16 (src/functor.jl:137-183, 274): operands, bias, outputs and gradients are bf16, products
+ * are accumulated in Float32 on the tensor cores (tcgen05.mma.kind::f16).  Pointers must be 16-byte aligned and
+ * leading dimensions multiples of 8 (FB_ERR_UNSUPPORTED otherwise).  fb_gemm_bf16 writes C as Float32 when
+ * c_is_f32 != 0. */
+int32_t fb_gemm_bf16(fb_ctx* ctx, void* stream, int32_t transa, int32_t transb, int64_t m, int64_t n, int64_t k,
+                     const uint16_t* A, int64_t lda, const uint16_t* B, int64_t ldb, void* C, int64_t ldc,
+                     int32_t accumulate, int32_t c_is_f32);
+int32_t fb_dense_fwd_bf16(fb_ctx* ctx, void* stream, int32_t act, const uint16_t* W, const uint16_t* b,
+                          const uint16_t* x, uint16_t* y, uint16_t* z, int64_t out_dim, int64_t in_dim, int64_t n);
+int32_t fb_dense_bwd_bf16(fb_ctx* ctx, void* stream, int32_t act, const uint16_t* W, const uint16_t* x,
+                          const uint16_t* y, const uint16_t* z, const uint16_t* dy, uint16_t* delta, uint16_t* dW,
+                          uint16_t* db, uint16_t* dx, int64_t out_dim, int64_t in_dim, int64_t n);
+
 /* ---------------------------------------------------------------------------- LayerNorm -- */
 
 /* y[d,n] = act.(gamma .* (x - mean) * rstd .+ beta), statistics over the first (flattened) d
