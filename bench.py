@@ -645,6 +645,7 @@ MHA_DTYPES = ("f32", "bf16")
 CASES = """gemm_fwd    Dense 4096=>4096 forward at --batch (3xTF32 tcgen05 GEMM, K-major x MN-major)
 gemm_dw     the dW GEMM of the same layer (MN-major x MN-major, K = batch)
 gemm_dx     the dX GEMM of the same layer (K-major x K-major)
+gemm_bf16_fwd / gemm_bf16_dw / gemm_bf16_dx   the same three products with BFloat16 storage (tcgen05 kind::f16)
 layernorm   LayerNorm(4096) forward + backward on 4096 x 8192
 batchnorm   BatchNorm(256, relu) training forward + backward on 32 x 32 x 256 x 128
 adam        Adam step over 32 Mi parameters in 4 leaves
@@ -681,6 +682,19 @@ def run_case(args):
             fn = lambda: call("fb_gemm_f32", 0, 1, d, d, n, P(dy), d, P(x), d, P(dW), d, 0, 0)       # dW = dy * x'
         else:
             fn = lambda: call("fb_gemm_f32", 1, 0, d, n, d, P(W), d, P(dy), d, P(dx), d, 0, 0)       # dx = W' * dy
+        work = (2.0 * n * d * d, "TFLOP/s")
+    elif case in ("gemm_bf16_fwd", "gemm_bf16_dw", "gemm_bf16_dx"):
+        n, d = args.batch, 4096
+        bfr = lambda k: rn(k).to(torch.bfloat16)
+        W, x, dy, b = bfr(d * d) * 0.02, bfr(n * d), bfr(n * d), bfr(d)
+        eb = lambda k: torch.empty(k, dtype=torch.bfloat16, device="cuda")
+        y, dW, dx = eb(n * d), eb(d * d), eb(n * d)
+        if case == "gemm_bf16_fwd":
+            fn = lambda: call("fb_dense_fwd_bf16", 4, P(W), P(b), P(x), P(y), None, d, d, n)
+        elif case == "gemm_bf16_dw":
+            fn = lambda: call("fb_gemm_bf16", 0, 1, d, d, n, P(dy), d, P(x), d, P(dW), d, 0, 0)
+        else:
+            fn = lambda: call("fb_gemm_bf16", 1, 0, d, n, d, P(W), d, P(dy), d, P(dx), d, 0, 0)
         work = (2.0 * n * d * d, "TFLOP/s")
     elif case == "layernorm":
         d, n = 4096, 8192

@@ -286,6 +286,7 @@ class GradBuckets:
         self.pflat = self.mflat = self.vflat = None
         self.adam = None
         self.armed = False
+        self.peer = None             # peer-memory tables of the copy-based exchange (see _setup_peer_exchange)
         self.loss = None
         self.guard = None            # device scalar the update kernels test for finiteness (see set_loss)
         self._guard_buf = None
@@ -395,7 +396,9 @@ class GradBuckets:
         if n == 1 or not isinstance(rule, Adam) or any((b[1] - b[0]) % n for b in self.buckets):
             return False
         if self.pflat is None:
-            self.pflat, self.mflat, self.vflat = (torch.zeros_like(self.flat) for _ in range(3))
+            self.mflat, self.vflat = (torch.zeros_like(self.flat) for _ in range(2))
+            # parameters live in memory the peers can write when the copy-based exchange is available
+            self.pflat = self._setup_peer_exchange() or torch.zeros_like(self.flat)
             for p in self.params:
                 off, cnt = self.offsets[id(p)], p.numel()
                 st = opt_state.leaves[id(p)].state
@@ -405,6 +408,69 @@ class GradBuckets:
                     arr.t = view
         self.adam = (rule, bt)
         return True
+
+    def _setup_peer_exchange(self):
+        """Maps, on every rank, a staging area and the parameter buffer of every other rank (CUDA IPC), so that the
+        reduce-scatter and the all-gather of the sharded step can run as device-to-device copies on the copy engines
+        (no SM is taken from the reverse sweep's GEMMs).  Returns this rank's parameter buffer as a tensor, or None
+        when any rank cannot map its peers (or FLUXB200_EXCHANGE=nccl): then the NCCL collectives are used."""
+        import torch.distributed as dist
+        be = self.backend
+        self.peer = None
+        want = os.environ.get("FLUXB200_EXCHANGE", "peer") == "peer" and be.size <= 16 and dist.is_initialized()
+        ctx = context()
+        nbytes = 4 * self.flat.numel()
+        HB = 64
+        mine, ptrs = [0] * (1 + 2 * HB), []
+        if want:
+            try:
+                for k in range(2):          # staging area, parameter buffer
+                    ptr, h = C.c_void_p(), (C.c_uint8 * HB)()
+                    lib.call("fb_peer_alloc", ctx.handle, nbytes, C.byref(ptr), h)
+                    ptrs.append(ptr.value)
+                    mine[1 + k * HB:1 + (k + 1) * HB] = list(bytes(h))
+                mine[0] = 1
+            except lib.FluxB200Error:
+                mine[0] = 0
+        gathered = [torch.zeros(1 + 2 * HB, dtype=torch.uint8) for _ in range(be.size)]
+        dist.all_gather(gathered, torch.tensor(mine, dtype=torch.uint8))
+        ok = all(int(g[0]) == 1 for g in gathered)
+        stage, pbuf = [None] * be.size, [None] * be.size
+        if ok:
+            try:
+                for r, g in enumerate(gathered):
+                    if r == be.rank:
+                        stage[r], pbuf[r] = ptrs
+                        continue
+                    for k, table in ((0, stage), (1, pbuf)):
+                        h = (C.c_uint8 * HB)(*g[1 + k * HB:1 + (k + 1) * HB].tolist())
+                        ptr = C.c_void_p()
+                        lib.call("fb_peer_open", ctx.handle, h, C.byref(ptr))
+                        table[r] = ptr.value
+            except lib.FluxB200Error:
+                ok = False
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) != 1:
+            for ptr in ptrs:
+                lib.call("fb_peer_free", ctx.handle, C.c_void_p(ptr))
+            return None
+
+        class _Raw:   # a device buffer owned by the library, seen by torch without a copy
+            def __init__(self, ptr, count):
+                self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3, "strides": None}
+
+        raw = _Raw(pbuf[be.rank], self.flat.numel())
+        ptensor = torch.as_tensor(raw, device=self.flat.device)
+        self.peer = {"stage": stage, "pflat": pbuf, "keep": raw,
+                     "token": torch.zeros(1, dtype=torch.float32, device=self.flat.device), "done": torch.cuda.Event()}
+        return ptensor
+
+    def _peer_barrier(self, cs):
+        """A one-element all-reduce on the communication stream: when it completes on this rank, the copies every
+        rank enqueued before it have reached their destinations."""
+        tok = C.c_void_p(self.peer["token"].data_ptr())
+        lib.call("fb_allreduce", self.backend.comm, cs, tok, tok, 1, lib.OP["+"])
 
     def set_loss(self, loss):
         """The step's loss (device scalar): the captured update kernels skip themselves when it is not finite.  With
@@ -442,12 +508,32 @@ class GradBuckets:
         if self.armed and self.adam is not None and self.loss is not None:
             from .core import context
             rule, bt = self.adam
-            blk = (end - start) // be.size
+            n = be.size
+            blk = (end - start) // n
             lo = 4 * (start + be.rank * blk)
             g, pp = self.flat.data_ptr() + lo, self.pflat.data_ptr() + lo
+            one = C.c_void_p * 1
+            peer = getattr(self, "peer", None)
+            if peer is not None:
+                # copy-based reduce-scatter: my block p goes to slot [me] of peer p's staging area; after the barrier
+                # the N slots of my block are summed in rank order (my own slot is read where it was produced)
+                h = context().handle
+                tab = C.c_void_p * n
+                lib.call("fb_peer_scatter_blocks", h, cs, ptr, tab(*[peer["stage"][r] + 4 * start for r in range(n)]), n, be.rank, blk)
+                self._peer_barrier(cs)
+                slots = tab(*[(peer["stage"][be.rank] + 4 * (start + r * blk)) if r != be.rank else g for r in range(n)])
+                lib.call("fb_reduce_slots", h, cs, n, slots, C.c_void_p(g), blk, 1.0 / n)
+                self._mark(f"bucket {bi} reduce-scatter end", be.stream)
+                lib.call("fb_adam_step_dev", h, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
+                         one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
+                         rule.epsilon, C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
+                self._mark(f"bucket {bi} adam end", be.stream)
+                lib.call("fb_peer_gather_block", h, cs, C.c_void_p(pp), tab(*[peer["pflat"][r] + lo for r in range(n)]), n, be.rank, blk)
+                self._mark(f"bucket {bi} comm end", be.stream)
+                self.events[bi].record(be.stream)
+                return
             lib.call("fb_reduce_scatter", be.comm, cs, ptr, C.c_void_p(g), blk, lib.OP["avg"])
             self._mark(f"bucket {bi} reduce-scatter end", be.stream)
-            one = C.c_void_p * 1
             lib.call("fb_adam_step_dev", context().handle, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
                      one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
                      rule.epsilon, C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
@@ -465,6 +551,10 @@ class GradBuckets:
                 self._launch(bi)
         self._mark("backward end")
         if self.backend.size > 1:
+            if self.armed and getattr(self, "peer", None) is not None:
+                # the peers' parameter blocks must have landed here before anybody reads the parameters again
+                self._peer_barrier(C.c_void_p(self.backend.stream.cuda_stream))
+                self.events[-1].record(self.backend.stream)
             for ev in self.events:
                 torch.cuda.current_stream().wait_event(ev)
             if self.guard_event is not None:
