@@ -52,7 +52,24 @@ __global__ void __launch_bounds__(256) colsum_parts_bf16_kernel(const float* __r
   out[c] = f2bf(s);
 }
 
+__global__ void __launch_bounds__(256) axpy_bf16_kernel(float alpha, const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int64_t count) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < count; i += (int64_t)gridDim.x * 256)
+    y[i] = f2bf(fmaf(alpha, bf2f(x[i]), bf2f(y[i])));
+}
+
 }  // namespace
+
+FB_API int32_t fb_axpy_bf16(fb_ctx* ctx, void* stream, float alpha, const uint16_t* x, uint16_t* y, int64_t count) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(count >= 0, FB_ERR_INVALID_ARG, "fb_axpy_bf16: negative count");
+  if (count == 0) return FB_OK;
+  FB_REQUIRE(x && y, FB_ERR_INVALID_ARG, "fb_axpy_bf16: NULL pointer");
+  int64_t blocks = (count + 255) / 256;
+  if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+  axpy_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(alpha, x, y, count);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}
 
 FB_API int32_t fb_gemm_bf16(fb_ctx* ctx, void* stream, int32_t transa, int32_t transb, int64_t m, int64_t n, int64_t k,
                             const uint16_t* A, int64_t lda, const uint16_t* B, int64_t ldb, void* C, int64_t ldc,

@@ -137,9 +137,12 @@ def gpu(x):
 
 
 def cpu(x):
-    """Copies back to a Julia-shaped numpy array (functor.jl:116)."""
+    """Copies back to a Julia-shaped numpy array (functor.jl:116); BFloat16 storage comes back as Float32 values."""
     if isinstance(x, B200Array):
-        return x.t.detach().cpu().numpy().reshape(x.size, order="F")
+        t = x.t.detach()
+        if t.dtype == torch.bfloat16:
+            t = t.float()
+        return t.cpu().numpy().reshape(x.size, order="F")
     if isinstance(x, (tuple, list)):
         return type(x)(cpu(v) for v in x)
     if isinstance(x, dict):
@@ -147,6 +150,35 @@ def cpu(x):
     if hasattr(x, "_fmap"):
         return x._fmap(cpu)
     return x
+
+
+def is_bf16(a) -> bool:
+    return isinstance(a, B200Array) and a.t.dtype == torch.bfloat16
+
+
+def to_bf16(a: B200Array) -> B200Array:
+    """Float32 -> BFloat16 storage (round to nearest even, bit-exact with Flux._to_bf16, src/functor.jl:161-166).
+    Under `withgradient` the cast is recorded: the cotangent comes back in the input's element type."""
+    if a is None or a.t.dtype == torch.bfloat16:
+        return a
+    ctx = context()
+    out = empty(a.size, torch.bfloat16)
+    lib.call("fb_cast_f32_bf16", ctx.handle, ctx.stream, a.ptr, out.ptr, a.numel())
+    if Tape.needs(a):
+        Tape.record(out, [a], lambda gs, src=a: [(src, to_f32(gs[0]))])
+    return out
+
+
+def to_f32(a: B200Array) -> B200Array:
+    """BFloat16 -> Float32 storage (exact)."""
+    if a is None or a.t.dtype != torch.bfloat16:
+        return a
+    ctx = context()
+    out = empty(a.size)
+    lib.call("fb_cast_bf16_f32", ctx.handle, ctx.stream, a.ptr, out.ptr, a.numel())
+    if Tape.needs(a):
+        Tape.record(out, [a], lambda gs, src=a: [(src, to_bf16(gs[0]))])
+    return out
 
 
 # ------------------------------------------------------------------------------------- tape ---
@@ -190,6 +222,10 @@ def accumulate(grads: dict, keep: dict, arr: B200Array, g: B200Array):
     if k in grads:
         if grads[k].t.data_ptr() != g.t.data_ptr():
             ctx = context()
-            lib.call("fb_axpy", ctx.handle, ctx.stream, 1.0, g.ptr, grads[k].ptr, g.numel())
+            if grads[k].t.dtype == torch.bfloat16:
+                g = to_bf16(g)
+                lib.call("fb_axpy_bf16", ctx.handle, ctx.stream, 1.0, g.ptr, grads[k].ptr, g.numel())
+            else:
+                lib.call("fb_axpy", ctx.handle, ctx.stream, 1.0, to_f32(g).ptr, grads[k].ptr, g.numel())
     else:
         grads[k] = g

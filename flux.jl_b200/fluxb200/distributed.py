@@ -398,7 +398,9 @@ class GradBuckets:
         if self.pflat is None:
             self.mflat, self.vflat = (torch.zeros_like(self.flat) for _ in range(2))
             # parameters live in memory the peers can write when the copy-based exchange is available
-            self.pflat = self._setup_peer_exchange() or torch.zeros_like(self.flat)
+            self.pflat = self._setup_peer_exchange()
+            if self.pflat is None:
+                self.pflat = torch.zeros_like(self.flat)
             for p in self.params:
                 off, cnt = self.offsets[id(p)], p.numel()
                 st = opt_state.leaves[id(p)].state

@@ -12,7 +12,7 @@ import numpy as np
 import torch
 
 from . import lib
-from .core import B200Array, Tape, context, empty, gpu, zeros
+from .core import B200Array, Tape, context, empty, gpu, is_bf16, to_bf16, to_f32, zeros
 from .init import glorot_uniform
 
 
@@ -107,32 +107,40 @@ def _round_bf16(a: B200Array) -> B200Array:
 
 
 def bf16(m):
-    """Flux.bf16 (src/functor.jl:274, 137-183): the opt-in low-precision path.  For a model: every trainable array is
-    rounded to its BFloat16 value (kept in Float32 storage) and its Dense layers switch to the bf16 GEMM path
-    (single TF32 pass: exact products of bf16 values, Float32 accumulation, outputs and gradients rounded to bf16).
-    BatchNorm statistics and affine parameters stay Float32 (normalise.jl:513-519).  For an array: a rounded copy."""
+    """Flux.bf16 (src/functor.jl:274, 137-183): the opt-in low-precision path.  For an array: BFloat16 storage (2 bytes
+    per element, round to nearest even).  For a model: the weights and biases of its Dense layers move to BFloat16
+    storage and those layers run on the bf16 tensor-core GEMM (Float32 accumulation, BFloat16 activations and
+    gradients); the parameters of the other layers are rounded to BFloat16 values and keep Float32 storage, since
+    their kernels compute in Float32 (as the reference keeps normalisation statistics in Float32,
+    normalise.jl:513-519).  Arrays that cross between the two are converted on the way."""
     if isinstance(m, B200Array):
-        out = empty(m.size)
-        ctx = context()
-        lib.call("fb_round_bf16", ctx.handle, ctx.stream, m.ptr, out.ptr, m.numel())
-        return out
+        return to_bf16(m)
     for layer in _walk(m):
         if isinstance(layer, BatchNorm):
             continue
         if isinstance(layer, Dense):
             layer.precision = "bf16"
+            layer.weight = to_bf16(layer.weight)
+            if layer.bias is not False:
+                layer.bias = to_bf16(layer.bias)
+            continue
         for name in layer.trainable_fields():
             v = getattr(layer, name, None)
-            if isinstance(v, B200Array):
+            if isinstance(v, B200Array) and v.t.dtype == torch.float32:
                 _round_bf16(v)
     return m
 
 
 def f32(m):
-    """Flux.f32: back to the Float32 path (values are already Float32 storage; only the GEMM path changes)."""
+    """Flux.f32 (src/functor.jl:137-148): back to Float32 storage and the Float32 kernels."""
+    if isinstance(m, B200Array):
+        return to_f32(m)
     for layer in _walk(m):
         if isinstance(layer, Dense) and layer.precision == "bf16":
             layer.precision = "default"
+            layer.weight = to_f32(layer.weight)
+            if layer.bias is not False:
+                layer.bias = to_f32(layer.bias)
     return m
 
 
@@ -178,6 +186,9 @@ class Dense(Layer):
         _size_check(self, x, 1, in_dim)
         n = x.numel() // in_dim
         ctx = context()
+        if is_bf16(self.weight):
+            return self._call_bf16(to_bf16(x), out_dim, in_dim, n)
+        x = to_f32(x)
         act, prec = lib.ACT[self.σ], lib.PREC[self.precision]
         b = self.bias if self.bias is not False else None
         recording = Tape.active
@@ -185,9 +196,6 @@ class Dense(Layer):
         z = empty(y.size) if (recording and self.σ in ("gelu", "gelu_tanh", "gelu_erf")) else None
         lib.call("fb_dense_fwd", ctx.handle, ctx.stream, act, prec, self.weight.ptr, _ptr(b), x.ptr, y.ptr, _ptr(z),
                  out_dim, in_dim, n)
-        lowp = self.precision == "bf16"
-        if lowp:
-            _round_bf16(y)
         if recording:
             W = self.weight
 
@@ -201,10 +209,6 @@ class Dense(Layer):
                 delta = empty(y.size) if act != 0 else None
                 lib.call("fb_dense_bwd", ctx.handle, ctx.stream, act, prec, W.ptr, x.ptr, y.ptr, _ptr(z), dy.ptr,
                          _ptr(delta), dW.ptr, _ptr(db), _ptr(dx), out_dim, in_dim, n)
-                if lowp:   # a bf16 model's gradients are bf16 values too
-                    for g in (dW, db, dx):
-                        if g is not None:
-                            _round_bf16(g)
                 res = [(W, dW)]
                 if b is not None:
                     res.append((b, db))
@@ -214,6 +218,42 @@ class Dense(Layer):
 
             Tape.record(y, [x, W, b], pullback)
         return y
+
+
+def _dense_call_bf16(self, x, out_dim, in_dim, n):
+    """The Dense call for BFloat16 storage: one fused tensor-core GEMM (bias, activation, pre-activation) forward,
+    fb_dense_bwd_bf16 in the pullback; every array involved is bf16."""
+    ctx = context()
+    act = lib.ACT[self.σ]
+    W = self.weight
+    b = self.bias if self.bias is not False else None
+    recording = Tape.active
+    bf = torch.bfloat16
+    y = empty((out_dim,) + x.size[1:], bf)
+    z = empty(y.size, bf) if (recording and self.σ in ("gelu", "gelu_tanh", "gelu_erf")) else None
+    lib.call("fb_dense_fwd_bf16", ctx.handle, ctx.stream, act, W.ptr, _ptr(b), x.ptr, y.ptr, _ptr(z), out_dim, in_dim, n)
+    if recording:
+        def pullback(gs, x=x, y=y, z=z):
+            dy = to_bf16(gs[0])
+            need_dx = Tape.needs(x)
+            dW = empty(W.size, bf)
+            db = empty(b.size, bf) if b is not None else None
+            dx = empty(x.size, bf) if need_dx else None
+            delta = empty(y.size, bf) if act != 0 else None
+            lib.call("fb_dense_bwd_bf16", ctx.handle, ctx.stream, act, W.ptr, x.ptr, y.ptr, _ptr(z), dy.ptr, _ptr(delta), dW.ptr,
+                     _ptr(db), _ptr(dx), out_dim, in_dim, n)
+            res = [(W, dW)]
+            if b is not None:
+                res.append((b, db))
+            if need_dx:
+                res.append((x, dx))
+            return res
+
+        Tape.record(y, [x, W, b], pullback)
+    return y
+
+
+Dense._call_bf16 = _dense_call_bf16
 
 
 # -------------------------------------------------------------------------------- LayerNorm ---
@@ -245,6 +285,7 @@ class LayerNorm(Layer):
         return f"LayerNorm({', '.join(map(str, self.size))})"
 
     def __call__(self, x: B200Array) -> B200Array:
+        x = to_f32(x)
         if self.affine:
             for d, s in enumerate(self.size):
                 _size_check(self, x, d + 1, s)
@@ -303,6 +344,7 @@ class BatchNorm(Layer):
         return Tape.active if self.active is None else bool(self.active)
 
     def __call__(self, x: B200Array) -> B200Array:
+        x = to_f32(x)
         N = x.ndim
         if N < 2:
             raise DimensionMismatch(f"layer {self} expects ndims(input) >= 2, but got {x}")
@@ -446,6 +488,7 @@ class Recurrence(Layer):
 
     def __call__(self, x: B200Array, state=None):
         cell = self.cell
+        x = to_f32(x)
         if not isinstance(cell, (LSTMCell, GRUCell)):
             return _scan_family(self, x, state)
         in_dim = cell.Wi.size[1]
@@ -558,6 +601,8 @@ def dot_product_attention(q: B200Array, k: B200Array, v: B200Array, bias=None, n
     """NNlib.dot_product_attention(q, k, v, bias; nheads, mask) -> (x, alpha) for 3-d B200 arrays."""
     if bias is not None:
         raise lib.FluxB200Error(-7, "additive attention bias has no B200 kernel; pass a boolean mask instead")
+    low = is_bf16(q)
+    q, k, v = to_f32(q), to_f32(k), to_f32(v)
     E, Lq, B = q.size
     Ev, Lk, _ = v.size
     if k.size != (E, Lk, B):
@@ -583,7 +628,8 @@ def dot_product_attention(q: B200Array, k: B200Array, v: B200Array, bias=None, n
             return [(q, dq), (k, dk), (v, dv)]
 
         Tape.record(o, [q, k, v], pullback)
-    return o, AttnScores(q, k, lse, m, causal, nheads, (Lk, Lq, nheads, B))
+    scores = AttnScores(q, k, lse, m, causal, nheads, (Lk, Lq, nheads, B))
+    return (to_bf16(o) if low else o), scores
 
 
 class MultiHeadAttention(Layer):

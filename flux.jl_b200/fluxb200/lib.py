@@ -59,6 +59,7 @@ PROTOTYPES = {
     "fb_dense_fwd": (_i32, [_p, _p, _i32, _i32, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_dense_bwd": (_i32, [_p, _p, _i32, _i32, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_gemm_bf16": (_i32, [_p, _p, _i32, _i32, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i64, _i32, _i32]),
+    "fb_axpy_bf16": (_i32, [_p, _p, _f, _p, _p, _i64]),
     "fb_dense_fwd_bf16": (_i32, [_p, _p, _i32, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_dense_bwd_bf16": (_i32, [_p, _p, _i32, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64]),
     "fb_layernorm_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i32]),

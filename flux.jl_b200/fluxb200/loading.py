@@ -140,7 +140,10 @@ def load_opt_state(opt, saved: dict):
     if len(params) != len(saved["leaves"]):
         raise ArgumentError(f"optimiser state has {len(saved['leaves'])} leaves, the model has {len(params)} trainable arrays")
     for p, s in zip(params, saved["leaves"]):
-        st = opt.leaves[id(p)].state
+        leaf = opt.leaves[id(p)]
+        if leaf.master is not None:      # BFloat16 parameter: the Float32 master copy restarts from the loaded value
+            leaf.master.t.copy_(p.t.float())
+        st = leaf.state
         if (st is None) != (s is None):
             raise ArgumentError("optimiser state structure mismatch")
         if s is None:

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from . import lib
-from .core import B200Array, Tape, accumulate, context, empty, gpu, zeros
+from .core import B200Array, Tape, accumulate, context, empty, gpu, to_bf16, to_f32, zeros
 from .layers import DimensionMismatch, Layer, trainables
 
 
@@ -30,6 +30,7 @@ def logitcrossentropy(yhat: B200Array, y, dims=1, agg="mean") -> B200Array:
     what `onehotbatch(labels, 1:C)` stands for)."""
     if dims != 1 or agg != "mean":
         raise lib.FluxB200Error(-7, "logitcrossentropy on B200 arrays supports dims=1, agg=mean")
+    yhat = to_f32(yhat)
     c = yhat.size[0]
     n = yhat.numel() // c
     ctx = context()
@@ -74,6 +75,7 @@ def onehotbatch(labels, nclasses):
 
 def sum_abs2(y: B200Array) -> B200Array:
     """sum(abs2, y); its pullback is the cotangent 2y."""
+    y = to_f32(y)
     ctx = context()
     out = empty(())
     lib.call("fb_sumsq", ctx.handle, ctx.stream, y.ptr, y.numel(), out.ptr)
@@ -91,6 +93,7 @@ def sum_abs2(y: B200Array) -> B200Array:
 
 def sum_all(y: B200Array) -> B200Array:
     """sum(y); its pullback fills the cotangent."""
+    y = to_f32(y)
     ctx = context()
     out = empty(())
     lib.call("fb_sum", ctx.handle, ctx.stream, y.ptr, y.numel(), out.ptr)
@@ -242,6 +245,9 @@ class Leaf:
 
     def __init__(self, rule, param: B200Array):
         self.rule = rule
+        # a BFloat16 parameter is updated through a Float32 master copy (the step eta * m / sqrt(v) is usually below
+        # half a bf16 ulp of the weight, so updating the bf16 value directly would lose it)
+        self.master = to_f32(param) if param.t.dtype == torch.bfloat16 else None
         if isinstance(rule, Adam):
             self.state = [zeros(param.size), zeros(param.size), (rule.beta[0], rule.beta[1])]
         else:
@@ -305,9 +311,15 @@ def update(opt_state: OptState, model, grad_tree):
     ps = [p for p in ps if not (id(p) in seen or seen.add(id(p)))]
     if not ps:
         return opt_state, model
+    # BFloat16 parameters: the rule runs on the Float32 master copy with the gradient widened to Float32; the
+    # parameter is the master rounded back
+    low = [p for p in ps if opt_state.leaves[id(p)].master is not None]
+    wmap = {id(p): (opt_state.leaves[id(p)].master if opt_state.leaves[id(p)].master is not None else p) for p in ps}
+    gmap = {k: to_f32(g) for k, g in gmap.items()}
     if isinstance(rule, Descent):
         for p in ps:
-            lib.call("fb_axpy", ctx.handle, ctx.stream, -rule.eta, gmap[id(p)].ptr, p.ptr, p.numel())
+            lib.call("fb_axpy", ctx.handle, ctx.stream, -rule.eta, gmap[id(p)].ptr, wmap[id(p)].ptr, p.numel())
+        _write_back(low, wmap)
         return opt_state, model
     # leaves share (β1ᵗ, β2ᵗ) when they have seen the same number of steps: group by that pair
     groups: dict = {}
@@ -316,7 +328,7 @@ def update(opt_state: OptState, model, grad_tree):
     for (b1t, b2t), plist in groups.items():
         k = len(plist)
         arr_t = C.c_void_p * k
-        w = arr_t(*[p.t.data_ptr() for p in plist])
+        w = arr_t(*[wmap[id(p)].t.data_ptr() for p in plist])
         g = arr_t(*[gmap[id(p)].t.data_ptr() for p in plist])
         m = arr_t(*[opt_state.leaves[id(p)].state[0].t.data_ptr() for p in plist])
         v = arr_t(*[opt_state.leaves[id(p)].state[1].t.data_ptr() for p in plist])
@@ -327,7 +339,14 @@ def update(opt_state: OptState, model, grad_tree):
         nb = (float(f32(b1t) * f32(rule.beta[0])), float(f32(b2t) * f32(rule.beta[1])))
         for p in plist:
             opt_state.leaves[id(p)].state[2] = nb
+    _write_back(low, wmap)
     return opt_state, model
+
+
+def _write_back(low, wmap):
+    ctx = context()
+    for p in low:
+        lib.call("fb_cast_f32_bf16", ctx.handle, ctx.stream, wmap[id(p)].ptr, p.ptr, p.numel())
 
 
 def trainstep(loss, model, batch, opt_state):
@@ -436,6 +455,8 @@ class GraphedTrainStep:
         rule = opt_state.rule
         if not isinstance(rule, Adam):
             raise lib.FluxB200Error(-7, "GraphedTrainStep supports the Adam rule")
+        if any(leaf.master is not None for leaf in opt_state.leaves.values()):
+            raise lib.FluxB200Error(-7, "GraphedTrainStep supports Float32 parameters; use trainstep for a bf16 model")
         self.model, self.opt_state, self.sink = model, opt_state, grad_sink
         self.static = tuple(_clone_static(b) for b in example_batch)
         self._stage = self._copy_stream = self._staged_ev = self._consumed_ev = None

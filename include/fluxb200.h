@@ -141,6 +141,8 @@ int32_t fb_dense_bwd(fb_ctx* ctx, void* stream, int32_t act, int32_t precision, 
 int32_t fb_gemm_bf16(fb_ctx* ctx, void* stream, int32_t transa, int32_t transb, int64_t m, int64_t n, int64_t k,
                      const uint16_t* A, int64_t lda, const uint16_t* B, int64_t ldb, void* C, int64_t ldc,
                      int32_t accumulate, int32_t c_is_f32);
+/* y += alpha * x on bf16 arrays (tangent accumulation of a bf16 model; one rounding per element). */
+int32_t fb_axpy_bf16(fb_ctx* ctx, void* stream, float alpha, const uint16_t* x, uint16_t* y, int64_t count);
 int32_t fb_dense_fwd_bf16(fb_ctx* ctx, void* stream, int32_t act, const uint16_t* W, const uint16_t* b,
                           const uint16_t* x, uint16_t* y, uint16_t* z, int64_t out_dim, int64_t in_dim, int64_t n);
 int32_t fb_dense_bwd_bf16(fb_ctx* ctx, void* stream, int32_t act, const uint16_t* W, const uint16_t* x,
