@@ -9,7 +9,10 @@ module B200Arrays
 using Adapt, Libdl
 import MLDataDevices
 
-export B200Array, B200Device, B200Matrix, B200VecOrMat, fbcall, fbctx, fbstream
+export B200Array, B200Device, B200Matrix, B200VecOrMat, BFloat16Bits, fbcall, fbctx, fbstream
+
+"The raw 16-bit pattern of a BFloat16 value: the element type of arrays in BFloat16 storage (Flux.bf16)."
+primitive type BFloat16Bits 16 end
 
 const libfluxb200 = Ref{Ptr{Cvoid}}(C_NULL)
 const ctx = Ref{Ptr{Cvoid}}(C_NULL)
@@ -81,6 +84,17 @@ end
 Base.fill!(a::B200Array{Float32}, v) =
     (check(ccall(sym(:fb_fill), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Float32, Int64), fbctx(), fbstream(), a.ptr, Float32(v), length(a))); a)
 Base.zero(a::B200Array{Float32}) = fill!(similar(a), 0)
+"zeros(Float32, dims...) on the device."
+function zeros(::Type{T}, dims::Integer...) where {T}
+    a = B200Array{T,length(dims)}(undef, Int.(dims))
+    check(ccall(sym(:fb_memset), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int32, Int64), fbctx(), fbstream(), a.ptr, Int32(0), sizeof(T) * length(a)))
+    return a
+end
+"A view of `count = prod(dims)` elements of the flat array `a` starting at element offset `off` (0-based), shaped `dims`."
+function view1d(a::B200Array{T,1}, off::Integer, dims::Dims{N}) where {T,N}
+    (0 <= off && off + prod(dims) <= length(a)) || throw(BoundsError(a, off + prod(dims)))
+    return B200Array{T,N}(a.ptr + off * sizeof(T), dims, a)
+end
 Base.copy(a::B200Array{T,N}) where {T,N} = (b = similar(a);
     check(ccall(sym(:fb_memcpy_d2d), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64), fbctx(), fbstream(), b.ptr, a.ptr, sizeof(T) * length(a))); b)
 
@@ -90,7 +104,9 @@ MLDataDevices.functional(::Type{<:B200Device}) = libfluxb200[] != C_NULL
 MLDataDevices.get_device(::B200Array) = B200Device()
 MLDataDevices.get_device_type(::B200Array) = B200Device
 MLDataDevices.set_device!(::Type{B200Device}, ::Nothing, rank::Integer) = (current_device[] = rank; nothing)   # used by FluxMPIExt.jl:17-22
-Adapt.adapt_storage(::B200Device, x::Array{<:Real}) = B200Array(Float32.(x))       # `model |> B200Device()`, like `gpu`
+Adapt.adapt_storage(::B200Device, x::Array{<:AbstractFloat}) = B200Array(Float32.(x))   # `model |> B200Device()`, like `gpu`
+Adapt.adapt_storage(::B200Device, x::Array{<:Integer}) = B200Array(Int32.(x))            # index arrays (Embedding), labels
+Adapt.adapt_storage(::B200Device, x::Array{Bool}) = B200Array(UInt8.(x))                 # masks
 Adapt.adapt_storage(::MLDataDevices.CPUDevice, x::B200Array) = Array(x)            # `cpu(model)`
 
 "Generic status-checked call into the library: fbcall(:fb_sumsq, (Ptr{Cvoid}, Int64, Ptr{Cvoid}), x.ptr, n, out.ptr)"
