@@ -16,7 +16,27 @@ struct AttnDims {
   int64_t E, Ev, Lq, Lk;
   int H, d, dv, causal;
   float scale;
+  // optional extras (the general kernels only): additive bias[j + Lk * i + bias_sh * h + bias_sb * b], dropout on the
+  // attention weights (keep-mask element ((b * H + h) * Lq + i) * Lk + j of the Philox stream), cotangent of alpha
+  const float* bias;
+  int64_t bias_sh, bias_sb;
+  const float* dalpha;
+  float p_drop, drop_scale;
+  uint64_t seed, offset;
 };
+
+// the logit of (query i, key j): scaled score plus the additive bias
+__device__ __forceinline__ float attn_logit(const AttnDims& D, float s, int64_t b, int h, int64_t i, int64_t j) {
+  s *= D.scale;
+  if (D.bias != nullptr) s += __ldg(D.bias + b * D.bias_sb + (int64_t)h * D.bias_sh + i * D.Lk + j);
+  return s;
+}
+// what dropout multiplies the attention weight (i, j) with: 0 or 1 / (1 - p)
+__device__ __forceinline__ float attn_dropmul(const AttnDims& D, int64_t b, int h, int64_t i, int64_t j) {
+  if (D.p_drop <= 0.0f) return 1.0f;
+  const uint64_t idx = (uint64_t)(((b * D.H + h) * D.Lq + i) * D.Lk + j);
+  return fb_dropout_keep(idx, D.p_drop, D.seed, D.offset) ? D.drop_scale : 0.0f;
+}
 
 // dst[r][c] = src[(row0 + r) * ld_src + c] for r < 64, c < LD - 4 (zero padded outside rows < nrows, c < width)
 template <int LD>
@@ -168,7 +188,7 @@ attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         keep[j] = attn_keep(D, mask, gi, j0 + tx + 16 * j);
-        S[i][j] = keep[j] ? S[i][j] * D.scale : -INFINITY;
+        S[i][j] = keep[j] ? attn_logit(D, S[i][j], b, h, gi, j0 + tx + 16 * j) : -INFINITY;
         mx = fmaxf(mx, S[i][j]);
       }
       mx = row16_max(mx);
@@ -180,7 +200,8 @@ attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
       for (int j = 0; j < 4; ++j) {
         const float p = keep[j] ? expf(S[i][j] - m_use) : 0.0f;
         rs += p;
-        Ps[(ty + 16 * i) * PLD + tx + 16 * j] = p;
+        // dropout acts on the normalised weights: the row sum keeps every term, the product with V the kept ones
+        Ps[(ty + 16 * i) * PLD + tx + 16 * j] = (keep[j] && D.p_drop > 0.0f) ? p * attn_dropmul(D, b, h, gi, j0 + tx + 16 * j) : p;
       }
       rs = row16_sum(rs);
       l[i] = l[i] * corr + rs;
@@ -234,7 +255,7 @@ template <int LD>
 __device__ __forceinline__ void recompute_p_ds(const AttnDims& D, const uint8_t* mask, const float* Qs, const float* Ks,
                                                const float* Vs, const float* dOs, const float* lse_bh,
                                                const float* dlt_bh, int64_t i0, int64_t j0, int ty, int tx,
-                                               float* Ps, float* dSs) {
+                                               float* Ps, float* dSs, int64_t b, int h) {
   const int kdim = (D.d + 3) & ~3, vdim = (D.dv + 3) & ~3;
   float S[4][4], dP[4][4];
   tile_abt<LD>(S, Qs, Ks, kdim, ty, tx);
@@ -247,9 +268,13 @@ __device__ __forceinline__ void recompute_p_ds(const AttnDims& D, const uint8_t*
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const bool keep = attn_keep(D, mask, gi, j0 + tx + 16 * j) && (ls != -INFINITY);
-      const float p = keep ? expf(S[i][j] * D.scale - ls) : 0.0f;
-      if (Ps) Ps[(ty + 16 * i) * PLD + tx + 16 * j] = p;
-      dSs[(ty + 16 * i) * PLD + tx + 16 * j] = p * (dP[i][j] - dl);
+      const int64_t gj = j0 + tx + 16 * j;
+      const float p = keep ? expf(attn_logit(D, S[i][j], b, h, gi, gj) - ls) : 0.0f;
+      const float dm = keep ? attn_dropmul(D, b, h, gi, gj) : 0.0f;
+      float dp = dP[i][j];
+      if (D.dalpha != nullptr && keep) dp += __ldg(D.dalpha + ((b * D.H + h) * D.Lq + gi) * D.Lk + gj);
+      if (Ps) Ps[(ty + 16 * i) * PLD + tx + 16 * j] = p * dm;          // the weights that multiplied V
+      dSs[(ty + 16 * i) * PLD + tx + 16 * j] = p * (dp * dm - dl);
     }
   }
 }
@@ -293,7 +318,7 @@ attn_bwd_dkdv_kernel(const float* __restrict__ q, const float* __restrict__ k, c
     load_tile<LD>(Qs, qb, D.E, i0, D.Lq, D.d);
     load_tile<LD>(dOs, dob, D.Ev, i0, D.Lq, D.dv);
     __syncthreads();
-    recompute_p_ds<LD>(D, mask, Qs, Ks, Vs, dOs, lse_bh, dlt_bh, i0, j0, ty, tx, Ps, dSs);
+    recompute_p_ds<LD>(D, mask, Qs, Ks, Vs, dOs, lse_bh, dlt_bh, i0, j0, ty, tx, Ps, dSs, b, h);
     __syncthreads();
     tile_ptx<NC, LD>(adv, Ps, dOs, ty, tx);
     tile_ptx<NC, LD>(adk, dSs, Qs, ty, tx);
@@ -354,7 +379,7 @@ attn_bwd_dq_kernel(const float* __restrict__ q, const float* __restrict__ k, con
     load_tile<LD>(Ks, kb, D.E, j0, D.Lk, D.d);
     load_tile<LD>(Vs, vb, D.Ev, j0, D.Lk, D.dv);
     __syncthreads();
-    recompute_p_ds<LD>(D, mask, Qs, Ks, Vs, dOs, lse_bh, dlt_bh, i0, j0, ty, tx, nullptr, dSs);
+    recompute_p_ds<LD>(D, mask, Qs, Ks, Vs, dOs, lse_bh, dlt_bh, i0, j0, ty, tx, nullptr, dSs, b, h);
     __syncthreads();
     tile_pv<NC, LD>(adq, dSs, Ks, ty, tx);
   }
@@ -378,12 +403,15 @@ attn_bwd_dq_kernel(const float* __restrict__ q, const float* __restrict__ k, con
 template <int NC>
 __global__ void __launch_bounds__(AT)
 attn_scores_kernel(const float* __restrict__ q, const float* __restrict__ k, const uint8_t* __restrict__ mask,
-                   const float* __restrict__ lse, float* __restrict__ alpha, AttnDims D) {
+                   const float* __restrict__ lse, float* __restrict__ alpha, float* __restrict__ extra_dlt, AttnDims D) {
+  // With extra_dlt the kernel does not write alpha: it adds sum_j alpha_ij * dalpha_ij to extra_dlt[b][h][i] (the
+  // share of an alpha cotangent in the softmax backward's row term).
   constexpr int LD = NC * 64 + 4;
   extern __shared__ float sm[];
   float* Qs = sm;
   float* Ks = Qs + TS * LD;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float row_extra[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   const int64_t j0 = (int64_t)blockIdx.x * TS, i0 = (int64_t)blockIdx.y * TS;
   const int64_t bh = blockIdx.z;
   const int64_t b = bh / D.H;
@@ -405,7 +433,21 @@ attn_scores_kernel(const float* __restrict__ q, const float* __restrict__ k, con
       const int64_t gj = j0 + tx + 16 * j;
       if (gj >= D.Lk) continue;
       const bool keep = attn_keep(D, mask, gi, gj) && (ls != -INFINITY);
-      ab[gi * D.Lk + gj] = keep ? expf(S[i][j] * D.scale - ls) : 0.0f;
+      const float a = keep ? expf(attn_logit(D, S[i][j], b, h, gi, gj) - ls) * attn_dropmul(D, b, h, gi, gj) : 0.0f;
+      if (extra_dlt != nullptr) {
+        // contribution of the alpha cotangent to delta_i = sum_j alpha_ij * dalpha_ij (alpha after dropout)
+        row_extra[i] += a * __ldg(D.dalpha + (bh * D.Lq + gi) * D.Lk + gj);
+      } else {
+        ab[gi * D.Lk + gj] = a;
+      }
+    }
+  }
+  if (extra_dlt != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float r = row16_sum(row_extra[i]);
+      const int64_t gi = i0 + ty + 16 * i;
+      if (tx == 0 && gi < D.Lq && r != 0.0f) atomicAdd(extra_dlt + bh * D.Lq + gi, r);
     }
   }
 }
@@ -425,23 +467,46 @@ int32_t attn_make_dims(const char* fn, AttnDims* D, int64_t e_dim, int64_t ev_di
   D->E = e_dim; D->Ev = ev_dim; D->Lq = lq; D->Lk = lk; D->H = nheads;
   D->d = (int)(e_dim / nheads); D->dv = (int)(ev_dim / nheads); D->causal = causal ? 1 : 0;
   D->scale = 1.0f / sqrtf((float)D->d);
+  D->bias = nullptr; D->bias_sh = 0; D->bias_sb = 0; D->dalpha = nullptr;
+  D->p_drop = 0.0f; D->drop_scale = 1.0f; D->seed = 0; D->offset = 0;
   return FB_OK;
 }
+
+// additive bias and dropout of the extended entry points
+int32_t attn_set_extras(const char* fn, AttnDims* D, const float* bias, int64_t bias_sh, int64_t bias_sb, float p_drop, uint64_t seed,
+                        uint64_t offset) {
+  FB_REQUIRE(p_drop >= 0.0f && p_drop < 1.0f, FB_ERR_INVALID_ARG, "%s: dropout probability %g is outside [0, 1)", fn, (double)p_drop);
+  FB_REQUIRE(bias_sh >= 0 && bias_sb >= 0, FB_ERR_INVALID_ARG, "%s: negative bias stride", fn);
+  D->bias = bias; D->bias_sh = bias ? bias_sh : 0; D->bias_sb = bias ? bias_sb : 0;
+  D->p_drop = p_drop; D->drop_scale = 1.0f / (1.0f - p_drop); D->seed = seed; D->offset = offset;
+  return FB_OK;
+}
+bool attn_has_extras(const AttnDims& D) { return D.bias != nullptr || D.p_drop > 0.0f || D.dalpha != nullptr; }
 
 }  // namespace
 
 FB_API int32_t fb_attn_fwd(fb_ctx* ctx, void* stream_, const float* q, const float* k, const float* v,
                            const uint8_t* mask, float* o, float* lse, int64_t e_dim, int64_t ev_dim, int64_t lq,
                            int64_t lk, int64_t batch, int32_t nheads, int32_t causal) {
+  return fb_attn_fwd_ex(ctx, stream_, q, k, v, mask, nullptr, 0, 0, 0.0f, 0, 0, o, lse, e_dim, ev_dim, lq, lk, batch, nheads, causal);
+}
+
+FB_API int32_t fb_attn_fwd_ex(fb_ctx* ctx, void* stream_, const float* q, const float* k, const float* v, const uint8_t* mask,
+                              const float* bias, int64_t bias_stride_h, int64_t bias_stride_b, float p_drop, uint64_t seed,
+                              uint64_t offset, float* o, float* lse, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk,
+                              int64_t batch, int32_t nheads, int32_t causal) {
   FB_CHECK_CTX(ctx);
   cudaStream_t stream = (cudaStream_t)stream_;
   AttnDims D;
   int32_t st = attn_make_dims("fb_attn_fwd", &D, e_dim, ev_dim, lq, lk, batch, nheads, causal);
   if (st != FB_OK) return st;
+  st = attn_set_extras("fb_attn_fwd", &D, bias, bias_stride_h, bias_stride_b, p_drop, seed, offset);
+  if (st != FB_OK) return st;
   if (lq == 0 || batch == 0) return FB_OK;
   FB_REQUIRE(q && k && v && o && lse, FB_ERR_INVALID_ARG, "fb_attn_fwd: NULL pointer");
-  // head size 64 without an explicit mask runs on the tensor cores
-  st = fb_attn_fwd_tc(ctx, stream, q, k, v, mask, o, lse, e_dim, ev_dim, lq, lk, batch, nheads, causal);
+  // head size 64 without an explicit mask, bias or dropout runs on the tensor cores
+  st = attn_has_extras(D) ? FB_ERR_UNSUPPORTED
+                          : fb_attn_fwd_tc(ctx, stream, q, k, v, mask, o, lse, e_dim, ev_dim, lq, lk, batch, nheads, causal);
   if (st != FB_ERR_UNSUPPORTED) return st;
   const int nc = (D.d > 64 || D.dv > 64) ? 2 : 1;
   const size_t smem = (size_t)(3 * TS * (nc * 64 + 4) + TS * PLD) * sizeof(float);
@@ -461,11 +526,23 @@ FB_API int32_t fb_attn_bwd(fb_ctx* ctx, void* stream_, const float* q, const flo
                            const uint8_t* mask, const float* o, const float* lse, const float* dout, float* dq,
                            float* dk, float* dv, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch,
                            int32_t nheads, int32_t causal) {
+  return fb_attn_bwd_ex(ctx, stream_, q, k, v, mask, nullptr, 0, 0, 0.0f, 0, 0, o, lse, dout, nullptr, dq, dk, dv, e_dim, ev_dim, lq, lk,
+                        batch, nheads, causal);
+}
+
+FB_API int32_t fb_attn_bwd_ex(fb_ctx* ctx, void* stream_, const float* q, const float* k, const float* v, const uint8_t* mask,
+                              const float* bias, int64_t bias_stride_h, int64_t bias_stride_b, float p_drop, uint64_t seed,
+                              uint64_t offset, const float* o, const float* lse, const float* dout, const float* dalpha, float* dq,
+                              float* dk, float* dv, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch,
+                              int32_t nheads, int32_t causal) {
   FB_CHECK_CTX(ctx);
   cudaStream_t stream = (cudaStream_t)stream_;
   AttnDims D;
   int32_t st = attn_make_dims("fb_attn_bwd", &D, e_dim, ev_dim, lq, lk, batch, nheads, causal);
   if (st != FB_OK) return st;
+  st = attn_set_extras("fb_attn_bwd", &D, bias, bias_stride_h, bias_stride_b, p_drop, seed, offset);
+  if (st != FB_OK) return st;
+  D.dalpha = dalpha;
   if (batch == 0) return FB_OK;
   FB_REQUIRE(lq >= 1 && lk >= 1, FB_ERR_SHAPE, "fb_attn_bwd: empty sequence");
   FB_REQUIRE(q && k && v && o && lse && dout && dq && dk && dv, FB_ERR_INVALID_ARG, "fb_attn_bwd: NULL pointer");
@@ -476,6 +553,22 @@ FB_API int32_t fb_attn_bwd(fb_ctx* ctx, void* stream_, const float* q, const flo
   FB_LAUNCH_CHECK();
   const int nc = (D.d > 64 || D.dv > 64) ? 2 : 1;
   const int ld = nc * 64 + 4;
+  if (dalpha != nullptr) {
+    // a cotangent of the attention weights adds sum_j alpha_ij * dalpha_ij to the row term of the softmax backward
+    FB_REQUIRE((lq + TS - 1) / TS <= 65535, FB_ERR_SHAPE, "fb_attn_bwd: query length too large");
+    const int ncs = D.d > 64 ? 2 : 1;
+    const size_t smem_s = (size_t)(2 * TS * (ncs * 64 + 4)) * sizeof(float);
+    dim3 grid_s((unsigned)((lk + TS - 1) / TS), (unsigned)((lq + TS - 1) / TS), (unsigned)(batch * nheads));
+    if (ncs == 1) {
+      FB_CUDA(cudaFuncSetAttribute(attn_scores_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s));
+      attn_scores_kernel<1><<<grid_s, AT, smem_s, stream>>>(q, k, mask, lse, nullptr, dlt, D);
+    } else {
+      FB_CUDA(cudaFuncSetAttribute(attn_scores_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s));
+      attn_scores_kernel<2><<<grid_s, AT, smem_s, stream>>>(q, k, mask, lse, nullptr, dlt, D);
+    }
+    FB_LAUNCH_CHECK();
+  }
+  const bool extras = attn_has_extras(D);
   const size_t smem_kv = (size_t)(4 * TS * ld + 2 * TS * PLD) * sizeof(float);
   const size_t smem_q = (size_t)(4 * TS * ld + TS * PLD) * sizeof(float);
   dim3 grid_kv((unsigned)((lk + TS - 1) / TS), (unsigned)nheads, (unsigned)batch);
@@ -484,7 +577,8 @@ FB_API int32_t fb_attn_bwd(fb_ctx* ctx, void* stream_, const float* q, const flo
     FB_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
     FB_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
     // dK / dV on the tensor cores where the shape allows (head size 64, no explicit mask, at most 2048 queries)
-    st = fb_attn_bwd_dkdv_tc(ctx, stream, q, k, v, mask, lse, dlt, dout, dk, dv, e_dim, ev_dim, lq, lk, batch, nheads, causal);
+    st = extras ? FB_ERR_UNSUPPORTED
+                : fb_attn_bwd_dkdv_tc(ctx, stream, q, k, v, mask, lse, dlt, dout, dk, dv, e_dim, ev_dim, lq, lk, batch, nheads, causal);
     if (st == FB_ERR_UNSUPPORTED) {
       attn_bwd_dkdv_kernel<1><<<grid_kv, AT, smem_kv, stream>>>(q, k, v, mask, lse, dlt, dout, dk, dv, D);
       FB_LAUNCH_CHECK();
@@ -492,7 +586,8 @@ FB_API int32_t fb_attn_bwd(fb_ctx* ctx, void* stream_, const float* q, const flo
       return st;
     }
     // dQ on the tensor cores where the shape allows (head size 64, no explicit mask, at most 2048 keys)
-    st = fb_attn_bwd_dq_tc(ctx, stream, q, k, v, mask, lse, dlt, dout, dq, e_dim, ev_dim, lq, lk, batch, nheads, causal);
+    st = extras ? FB_ERR_UNSUPPORTED
+                : fb_attn_bwd_dq_tc(ctx, stream, q, k, v, mask, lse, dlt, dout, dq, e_dim, ev_dim, lq, lk, batch, nheads, causal);
     if (st != FB_ERR_UNSUPPORTED) return st;
     attn_bwd_dq_kernel<1><<<grid_q, AT, smem_q, stream>>>(q, k, v, mask, lse, dlt, dout, dq, D);
   } else {
@@ -509,10 +604,19 @@ FB_API int32_t fb_attn_bwd(fb_ctx* ctx, void* stream_, const float* q, const flo
 FB_API int32_t fb_attn_scores(fb_ctx* ctx, void* stream_, const float* q, const float* k, const uint8_t* mask,
                               const float* lse, float* alpha, int64_t e_dim, int64_t lq, int64_t lk, int64_t batch,
                               int32_t nheads, int32_t causal) {
+  return fb_attn_scores_ex(ctx, stream_, q, k, mask, nullptr, 0, 0, 0.0f, 0, 0, lse, alpha, e_dim, lq, lk, batch, nheads, causal);
+}
+
+FB_API int32_t fb_attn_scores_ex(fb_ctx* ctx, void* stream_, const float* q, const float* k, const uint8_t* mask, const float* bias,
+                                 int64_t bias_stride_h, int64_t bias_stride_b, float p_drop, uint64_t seed, uint64_t offset,
+                                 const float* lse, float* alpha, int64_t e_dim, int64_t lq, int64_t lk, int64_t batch,
+                                 int32_t nheads, int32_t causal) {
   FB_CHECK_CTX(ctx);
   cudaStream_t stream = (cudaStream_t)stream_;
   AttnDims D;
   int32_t st = attn_make_dims("fb_attn_scores", &D, e_dim, e_dim, lq, lk, batch, nheads, causal);
+  if (st != FB_OK) return st;
+  st = attn_set_extras("fb_attn_scores", &D, bias, bias_stride_h, bias_stride_b, p_drop, seed, offset);
   if (st != FB_OK) return st;
   if (lq == 0 || lk == 0 || batch == 0) return FB_OK;
   FB_REQUIRE(q && k && lse && alpha, FB_ERR_INVALID_ARG, "fb_attn_scores: NULL pointer");
@@ -522,10 +626,10 @@ FB_API int32_t fb_attn_scores(fb_ctx* ctx, void* stream_, const float* q, const 
   dim3 grid((unsigned)((lk + TS - 1) / TS), (unsigned)((lq + TS - 1) / TS), (unsigned)(batch * nheads));
   if (nc == 1) {
     FB_CUDA(cudaFuncSetAttribute(attn_scores_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attn_scores_kernel<1><<<grid, AT, smem, stream>>>(q, k, mask, lse, alpha, D);
+    attn_scores_kernel<1><<<grid, AT, smem, stream>>>(q, k, mask, lse, alpha, nullptr, D);
   } else {
     FB_CUDA(cudaFuncSetAttribute(attn_scores_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attn_scores_kernel<2><<<grid, AT, smem, stream>>>(q, k, mask, lse, alpha, D);
+    attn_scores_kernel<2><<<grid, AT, smem, stream>>>(q, k, mask, lse, alpha, nullptr, D);
   }
   FB_LAUNCH_CHECK();
   return FB_OK;

@@ -29,16 +29,6 @@ constexpr int KT = 64;    // keys per block
 constexpr int HD = 64;    // head size (q/k features and v features per head)
 constexpr int ATC_THREADS = 320;
 
-// byte offsets inside the 1024-byte aligned dynamic shared memory
-constexpr int OFF_QHI = 0, OFF_QLO = 32768;              // 4 chunks x [128 rows][16 floats]
-constexpr int OFF_KHI = 65536, OFF_KLO = 81920;          // 4 chunks x [64 rows][16 floats]
-constexpr int OFF_VHI = 98304, OFF_VLO = 114688;         // 2 chunks x [64 key rows][32 floats]
-constexpr int OFF_PHI = 131072, OFF_PLO = 163840;        // 4 chunks x [128 rows][16 floats]
-constexpr int OFF_BAR = 196608;
-constexpr int ATC_SMEM = OFF_BAR + 256 + 1024;           // barriers + alignment slack
-
-enum { B_QFULL = 0, B_QREADY, B_KFULL, B_KREADY, B_KFREE, B_VFULL, B_VREADY, B_VFREE, B_SFULL, B_PREADY, B_OFULL, B_COUNT };
-
 __device__ __forceinline__ void tc_st_32x32b_x32(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -75,268 +65,6 @@ struct AtcDims {
   float scale_log2;   // log2(e) / sqrt(d)
   float scale;        // 1 / sqrt(d)
 };
-
-// P_TMEM: the softmax warps put P (hi in place of S, lo in columns 128..191) into tensor memory and P V takes its A
-// operand from there, instead of staging P in shared memory.
-template <bool P_TMEM>
-__global__ void __launch_bounds__(ATC_THREADS, 1)
-attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, float* __restrict__ o, float* __restrict__ lse, AtcDims D,
-                   int32_t* __restrict__ dev_err) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t sb = smem_u32(smem);
-  const uint32_t bar0 = sb + OFF_BAR;
-  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-  volatile uint32_t* s_tmem = (volatile uint32_t*)(smem + OFF_BAR + 8 * B_COUNT);
-  volatile int* s_abort = (volatile int*)(smem + OFF_BAR + 8 * B_COUNT + 8);
-  volatile int* s_skip = (volatile int*)(smem + OFF_BAR + 8 * B_COUNT + 16);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t i0 = (int64_t)blockIdx.x * QT;
-  const int h = blockIdx.y;
-  const int64_t b = blockIdx.z;
-  int64_t kv_end = D.Lk;
-  if (D.causal && i0 + QT < kv_end) kv_end = i0 + QT;
-  const int nkb = (int)((kv_end + KT - 1) / KT);
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar(B_QFULL), 1);
-    mbar_init(bar(B_QREADY), 4);
-    mbar_init(bar(B_KFULL), 1);
-    mbar_init(bar(B_KREADY), 4);
-    mbar_init(bar(B_KFREE), 1);
-    mbar_init(bar(B_VFULL), 1);
-    mbar_init(bar(B_VREADY), 4);
-    mbar_init(bar(B_VFREE), 1);
-    mbar_init(bar(B_SFULL), 1);
-    mbar_init(bar(B_PREADY), 4);
-    mbar_init(bar(B_OFULL), 1);
-    *s_abort = 0;
-    *s_skip = (*(volatile int32_t*)dev_err != 0) ? 1 : 0;   // an error word left set means: do not start
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    fence_proxy_async();
-  }
-  __syncthreads();
-  if (*s_skip != 0) return;
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)s_tmem)),
-                 "r"(P_TMEM ? 256u : 128u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *s_tmem;
-
-  if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer ---
-    if (lane == 0) {
-      const int qrow = (int)(b * D.Lq + i0), krow0 = (int)(b * D.Lk);
-      mbar_arrive_expect_tx(bar(B_QFULL), 32768u);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tma_load_2d(sb + OFF_QHI + c * 8192, &tmQ, h * HD + 16 * c, qrow, bar(B_QFULL));
-      for (int j = 0; j < nkb; ++j) {
-        if (j > 0 && !mbar_wait(bar(B_KFREE), (uint32_t)(j - 1) & 1u, s_abort)) break;
-        mbar_arrive_expect_tx(bar(B_KFULL), 16384u);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tma_load_2d(sb + OFF_KHI + c * 4096, &tmK, h * HD + 16 * c, krow0 + j * KT, bar(B_KFULL));
-        if (j > 0 && !mbar_wait(bar(B_VFREE), (uint32_t)(j - 1) & 1u, s_abort)) break;
-        mbar_arrive_expect_tx(bar(B_VFULL), 16384u);
-        tma_load_3d(sb + OFF_VHI, &tmV, 0, krow0 + j * KT, 2 * h, bar(B_VFULL));
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer ---
-    if (lane == 0) {
-      const uint32_t idesc_qk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(KT >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
-      const uint32_t idesc_pv = idesc_qk | (1u << 16);   // B = V is MN-major; N = 64 value features
-      bool ok = mbar_wait(bar(B_QREADY), 0u, s_abort);
-      for (int j = 0; j < nkb && ok; ++j) {
-        const uint32_t ph = (uint32_t)j & 1u;
-        ok = mbar_wait(bar(B_KREADY), ph, s_abort);
-        if (!ok) break;
-        tc_fence_after();
-        // S = Q K' (contraction over the 64 features: 4 chunks x 2 k-steps of 8)
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t qo = (uint32_t)((ks >> 1) * 8192 + (ks & 1) * 32), ko = (uint32_t)((ks >> 1) * 4096 + (ks & 1) * 32);
-          const uint64_t q_hi = make_smem_desc(sb + OFF_QHI + qo, 16, 512, LAYOUT_SW64);
-          const uint64_t q_lo = make_smem_desc(sb + OFF_QLO + qo, 16, 512, LAYOUT_SW64);
-          const uint64_t k_hi = make_smem_desc(sb + OFF_KHI + ko, 16, 512, LAYOUT_SW64);
-          const uint64_t k_lo = make_smem_desc(sb + OFF_KLO + ko, 16, 512, LAYOUT_SW64);
-          tc_mma_tf32(tmem_base, q_lo, k_hi, idesc_qk, ks > 0 ? 1u : 0u);
-          tc_mma_tf32(tmem_base, q_hi, k_lo, idesc_qk, 1u);
-          tc_mma_tf32(tmem_base, q_hi, k_hi, idesc_qk, 1u);
-        }
-        tc_commit(bar(B_SFULL));
-        tc_commit(bar(B_KFREE));
-        ok = mbar_wait(bar(B_PREADY), ph, s_abort) && mbar_wait(bar(B_VREADY), ph, s_abort);
-        if (!ok) break;
-        tc_fence_after();
-        // P V (contraction over the 64 keys: 8 k-steps of 8; P chunk = 16 keys)
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t po = (uint32_t)((ks >> 1) * 8192 + (ks & 1) * 32), vo = (uint32_t)(ks * 1024);
-          const uint64_t p_hi = make_smem_desc(sb + OFF_PHI + po, 16, 512, LAYOUT_SW64);
-          const uint64_t p_lo = make_smem_desc(sb + OFF_PLO + po, 16, 512, LAYOUT_SW64);
-          const uint64_t v_hi = make_smem_desc(sb + OFF_VHI + vo, KT * 128, 512, LAYOUT_SW128_32B);
-          const uint64_t v_lo = make_smem_desc(sb + OFF_VLO + vo, KT * 128, 512, LAYOUT_SW128_32B);
-          if (P_TMEM) {
-            const uint32_t a_hi = tmem_base + (uint32_t)(8 * ks), a_lo = tmem_base + 128u + (uint32_t)(8 * ks);
-            tc_mma_tf32_ta(tmem_base + 64u, a_lo, v_hi, idesc_pv, ks > 0 ? 1u : 0u);
-            tc_mma_tf32_ta(tmem_base + 64u, a_hi, v_lo, idesc_pv, 1u);
-            tc_mma_tf32_ta(tmem_base + 64u, a_hi, v_hi, idesc_pv, 1u);
-          } else {
-            tc_mma_tf32(tmem_base + 64u, p_lo, v_hi, idesc_pv, ks > 0 ? 1u : 0u);
-            tc_mma_tf32(tmem_base + 64u, p_hi, v_lo, idesc_pv, 1u);
-            tc_mma_tf32(tmem_base + 64u, p_hi, v_hi, idesc_pv, 1u);
-          }
-        }
-        tc_commit(bar(B_OFULL));
-        tc_commit(bar(B_VFREE));
-      }
-    }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ softmax warps ---
-    const int q = warp & 3;                  // TMEM lane quadrant of this warp
-    const int row = 32 * q + lane;           // query row inside the tile = TMEM lane
-    const int64_t gi = i0 + row;
-    const uint32_t t_row = tmem_base + ((uint32_t)(32 * q) << 16);
-    float m = -INFINITY, l = 0.0f;
-    float acc[HD];
-#pragma unroll
-    for (int c = 0; c < HD; ++c) acc[c] = 0.0f;
-    const uint32_t sw = (uint32_t)((row >> 1) & 3);
-    bool ok = true;
-    for (int j = 0; j < nkb && ok; ++j) {
-      const uint32_t ph = (uint32_t)j & 1u;
-      const int64_t j0 = (int64_t)j * KT;
-      ok = mbar_wait(bar(B_SFULL), ph, s_abort);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t s0[32], s1[32];
-      tc_ld_32x32b_x32(t_row, s0);
-      tc_ld_32x32b_x32(t_row + 32u, s1);
-      tc_wait_ld();
-      // keys this query may see in this block: key < Lk, and key <= query when causal
-      int64_t lim = D.Lk - j0;
-      if (D.causal && gi - j0 + 1 < lim) lim = gi - j0 + 1;
-      const int nvalid = lim < 0 ? 0 : (lim > KT ? KT : (int)lim);
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        if (c < nvalid) mx = fmaxf(mx, __uint_as_float(s0[c]));
-        if (c + 32 < nvalid) mx = fmaxf(mx, __uint_as_float(s1[c]));
-      }
-      const float m_new = fmaxf(m, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-      const float alpha = exp2f((m - m_use) * D.scale_log2);   // m = -inf gives 0
-      float rs = 0.0f;
-      if (P_TMEM) {
-        // P over S in place (the raw value is the hi operand), its lo part in columns 128..191
-        uint32_t lo0[32], lo1[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float p0 = (c < nvalid) ? exp2f((__uint_as_float(s0[c]) - m_use) * D.scale_log2) : 0.0f;
-          const float p1 = (c + 32 < nvalid) ? exp2f((__uint_as_float(s1[c]) - m_use) * D.scale_log2) : 0.0f;
-          rs += p0 + p1;
-          s0[c] = __float_as_uint(p0); s1[c] = __float_as_uint(p1);
-          lo0[c] = __float_as_uint(tf32_lo(p0)); lo1[c] = __float_as_uint(tf32_lo(p1));
-        }
-        tc_st_32x32b_x32(t_row, s0);
-        tc_st_32x32b_x32(t_row + 32u, s1);
-        tc_st_32x32b_x32(t_row + 128u, lo0);
-        tc_st_32x32b_x32(t_row + 160u, lo1);
-        tc_wait_st();
-      } else {
-      // P in the K-major 64-byte swizzled layout: chunk = key / 16, 16-byte piece (key % 16) / 4 XOR (row / 2) % 4
-#pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        float p[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = 4 * g + e;
-          const float sv = __uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]);
-          p[e] = (c < nvalid) ? exp2f((sv - m_use) * D.scale_log2) : 0.0f;
-          rs += p[e];
-        }
-        const uint32_t off = (uint32_t)((g >> 2) * 8192 + row * 64) + ((((uint32_t)g & 3u) ^ sw) << 4);
-        *(float4*)(smem + OFF_PHI + off) = make_float4(p[0], p[1], p[2], p[3]);
-        *(float4*)(smem + OFF_PLO + off) = make_float4(tf32_lo(p[0]), tf32_lo(p[1]), tf32_lo(p[2]), tf32_lo(p[3]));
-      }
-      }
-      fence_proxy_async();   // P becomes visible to the tensor core's async-proxy reads
-      tc_fence_before();     // the reads of S (and of the previous block's P V) precede the arrive
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PREADY));
-      l = l * alpha + rs;
-      m = m_new;
-#pragma unroll
-      for (int c = 0; c < HD; ++c) acc[c] *= alpha;
-      ok = mbar_wait(bar(B_OFULL), ph, s_abort);
-      if (!ok) break;
-      tc_fence_after();
-      tc_ld_32x32b_x32(t_row + 64u, s0);
-      tc_ld_32x32b_x32(t_row + 96u, s1);
-      tc_wait_ld();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        acc[c] += __uint_as_float(s0[c]);
-        acc[c + 32] += __uint_as_float(s1[c]);
-      }
-    }
-    if (ok && gi < D.Lq) {
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      float* orow = o + (b * D.Lq + gi) * D.Ev + (int64_t)h * HD;
-#pragma unroll
-      for (int c = 0; c < HD; c += 4)
-        *(float4*)(orow + c) = make_float4(acc[c] * inv, acc[c + 1] * inv, acc[c + 2] * inv, acc[c + 3] * inv);
-      // the running maximum is of unscaled scores
-      lse[(b * D.H + h) * D.Lq + gi] = (l > 0.0f) ? m * D.scale + logf(l) : -INFINITY;
-    }
-  } else {
-    // --------------------------------------------- split warps: lo = x - tf32(x) twins ---
-    const int tt = (warp - 6) * 32 + lane;   // 0..127
-    auto split = [&](int off_hi, int off_lo, int n16) {   // n16 = 16-byte pieces per thread
-      const float4* hi = (const float4*)(smem + off_hi);
-      float4* lo = (float4*)(smem + off_lo);
-      for (int i = 0; i < n16; ++i) {
-        float4 v = hi[tt + i * 128];
-        v.x = tf32_lo(v.x); v.y = tf32_lo(v.y); v.z = tf32_lo(v.z); v.w = tf32_lo(v.w);
-        lo[tt + i * 128] = v;
-      }
-      fence_proxy_async();
-      __syncwarp();
-    };
-    bool ok = mbar_wait(bar(B_QFULL), 0u, s_abort);
-    if (ok) {
-      split(OFF_QHI, OFF_QLO, 16);
-      if (lane == 0) mbar_arrive(bar(B_QREADY));
-    }
-    for (int j = 0; j < nkb && ok; ++j) {
-      const uint32_t ph = (uint32_t)j & 1u;
-      ok = mbar_wait(bar(B_KFULL), ph, s_abort);
-      if (!ok) break;
-      split(OFF_KHI, OFF_KLO, 8);
-      if (lane == 0) mbar_arrive(bar(B_KREADY));
-      ok = mbar_wait(bar(B_VFULL), ph, s_abort);
-      if (!ok) break;
-      split(OFF_VHI, OFF_VLO, 8);
-      if (lane == 0) mbar_arrive(bar(B_VREADY));
-    }
-  }
-
-  // ---------------------------------------------------------------------- teardown ---
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P_TMEM ? 256u : 128u) : "memory");
-  }
-  if (threadIdx.x == 0 && *s_abort != 0) atomicExch(dev_err, 4001);
-}
 
 // Pipelined variant: three K / V stages in shared memory (a K tile is reloaded three blocks ahead, which covers the
 // latency of its TMA load); Q lives in tensor memory as the A operand of Q K' (hi and lo parts, stored once by the
@@ -1211,32 +939,12 @@ bool attn_tc_enabled() {
   return on != 0;
 }
 
-// FLUXB200_ATTN_PIPE = 0 selects the unpipelined kernels (one S / P V buffer, one K / V stage).
-bool attn_pipelined() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("FLUXB200_ATTN_PIPE");
-    on = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return on != 0;
-}
-
 // FLUXB200_ATTN_BWD_TC = 0 keeps the backward pass on the Float32 FMA kernels.
 bool attn_bwd_tc_enabled() {
   static int on = -1;
   if (on < 0) {
     const char* e = getenv("FLUXB200_ATTN_BWD_TC");
     on = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return on != 0;
-}
-
-// FLUXB200_ATTN_PTMEM = 1: P travels through tensor memory instead of shared memory.
-bool attn_p_in_tmem() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("FLUXB200_ATTN_PTMEM");
-    on = (e != nullptr && e[0] == '1') ? 1 : 0;
   }
   return on != 0;
 }
@@ -1266,9 +974,8 @@ int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const f
   if (lq < 1 || lk < 1 || batch < 1 || batch * lq > 0x7fffff00 || batch * lk > 0x7fffff00 || batch > 65535 || nheads > 65535)
     return FB_ERR_UNSUPPORTED;
   if (!fb_aligned16(q) || !fb_aligned16(k) || !fb_aligned16(v) || !fb_aligned16(o)) return FB_ERR_UNSUPPORTED;
-  CUtensorMap tmQ, tmK, tmV;
-  if (!encode_map(&tmQ, q, batch * lq, e_dim, e_dim, 16, QT, CU_TENSOR_MAP_SWIZZLE_64B) ||
-      !encode_map(&tmK, k, batch * lk, e_dim, e_dim, 16, KT, CU_TENSOR_MAP_SWIZZLE_64B) ||
+  CUtensorMap tmK, tmV;
+  if (!encode_map(&tmK, k, batch * lk, e_dim, e_dim, 16, KT, CU_TENSOR_MAP_SWIZZLE_64B) ||
       !encode_rows3d(&tmV, v, batch * lk, ev_dim, KT, HD / 32))
     return FB_ERR_UNSUPPORTED;
   AtcDims D;
@@ -1276,16 +983,8 @@ int32_t fb_attn_fwd_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, const f
   D.scale = 1.0f / sqrtf((float)HD);
   D.scale_log2 = D.scale * 1.4426950408889634f;
   dim3 grid((unsigned)((lq + QT - 1) / QT), (unsigned)nheads, (unsigned)batch);
-  if (attn_pipelined()) {
-    FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC2_SMEM));
-    attn_fwd_tc2_kernel<<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(q, tmK, tmV, o, lse, D, ctx->dev_error);
-  } else if (attn_p_in_tmem()) {
-    FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
-    attn_fwd_tc_kernel<true><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
-  } else {
-    FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
-    attn_fwd_tc_kernel<false><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(tmQ, tmK, tmV, o, lse, D, ctx->dev_error);
-  }
+  FB_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC2_SMEM));
+  attn_fwd_tc2_kernel<<<grid, ATC_THREADS, ATC2_SMEM, stream>>>(q, tmK, tmV, o, lse, D, ctx->dev_error);
   FB_LAUNCH_CHECK();
   return FB_OK;
 }

@@ -116,6 +116,34 @@ __device__ __forceinline__ float fb_act_grad_y(int act, float y) {
 static inline bool fb_act_valid(int act) { return act >= FB_ACT_IDENTITY && act <= FB_ACT_GELU_ERF; }
 static inline bool fb_act_needs_z(int act) { return act == FB_ACT_GELU_TANH || act == FB_ACT_GELU_ERF; }
 
+// ------------------------------------------------------------------ counter-based random numbers ---
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3"), 64-bit counter, 64-bit key.
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+  const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+  const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n1 = (uint32_t)p1;
+  const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1, n3 = (uint32_t)p0;
+  c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+}
+__device__ __forceinline__ void philox4x32_10(uint64_t counter, uint64_t seed, uint32_t (&out)[4]) {
+  uint32_t c[4] = {(uint32_t)counter, (uint32_t)(counter >> 32), 0u, 0u};
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    philox_round(c, k0, k1);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c[0]; out[1] = c[1]; out[2] = c[2]; out[3] = c[3];
+}
+
+// Dropout keep decision for element `idx` of a mask stream: word idx % 4 of Philox(counter = offset + idx / 4).
+__device__ __forceinline__ bool fb_dropout_keep(uint64_t idx, float p, uint64_t seed, uint64_t offset) {
+  uint32_t r[4];
+  philox4x32_10((idx >> 2) + offset, seed, r);
+  const uint32_t w = (idx & 3) == 0 ? r[0] : (idx & 3) == 1 ? r[1] : (idx & 3) == 2 ? r[2] : r[3];
+  return (float)(w >> 8) * (1.0f / 16777216.0f) >= p;
+}
+
 // -------------------------------------------------------------------------- reductions ---
 __device__ __forceinline__ float fb_warp_sum(float v) {
 #pragma unroll

@@ -161,24 +161,6 @@ embedding_bwd_kernel(const float* __restrict__ dy, const int32_t* __restrict__ i
 // --------------------------------------------------------------------------------- Dropout ---
 // Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3"): counter = element index / 4 plus the
 // caller's offset, key = the 64-bit seed.  Element i takes word i % 4 of its counter's output.
-__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
-  const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
-  const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n1 = (uint32_t)p1;
-  const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1, n3 = (uint32_t)p0;
-  c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
-}
-__device__ __forceinline__ void philox4x32_10(uint64_t counter, uint64_t seed, uint32_t (&out)[4]) {
-  uint32_t c[4] = {(uint32_t)counter, (uint32_t)(counter >> 32), 0u, 0u};
-  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    philox_round(c, k0, k1);
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
-  }
-  out[0] = c[0]; out[1] = c[1]; out[2] = c[2]; out[3] = c[3];
-}
-
 __global__ void __launch_bounds__(FT)
 dropout_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t count, float p, float scale, uint64_t seed,
                uint64_t offset) {

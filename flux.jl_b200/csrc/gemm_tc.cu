@@ -115,7 +115,7 @@ template <bool A_MN, bool B_MN, int BN, int PASSES, bool PAIR, int SG>
 __global__ void __launch_bounds__(Cfg<BN, PASSES, PAIR, SG>::NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                float* __restrict__ C, int64_t ldc, float* __restrict__ Z, const float* __restrict__ bias_n, int M,
-               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int prefetch_kb, int a3d, int b3d,
+               int N, int K, int act, int accumulate, int32_t* __restrict__ dev_err, int a3d, int b3d,
                const Sched sch) {
   using cfg = Cfg<BN, PASSES, PAIR, SG>;
   constexpr int SPLIT_GROUPS = SG;
@@ -201,21 +201,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer ---
     if (lane == 0) {
       int m0 = 0, nb0 = 0;
-      auto prefetch = [&](int kbp) {
-        const int kp = kbp * BK;
-        if (A_MN) {
-#pragma unroll
-          for (int c = 0; c < BM / 32; ++c) tma_prefetch_2d(&tmA, m0 + 32 * c, kp);
-        } else {
-          tma_prefetch_2d(&tmA, kp, m0);
-        }
-        if (B_MN) {
-#pragma unroll
-          for (int c = 0; c < cfg::BNC / 32; ++c) tma_prefetch_2d(&tmB, nb0 + 32 * c, kp);
-        } else {
-          tma_prefetch_2d(&tmB, kp, nb0);
-        }
-      };
       int it = 0;   // k-blocks issued so far over all tiles: names the stage and its phase
       bool ok = true;
       WorkIter wi(sch, cid, G);
@@ -223,11 +208,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       while (ok && wi.next(sch, cid, G, num_kb, p)) {
         m0 = tile_m0(p.tile);
         nb0 = tile_n0(p.tile) + (PAIR ? cfg::BNC * (int)rank : 0);
-        for (int kb = p.kb0; kb < p.kb0 + prefetch_kb && kb < p.kb1; ++kb) prefetch(kb);
         for (int kb = p.kb0; kb < p.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-          if (prefetch_kb > 0 && kb + prefetch_kb < p.kb1) prefetch(kb + prefetch_kb);
           ok = mbar_wait_cluster(empty_bar(s), ph ^ 1u, s_abort);
           if (!ok) break;
           mbar_arrive_expect_tx(full_bar(s), (uint32_t)(cfg::A_BYTES + cfg::B_BYTES));
@@ -571,32 +554,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // --------------------------------------------------------------------------- host side ---
-// FLUXB200_PREFETCH = n: the producer prefetches tiles into L2 n k-blocks ahead of its loads (0 = off, default).
-int prefetch_from_env() {
-  static int n = -1;
-  if (n < 0) {
-    const char* e = getenv("FLUXB200_PREFETCH");
-    n = e ? atoi(e) : 0;
-    if (n < 0 || n > 64) n = 0;
-  }
-  return n;
-}
-
 // Workspace of the split-tile schedule, owned by the context: slots for partial sums and the tickets.
 struct GemmWorkspace {
   float* ws;
   int* tickets;
 };
-
-// FLUXB200_STREAMK = 0 keeps every tile whole; 2 cuts every incomplete last wave, however full.
-int stream_k_mode() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("FLUXB200_STREAMK");
-    on = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
-  }
-  return on;
-}
 
 // 3-d view {32, K, MN / 32} of an MN-major matrix (row k holds MN contiguous floats): box {32, BK, chunks}.
 // Only for MN a multiple of 32, so that no chunk straddles the end of a row.
@@ -659,8 +621,7 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   // gain nothing: the kernel runs at the power limit, where idle SMs let the busy ones clock higher.)
   const int64_t rest = num_tiles % Gmax;
   const GemmWorkspace* gw = (const GemmWorkspace*)ctx->gemm_ws;
-  const int skm = stream_k_mode();
-  if (rest != 0 && (4 * rest < 3 * Gmax || skm == 2) && sch.nu > 1 && rest * sch.nu < 0x40000000 && gw != nullptr && skm != 0) {
+  if (rest != 0 && 4 * rest < 3 * Gmax && sch.nu > 1 && rest * sch.nu < 0x40000000 && gw != nullptr) {
     sch.dp_tiles = (int)(num_tiles - rest);
     sch.U = (int)(rest * sch.nu);
     sch.ws = gw->ws;
@@ -681,7 +642,7 @@ int32_t launch_variant(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) 
   lc.attrs = attr;
   lc.numAttrs = 1;
   FB_CUDA(cudaLaunchKernelEx(&lc, kern, tmA, tmB, a.C, a.ldc, a.Z, a.bias_n, (int)a.M, (int)a.N, (int)a.K, a.act,
-                             a.accumulate, ctx->dev_error, prefetch_from_env(), a3d, b3d, sch));
+                             a.accumulate, ctx->dev_error, a3d, b3d, sch));
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
@@ -704,18 +665,10 @@ int32_t launch_layout(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& a) {
   return launch_layout_sg<BN, PASSES, PAIR, (PAIR ? 4 : 2)>(ctx, stream, a);
 }
 
-// FLUXB200_PAIR = 0 keeps every problem on one-CTA tiles.  Measured on B200 (4096^3, 3xTF32, persistent kernels):
-// one-CTA 128 x 256 tiles 200-213 TFLOP/s (shared-memory bandwidth bound: every MMA re-reads all 256 B columns),
-// two-CTA 256 x 256 tiles 215-232 TFLOP/s (each CTA reads only its 128 B columns).
-bool pair_kernel_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("FLUXB200_PAIR");
-    on = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return on != 0;
-}
-
+// Measured on B200 (4096^3, 3xTF32, persistent kernels): one-CTA 128 x 256 tiles 200-213 TFLOP/s (every MMA re-reads
+// all 256 B columns from shared memory), two-CTA 256 x 256 tiles 215-232 TFLOP/s (each CTA reads only its 128 B
+// columns).  At 1024 x 4096 x 4096 (one wave of 64 two-CTA tiles on 74 SM pairs) both, and cutting every tile along
+// K over all pairs, take 0.204-0.207 ms: what is left there is the unoverlapped prologue and epilogue of a single tile.
 }  // namespace
 
 bool fb_gemm_tc_supported(const fb_gemm_args& a) {
@@ -740,16 +693,10 @@ int32_t fb_gemm_tc_launch(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_args& 
   // split / barrier round trip, so one 86 %-full wave of them beats two waves of 128 x 128 tiles
   const int64_t tiles256 = ((a.M + BM - 1) / BM) * ((a.N + 255) / 256);
   const bool narrow = (a.N <= 128) || (2 * tiles256 <= ctx->sm_count);
-  // FLUXB200_GEMM_TILE = one256 | one128 forces the one-CTA tile of that width (measurement aid)
-  static const char* tile_env = getenv("FLUXB200_GEMM_TILE");
-  if (passes == 3 && tile_env != nullptr && !passes_flag_pair) {
-    if (strcmp(tile_env, "one256") == 0) return launch_layout<256, 3, false>(ctx, stream, a);
-    if (strcmp(tile_env, "one128") == 0) return launch_layout<128, 3, false>(ctx, stream, a);
-  }
   if (passes == 3) {
     // two-CTA 256 x 256 tiles once there are enough of them to occupy a good part of the SM pairs
     const int64_t pair_tiles = ((a.M + 255) / 256) * ((a.N + 255) / 256);
-    if (a.M >= 256 && a.N >= 256 && (passes_flag_pair || (pair_kernel_enabled() && 4 * pair_tiles >= ctx->sm_count)))
+    if (a.M >= 256 && a.N >= 256 && (passes_flag_pair || 4 * pair_tiles >= ctx->sm_count))
       return launch_layout<256, 3, true>(ctx, stream, a);
     if (narrow) return launch_layout<128, 3, false>(ctx, stream, a);
     return launch_layout<256, 3, false>(ctx, stream, a);

@@ -38,6 +38,52 @@ reduce_slots_kernel(SlotTable t, int nslots, float* __restrict__ out, int64_t co
   }
 }
 
+// Copies to different peers are issued on different auxiliary streams so that several copy engines work at once
+// (one stream's copies run one after the other and reach less than half of the NVLink bandwidth).  The fork / join
+// events make the auxiliary work part of the caller's stream order, also under stream capture.  The pool is created
+// by fb_peer_alloc, outside any capture.
+constexpr int PEER_AUX = 8;
+constexpr int PEER_MAX_DEVICES = 64;
+struct PeerPool {
+  bool ready = false;
+  cudaStream_t aux[PEER_AUX];
+  cudaEvent_t fork, join[PEER_AUX];
+};
+PeerPool g_peer_pool[PEER_MAX_DEVICES];
+
+int32_t peer_pool_create(int device) {
+  if (device < 0 || device >= PEER_MAX_DEVICES) return fb_fail(FB_ERR_UNSUPPORTED, "peer exchange: device index %d not supported", device);
+  PeerPool& pp = g_peer_pool[device];
+  if (pp.ready) return FB_OK;
+  int lo = 0, hi = 0;
+  FB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  for (int i = 0; i < PEER_AUX; ++i) {
+    FB_CUDA(cudaStreamCreateWithPriority(&pp.aux[i], cudaStreamNonBlocking, hi));
+    FB_CUDA(cudaEventCreateWithFlags(&pp.join[i], cudaEventDisableTiming));
+  }
+  FB_CUDA(cudaEventCreateWithFlags(&pp.fork, cudaEventDisableTiming));
+  pp.ready = true;
+  return FB_OK;
+}
+
+// copies[i] = (dst, src) for i < n, all of `bytes` bytes: spread over the auxiliary streams, joined back into `stream`
+int32_t peer_parallel_copies(fb_ctx* ctx, cudaStream_t stream, int n, float* const* dst, const float* const* src, size_t bytes) {
+  PeerPool& pp = g_peer_pool[ctx->device];
+  if (!pp.ready) {
+    for (int i = 0; i < n; ++i) FB_CUDA(cudaMemcpyAsync(dst[i], src[i], bytes, cudaMemcpyDeviceToDevice, stream));
+    return FB_OK;
+  }
+  FB_CUDA(cudaEventRecord(pp.fork, stream));
+  const int used = n < PEER_AUX ? n : PEER_AUX;
+  for (int a = 0; a < used; ++a) FB_CUDA(cudaStreamWaitEvent(pp.aux[a], pp.fork, 0));
+  for (int i = 0; i < n; ++i) FB_CUDA(cudaMemcpyAsync(dst[i], src[i], bytes, cudaMemcpyDeviceToDevice, pp.aux[i % PEER_AUX]));
+  for (int a = 0; a < used; ++a) {
+    FB_CUDA(cudaEventRecord(pp.join[a], pp.aux[a]));
+    FB_CUDA(cudaStreamWaitEvent(stream, pp.join[a], 0));
+  }
+  return FB_OK;
+}
+
 }  // namespace
 
 FB_API int32_t fb_peer_alloc(fb_ctx* ctx, int64_t bytes, void** ptr_out, void* handle_host) {
@@ -45,6 +91,8 @@ FB_API int32_t fb_peer_alloc(fb_ctx* ctx, int64_t bytes, void** ptr_out, void* h
   FB_REQUIRE(ptr_out && handle_host && bytes >= 1, FB_ERR_INVALID_ARG, "fb_peer_alloc: bad arguments");
   *ptr_out = nullptr;
   FB_CUDA(cudaSetDevice(ctx->device));
+  const int32_t pst = peer_pool_create(ctx->device);
+  if (pst != FB_OK) return pst;
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, (size_t)bytes);
   if (e != cudaSuccess) {
@@ -101,13 +149,15 @@ FB_API int32_t fb_peer_scatter_blocks(fb_ctx* ctx, void* stream, const float* bu
   FB_CHECK_CTX(ctx);
   FB_REQUIRE(bucket && peer_stage_host && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && blk >= 1,
              FB_ERR_INVALID_ARG, "fb_peer_scatter_blocks: bad arguments (ranks %d, rank %d, block %lld)", nranks, rank, (long long)blk);
+  float* dst[PEER_MAX_RANKS];
+  const float* src[PEER_MAX_RANKS];
   for (int i = 1; i < nranks; ++i) {
     const int p = (rank + i) % nranks;     // every rank starts with a different peer
     FB_REQUIRE(peer_stage_host[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_scatter_blocks: peer %d has no staging pointer", p);
-    FB_CUDA(cudaMemcpyAsync(peer_stage_host[p] + (int64_t)rank * blk, bucket + (int64_t)p * blk, (size_t)blk * sizeof(float),
-                            cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    dst[i - 1] = peer_stage_host[p] + (int64_t)rank * blk;
+    src[i - 1] = bucket + (int64_t)p * blk;
   }
-  return FB_OK;
+  return peer_parallel_copies(ctx, (cudaStream_t)stream, nranks - 1, dst, src, (size_t)blk * sizeof(float));
 }
 
 FB_API int32_t fb_peer_gather_block(fb_ctx* ctx, void* stream, const float* my_block, float* const* peer_dst_host, int32_t nranks,
@@ -115,12 +165,15 @@ FB_API int32_t fb_peer_gather_block(fb_ctx* ctx, void* stream, const float* my_b
   FB_CHECK_CTX(ctx);
   FB_REQUIRE(my_block && peer_dst_host && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && blk >= 1,
              FB_ERR_INVALID_ARG, "fb_peer_gather_block: bad arguments (ranks %d, rank %d, block %lld)", nranks, rank, (long long)blk);
+  float* dst[PEER_MAX_RANKS];
+  const float* src[PEER_MAX_RANKS];
   for (int i = 1; i < nranks; ++i) {
     const int p = (rank + i) % nranks;
     FB_REQUIRE(peer_dst_host[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_gather_block: peer %d has no destination pointer", p);
-    FB_CUDA(cudaMemcpyAsync(peer_dst_host[p], my_block, (size_t)blk * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    dst[i - 1] = peer_dst_host[p];
+    src[i - 1] = my_block;
   }
-  return FB_OK;
+  return peer_parallel_copies(ctx, (cudaStream_t)stream, nranks - 1, dst, src, (size_t)blk * sizeof(float));
 }
 
 FB_API int32_t fb_reduce_slots(fb_ctx* ctx, void* stream, int32_t nslots, const float* const* slots_host, float* out, int64_t count,

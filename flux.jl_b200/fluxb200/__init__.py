@@ -10,7 +10,7 @@ from .layers import (ArgumentError, AttnScores, BatchNorm, CausalMask, Chain, De
                      GRUCell, GRUv3, GRUv3Cell, GroupNorm, InstanceNorm, LSTM, LSTMCell, Layer, LayerNorm, MultiHeadAttention,
                      RNN, RNNCell, Recurrence, dot_product_attention, make_causal_mask, testmode, trainables, trainmode, bf16,
                      f32)
-from .train import (Adam, Descent, DomainError, GraphedGradient, GraphedTrainStep, OneHotLabels, gradient, logitcrossentropy, onehotbatch, setup, scale, sum_abs2, sum_all,
+from .train import (add, Adam, Descent, DomainError, GraphedGradient, GraphedTrainStep, OneHotLabels, gradient, logitcrossentropy, onehotbatch, setup, scale, sum_abs2, sum_all,
                     train, trainstep, update, withgradient)
 from .init import create_bias, glorot_uniform, nfan, ones32, rand32, randn32, seed, zeros32
 from .loading import load_checkpoint, load_opt_state, loadmodel, opt_state, save_checkpoint, state

@@ -578,29 +578,50 @@ def make_causal_mask(x=None):
 
 
 class AttnScores:
-    """The second return value of MultiHeadAttention: alpha[kv, q, heads, batch], materialised on first use
-    (attention.jl:128-132 returns it eagerly; here it costs nothing unless it is read)."""
+    """The second return value of MultiHeadAttention: alpha[kv, q, heads, batch] (after dropout, as NNlib returns it),
+    materialised on first use (attention.jl:128-132 returns it eagerly; here it costs nothing unless it is read).
+    Materialising it under `withgradient` makes it an output of the attention call on the tape, so a loss may use it."""
 
-    def __init__(self, q, k, lse, mask, causal, nheads, dims):
+    def __init__(self, q, k, lse, mask, causal, nheads, dims, extras, entry=None):
         self._args = (q, k, lse, mask, causal, nheads, dims)
+        self._extras = extras          # (bias, stride_h, stride_b, p, seed, offset)
+        self._entry = entry            # the tape entry of the attention call (its output list grows by alpha)
         self._val = None
         self.size = dims
 
     def materialize(self) -> B200Array:
         if self._val is None:
             q, k, lse, mask, causal, nheads, (Lk, Lq, H, B) = self._args
+            bias, sh, sb, p, seed, off = self._extras
             ctx = context()
             a = empty((Lk, Lq, H, B))
-            lib.call("fb_attn_scores", ctx.handle, ctx.stream, q.ptr, k.ptr, _ptr(mask), lse.ptr, a.ptr, q.size[0], Lq, Lk, B,
-                     nheads, 1 if causal else 0)
+            lib.call("fb_attn_scores_ex", ctx.handle, ctx.stream, q.ptr, k.ptr, _ptr(mask), _ptr(bias), sh, sb, p, seed, off, lse.ptr,
+                     a.ptr, q.size[0], Lq, Lk, B, nheads, 1 if causal else 0)
             self._val = a
+            if Tape.active and self._entry is not None:
+                self._entry[0].append(a)
+                Tape.tracked.add(id(a))
         return self._val
 
 
-def dot_product_attention(q: B200Array, k: B200Array, v: B200Array, bias=None, nheads=1, mask=None):
-    """NNlib.dot_product_attention(q, k, v, bias; nheads, mask) -> (x, alpha) for 3-d B200 arrays."""
-    if bias is not None:
-        raise lib.FluxB200Error(-7, "additive attention bias has no B200 kernel; pass a boolean mask instead")
+def _attention_bias(bias, Lk, Lq, H, B):
+    """bias broadcastable to (kv_len, q_len, nheads, batch) (attention.jl:40-44) -> (device array, head stride, batch stride)."""
+    if bias is None:
+        return None, 0, 0
+    if isinstance(bias, np.ndarray):
+        bias = gpu(bias.astype(np.float32))
+    bias = to_f32(bias)
+    size = tuple(bias.size) + (1,) * (4 - bias.ndim)
+    if len(size) != 4 or size[0] != Lk or size[1] != Lq or size[2] not in (1, H) or size[3] not in (1, B):
+        raise DimensionMismatch(f"bias of size {bias.size} is not broadcastable to (kv_len, q_len, nheads, batch) = ({Lk}, {Lq}, {H}, {B})")
+    sh = Lk * Lq if size[2] == H and H > 1 else 0
+    sb = Lk * Lq * size[2] if size[3] == B and B > 1 else 0
+    return bias, sh, sb
+
+
+def dot_product_attention(q: B200Array, k: B200Array, v: B200Array, bias=None, nheads=1, mask=None, fdrop=None):
+    """NNlib.dot_product_attention(q, k, v, bias; nheads, mask, fdrop) -> (x, alpha) for 3-d B200 arrays.  `fdrop` is a
+    Dropout layer acting on the attention weights (MultiHeadAttention's `attn_drop`)."""
     low = is_bf16(q)
     q, k, v = to_f32(q), to_f32(k), to_f32(v)
     E, Lq, B = q.size
@@ -615,20 +636,28 @@ def dot_product_attention(q: B200Array, k: B200Array, v: B200Array, bias=None, n
         m = gpu(np.asarray(mask, dtype=np.uint8)) if isinstance(mask, np.ndarray) else mask
         if m.size != (Lk, Lq):
             raise DimensionMismatch(f"mask of size {m.size} must be (kv_len, q_len) = ({Lk}, {Lq})")
+    bias_a, sh, sb = _attention_bias(bias, Lk, Lq, nheads, B)
+    p, seed, off = 0.0, 0, 0
+    if fdrop is not None and fdrop.p > 0 and fdrop._isactive():
+        p, seed, off = fdrop.p, fdrop.seed, fdrop.next_offset(Lk * Lq * nheads * B)
+    extras = (bias_a, sh, sb, p, seed, off)
     ctx = context()
     o, lse = empty((Ev, Lq, B)), empty((Lq, nheads, B))
-    lib.call("fb_attn_fwd", ctx.handle, ctx.stream, q.ptr, k.ptr, v.ptr, _ptr(m), o.ptr, lse.ptr, E, Ev, Lq, Lk, B, nheads,
-             1 if causal else 0)
+    lib.call("fb_attn_fwd_ex", ctx.handle, ctx.stream, q.ptr, k.ptr, v.ptr, _ptr(m), _ptr(bias_a), sh, sb, p, seed, off, o.ptr, lse.ptr,
+             E, Ev, Lq, Lk, B, nheads, 1 if causal else 0)
+    entry = None
     if Tape.active:
         def pullback(gs):
-            do = gs[0]
+            do = gs[0] if gs[0] is not None else zeros(o.size)
+            dalpha = gs[1] if len(gs) > 1 else None
             dq, dk, dv = empty(q.size), empty(k.size), empty(v.size)
-            lib.call("fb_attn_bwd", ctx.handle, ctx.stream, q.ptr, k.ptr, v.ptr, _ptr(m), o.ptr, lse.ptr, do.ptr, dq.ptr,
-                     dk.ptr, dv.ptr, E, Ev, Lq, Lk, B, nheads, 1 if causal else 0)
+            lib.call("fb_attn_bwd_ex", ctx.handle, ctx.stream, q.ptr, k.ptr, v.ptr, _ptr(m), _ptr(bias_a), sh, sb, p, seed, off, o.ptr,
+                     lse.ptr, do.ptr, _ptr(dalpha), dq.ptr, dk.ptr, dv.ptr, E, Ev, Lq, Lk, B, nheads, 1 if causal else 0)
             return [(q, dq), (k, dk), (v, dv)]
 
         Tape.record(o, [q, k, v], pullback)
-    scores = AttnScores(q, k, lse, m, causal, nheads, (Lk, Lq, nheads, B))
+        entry = Tape.entries[-1]
+    scores = AttnScores(q, k, lse, m, causal, nheads, (Lk, Lq, nheads, B), extras, entry)
     return (to_bf16(o) if low else o), scores
 
 
@@ -639,7 +668,7 @@ class MultiHeadAttention(Layer):
     _trainable = ("q_proj", "k_proj", "v_proj", "out_proj")
 
     def __init__(self, Wq, Wk=None, Wv=None, Wo=None, nheads=8, biases=None, precision="default", bias=False,
-                 init=glorot_uniform):
+                 init=glorot_uniform, dropout_prob=0.0):
         bq = bk = bv = bo = False
         if biases is not None:
             bq, bk, bv, bo = biases
@@ -664,7 +693,7 @@ class MultiHeadAttention(Layer):
         self.k_proj = Dense(Wk, bk, precision=precision)
         self.v_proj = Dense(Wv, bv, precision=precision)
         self.out_proj = Dense(Wo, bo, precision=precision)
-        self.attn_drop = None   # Dropout(0.0)
+        self.attn_drop = Dropout(float(dropout_prob))
         qk, vd = self.q_proj.weight.size[0], self.v_proj.weight.size[0]
         if qk % nheads:
             raise ArgumentError(f"qk_dim = {qk} should be divisible by nheads = {nheads}")
@@ -680,7 +709,7 @@ class MultiHeadAttention(Layer):
         q = self.q_proj(q_in)
         k = self.k_proj(k_in)
         v = self.v_proj(v_in)
-        x, alpha = dot_product_attention(q, k, v, bias, nheads=self.nheads, mask=mask)
+        x, alpha = dot_product_attention(q, k, v, bias, nheads=self.nheads, mask=mask, fdrop=self.attn_drop)
         return self.out_proj(x), alpha
 
 

@@ -105,6 +105,10 @@ PROTOTYPES = {
     "fb_attn_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i32]),
     "fb_attn_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i32]),
     "fb_attn_scores": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32]),
+    "fb_attn_fwd_ex": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, C.c_uint64, C.c_uint64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i32]),
+    "fb_attn_bwd_ex": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, C.c_uint64, C.c_uint64, _p, _p, _p, _p, _p, _p, _p,
+                              _i64, _i64, _i64, _i64, _i64, _i32, _i32]),
+    "fb_attn_scores_ex": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, C.c_uint64, C.c_uint64, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32]),
     "fb_comm_get_unique_id": (_i32, [_p]),
     "fb_comm_init_rank": (_i32, [_p, _p, _i32, _i32, C.POINTER(_p)]),
     "fb_comm_destroy": (_i32, [_p]),

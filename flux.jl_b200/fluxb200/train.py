@@ -109,6 +109,19 @@ def sum_all(y: B200Array) -> B200Array:
     return out
 
 
+def add(a: B200Array, b: B200Array) -> B200Array:
+    """a + b for two arrays of one size (e.g. two loss terms); the cotangent goes to both."""
+    a, b = to_f32(a), to_f32(b)
+    if a.size != b.size:
+        raise DimensionMismatch(f"dimensions must match: a has dims {a.size}, b has dims {b.size}")
+    ctx = context()
+    out = B200Array(a.t.clone(), a.size)
+    lib.call("fb_axpy", ctx.handle, ctx.stream, 1.0, b.ptr, out.ptr, out.numel())
+    if Tape.needs(a, b):
+        Tape.record(out, [a, b], lambda gs: [(a, gs[0]), (b, gs[0])])
+    return out
+
+
 def scale(c: float, a: B200Array) -> B200Array:
     """c * a for a Python scalar c."""
     ctx = context()

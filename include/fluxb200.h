@@ -390,6 +390,33 @@ int32_t fb_attn_scores(fb_ctx* ctx, void* stream, const float* q, const float* k
                        const float* lse, float* alpha, int64_t e_dim, int64_t lq, int64_t lk,
                        int64_t batch, int32_t nheads, int32_t causal);
 
+/* The same three calls with the remaining arguments of NNlib.dot_product_attention(q, k, v, bias; nheads, mask, fdrop)
+ * (src/layers/attention.jl:120-128):
+ *  - bias (optional): added to the scaled scores before the mask and the softmax.  It is read at
+ *    bias[j + lk * i + bias_stride_h * h + bias_stride_b * b] for key j, query i: a [lk, lq] bias shared by all heads
+ *    and batch entries has both strides 0, a full [lk, lq, h, B] bias has strides lk*lq and lk*lq*h.  The bias gets no
+ *    gradient (it is a constant of the layer call, attention.jl:40-44).
+ *  - p_drop, seed, offset: dropout on the attention weights (the layer's `attn_drop`, attention.jl:91): weight
+ *    (i, j) of head h, batch entry b is kept iff element ((b * nheads + h) * lq + i) * lk + j of the mask stream of
+ *    fb_dropout(seed, offset) is kept, and scaled by 1 / (1 - p_drop).  fb_attn_scores_ex returns the weights after
+ *    dropout, as the reference does.
+ *  - dalpha (fb_attn_bwd_ex, optional [lk, lq, h, B]): a cotangent of the returned attention weights, for losses
+ *    that read them (test/layers/attention.jl:56-61).
+ * With any of these present the general (FMA) kernels run; without them the calls are the ones above. */
+int32_t fb_attn_fwd_ex(fb_ctx* ctx, void* stream, const float* q, const float* k, const float* v, const uint8_t* mask,
+                       const float* bias, int64_t bias_stride_h, int64_t bias_stride_b, float p_drop, uint64_t seed,
+                       uint64_t offset, float* o, float* lse, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk,
+                       int64_t batch, int32_t nheads, int32_t causal);
+int32_t fb_attn_bwd_ex(fb_ctx* ctx, void* stream, const float* q, const float* k, const float* v, const uint8_t* mask,
+                       const float* bias, int64_t bias_stride_h, int64_t bias_stride_b, float p_drop, uint64_t seed,
+                       uint64_t offset, const float* o, const float* lse, const float* dout, const float* dalpha,
+                       float* dq, float* dk, float* dv, int64_t e_dim, int64_t ev_dim, int64_t lq, int64_t lk,
+                       int64_t batch, int32_t nheads, int32_t causal);
+int32_t fb_attn_scores_ex(fb_ctx* ctx, void* stream, const float* q, const float* k, const uint8_t* mask,
+                          const float* bias, int64_t bias_stride_h, int64_t bias_stride_b, float p_drop, uint64_t seed,
+                          uint64_t offset, const float* lse, float* alpha, int64_t e_dim, int64_t lq, int64_t lk,
+                          int64_t batch, int32_t nheads, int32_t causal);
+
 /* ------------------------------------------------------------------- DistributedUtils -- */
 
 /* NCCL unique id (128 bytes) created on one rank and handed to the others by the caller's bootstrap

@@ -662,12 +662,13 @@ def _apply_ji(a, w):
     return np.matmul(a.transpose(3, 0, 1, 2), w.transpose(3, 2, 0, 1)).transpose(1, 2, 3, 0)
 
 
-def dot_product_attention(q, k, v, bias=None, nheads=1, mask=None, return_cache=False):
+def dot_product_attention(q, k, v, bias=None, nheads=1, mask=None, return_cache=False, drop=None):
     """q (E, Lq, B), k (E, Lk, B), v (Ev, Lk, B) -> x (Ev, Lq, B), alpha (Lk, Lq, h, B).
 
     Head h is the contiguous feature block h*d:(h+1)*d of the embed axis; scores
     k'q / sqrt(d); additive bias; boolean mask (true = keep, masked logits -> -inf);
-    softmax over the kv axis; x = v alpha.
+    softmax over the kv axis; `fdrop` on the weights (attention.jl:91, 128; here `drop` = keep-mask / (1 - p) of
+    alpha's shape); x = v alpha.  The returned alpha is the one after dropout, as in NNlib.
     """
     E, Lq, B = q.shape
     Ev, Lk, _ = v.shape
@@ -686,20 +687,21 @@ def dot_product_attention(q, k, v, bias=None, nheads=1, mask=None, return_cache=
         logits = np.where(m, logits, -np.inf)
     mx = logits.max(axis=0, keepdims=True)
     e = np.exp(logits - mx)
-    alpha = e / e.sum(axis=0, keepdims=True)
+    alpha0 = e / e.sum(axis=0, keepdims=True)
+    alpha = alpha0 if drop is None else alpha0 * drop
     xh = _apply_ji(vh, alpha)
     x = xh.reshape(Ev, Lq, B)
     if return_cache:
-        return x, alpha, (qh, kh, vh, scale)
+        return x, alpha, (qh, kh, vh, scale, alpha0)
     return x, alpha
 
 
-def dot_product_attention_bwd(q, k, v, dx, bias=None, nheads=1, mask=None, dalpha=None):
-    """Reverse of dot_product_attention: dV = dO alpha', dalpha = V' dO,
-    dS = alpha .* (dalpha - sum(alpha .* dalpha)), dQ = K dS scale, dK = Q dS' scale."""
+def dot_product_attention_bwd(q, k, v, dx, bias=None, nheads=1, mask=None, dalpha=None, drop=None):
+    """Reverse of dot_product_attention: dV = dO alpha', dalpha = V' dO (+ the cotangent of the returned weights),
+    through the dropout factor, dS = alpha0 .* (dalpha - sum(alpha0 .* dalpha)), dQ = K dS scale, dK = Q dS' scale."""
     E, Lq, B = q.shape
     Ev, Lk, _ = v.shape
-    x, alpha, (qh, kh, vh, scale) = dot_product_attention(q, k, v, bias, nheads, mask, return_cache=True)
+    x, alpha, (qh, kh, vh, scale, alpha0) = dot_product_attention(q, k, v, bias, nheads, mask, return_cache=True, drop=drop)
     d = E // nheads
     dv = Ev // nheads
     dxh = dx.reshape(nheads, dv, Lq, B)
@@ -707,7 +709,9 @@ def dot_product_attention_bwd(q, k, v, dx, bias=None, nheads=1, mask=None, dalph
     da = _contract_c(vh, dxh)
     if dalpha is not None:
         da = da + dalpha
-    ds = alpha * (da - (alpha * da).sum(axis=0, keepdims=True))
+    if drop is not None:
+        da = da * drop
+    ds = alpha0 * (da - (alpha0 * da).sum(axis=0, keepdims=True))
     dqh = _apply_ji(kh, ds) * scale
     dkh = _apply_ji(qh, ds.transpose(1, 0, 2, 3)) * scale
     return dqh.reshape(E, Lq, B), dkh.reshape(E, Lk, B), dvh.reshape(Ev, Lk, B)

@@ -460,3 +460,44 @@ def test_layer_applied_twice_accumulates_into_the_gradient_bucket(F):
     close(F.cpu(sink.views[id(layer.bias)]), db1 + db2, name="db in the bucket", rtol=2e-4, atol_scale=2e-4)
     close(F.cpu(g["layers"][0]["weight"]), dW1 + dW2, name="dW in the tree", rtol=2e-4, atol_scale=2e-4)
     assert all(sink.launched)
+
+
+def test_multiheadattention_bias_dropout_and_loss_on_the_weights(F):
+    """test/layers/attention.jl:45-61: an additive bias that masks gives the causal zero pattern; a loss that uses the
+    returned attention weights differentiates; dropout on the weights is active under `withgradient` only."""
+    rng = np.random.default_rng(9)
+    E, S, B, H = 32, 12, 2, 4
+    Ws = [O.glorot_uniform(rng, E, E) for _ in range(4)]
+    x = rng.normal(size=(E, S, B)).astype(np.float32)
+    mha, xg = F.MultiHeadAttention(*Ws, nheads=H), F.gpu(x)
+    bias = np.where(O.make_causal_mask(S), 0.0, -1e9).astype(np.float32)           # used as a mask
+    y, alpha = mha(xg, bias=bias)
+    a = F.cpu(alpha.materialize())
+    assert (a[1, 0, :, :] == 0).all() and np.allclose(a[:, :, 0, 0], np.triu(a[:, :, 0, 0]))
+    W64 = [w.astype(np.float64) for w in Ws]
+    yref, aref = O.mha_fwd(*W64, x.astype(np.float64), nheads=H, mask=O.make_causal_mask(S))
+    close(F.cpu(y), yref)
+    close(a, aref, atol_scale=1e-5)
+
+    def loss(m):                                                                      # sum(abs2, y) + sum(abs2, alpha)
+        yy, al = m(xg, mask=F.make_causal_mask())
+        return F.add(F.sum_abs2(yy), F.sum_abs2(al.materialize()))
+    val, (g,) = F.withgradient(loss, mha)
+    close(val, (yref ** 2).sum() + (aref ** 2).sum())
+    x64 = x.astype(np.float64)
+    qq, kk, vv = (O.dense_fwd(w, None, x64) for w in W64[:3])
+    xa, _ = O.dot_product_attention(qq, kk, vv, None, H, O.make_causal_mask(S))
+    dWo, _, dxa = O.dense_bwd(W64[3], None, xa, 2 * yref)
+    dq, dk, dv = O.dot_product_attention_bwd(qq, kk, vv, dxa, None, H, O.make_causal_mask(S), dalpha=2 * aref)
+    close(F.cpu(g["q_proj"]["weight"]), O.dense_bwd(W64[0], None, x64, dq)[0], name="dWq", rtol=2e-4, atol_scale=2e-4)
+    close(F.cpu(g["k_proj"]["weight"]), O.dense_bwd(W64[1], None, x64, dk)[0], name="dWk", rtol=2e-4, atol_scale=2e-4)
+    close(F.cpu(g["out_proj"]["weight"]), dWo, name="dWo", rtol=2e-4, atol_scale=2e-4)
+    # dropout on the weights: inactive at inference, active (and different from call to call) in a gradient call
+    md = F.MultiHeadAttention(*Ws, nheads=H, dropout_prob=0.5)
+    y0 = F.cpu(md(xg)[0])
+    close(y0, O.mha_fwd(*W64, x64, nheads=H)[0])
+    F.trainmode(md)
+    y1, y2 = F.cpu(md(xg)[0]), F.cpu(md(xg)[0])
+    assert np.abs(y1 - y0).max() > 1e-3 and np.abs(y1 - y2).max() > 1e-3
+    _, al = md(xg)
+    assert 0.3 < (F.cpu(al.materialize()) == 0).mean() < 0.7

@@ -651,3 +651,53 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_works():
         assert st == -1               # the self test refuses long waits
     finally:
         lib.call("fb_ctx_destroy", h)
+
+
+@pytest.mark.parametrize("E,heads,Lq,Lk,B", [(8, 2, 5, 7, 3), (128, 2, 70, 130, 2), (96, 4, 64, 64, 1)])
+@pytest.mark.parametrize("bias_kind,p,with_dalpha,causal", [("shared", 0.0, False, 0), ("full", 0.0, True, 0), (None, 0.3, False, 1),
+                                                          ("heads", 0.25, True, 0)])
+def test_attention_bias_dropout_alpha_cotangent(fb, E, heads, Lq, Lk, B, bias_kind, p, with_dalpha, causal):
+    """The remaining arguments of NNlib.dot_product_attention (src/layers/attention.jl:120-128): additive bias
+    (broadcast over heads / batch or full), dropout on the attention weights (mask regenerated by the oracle from the
+    same counter-based stream), and a cotangent of the returned weights (test/layers/attention.jl:45-61)."""
+    if causal and Lq != Lk:
+        pytest.skip("causal masks are square in the reference")
+    rng = np.random.default_rng(E + Lq + Lk + B + heads)
+    q = rng.normal(size=(E, Lq, B)).astype(np.float32)
+    k = rng.normal(size=(E, Lk, B)).astype(np.float32)
+    v = rng.normal(size=(E, Lk, B)).astype(np.float32)
+    do = rng.normal(size=(E, Lq, B)).astype(np.float32)
+    bias, sh, sb = None, 0, 0
+    if bias_kind == "shared":
+        bias = rng.normal(size=(Lk, Lq)).astype(np.float32)
+    elif bias_kind == "heads":
+        bias, sh = rng.normal(size=(Lk, Lq, heads, 1)).astype(np.float32), Lk * Lq
+    elif bias_kind == "full":
+        bias, sh, sb = rng.normal(size=(Lk, Lq, heads, B)).astype(np.float32), Lk * Lq, Lk * Lq * heads
+    seed, off = 1234567, 17
+    drop = None
+    if p > 0:
+        drop = O.dropout_mask(Lk * Lq * heads * B, p, seed, off).reshape((Lk, Lq, heads, B), order="F") / (1 - p)
+    dalpha = rng.normal(size=(Lk, Lq, heads, B)).astype(np.float32) if with_dalpha else None
+    mask = O.make_causal_mask(Lq) if causal else None
+    tq, tk, tv, tdo = dev(q), dev(k), dev(v), dev(do)
+    tb = dev(bias) if bias is not None else None
+    tda = dev(dalpha) if with_dalpha else None
+    o, lse, alpha = dempty(E, Lq, B), dempty(Lq, heads, B), dempty(Lk, Lq, heads, B)
+    fb.call("fb_attn_fwd_ex", P(tq), P(tk), P(tv), None, P(tb), sh, sb, p, seed, off, P(o), P(lse), E, E, Lq, Lk, B, heads, causal)
+    fb.call("fb_attn_scores_ex", P(tq), P(tk), None, P(tb), sh, sb, p, seed, off, P(lse), P(alpha), E, Lq, Lk, B, heads, causal)
+    q64, k64, v64, do64 = f64(q, k, v, do)
+    b64 = None if bias is None else bias.astype(np.float64)
+    oref, aref = O.dot_product_attention(q64, k64, v64, b64, heads, mask, drop=drop)
+    close(host(o, (E, Lq, B)), oref, name="o")
+    close(host(alpha, (Lk, Lq, heads, B)), aref, name="alpha", atol_scale=1e-5)
+    dq, dk, dv = dempty(E, Lq, B), dempty(E, Lk, B), dempty(E, Lk, B)
+    fb.call("fb_attn_bwd_ex", P(tq), P(tk), P(tv), None, P(tb), sh, sb, p, seed, off, P(o), P(lse), P(tdo), P(tda), P(dq), P(dk), P(dv),
+            E, E, Lq, Lk, B, heads, causal)
+    rq, rk, rv = O.dot_product_attention_bwd(q64, k64, v64, do64, b64, heads, mask, dalpha=None if dalpha is None else dalpha.astype(np.float64),
+                                             drop=drop)
+    close(host(dq, (E, Lq, B)), rq, name="dq", rtol=2e-4, atol_scale=2e-4)
+    close(host(dk, (E, Lk, B)), rk, name="dk", rtol=2e-4, atol_scale=2e-4)
+    close(host(dv, (E, Lk, B)), rv, name="dv", rtol=2e-4, atol_scale=2e-4)
+    st, msg = fb.status("fb_attn_fwd_ex", P(tq), P(tk), P(tv), None, None, 0, 0, 1.0, 0, 0, P(o), P(lse), E, E, Lq, Lk, B, heads, 0)
+    assert st == -1 and "dropout probability" in msg

@@ -211,6 +211,24 @@ def test_attention_bwd_fd():
         fd_check(loss, (*W, x), g, i, rtol=2e-5, atol=1e-6)
 
 
+def test_attention_bias_dropout_and_alpha_cotangent_fd():
+    """dot_product_attention with an additive bias, dropout on the weights and a loss that also reads the returned
+    weights (test/layers/attention.jl:45-61): finite differences of q, k, v."""
+    rng = np.random.default_rng(8)
+    E, H, Lq, Lk, B = 4, 2, 3, 5, 2
+    q, k, v = rng.normal(size=(E, Lq, B)), rng.normal(size=(E, Lk, B)), rng.normal(size=(E, Lk, B))
+    bias = rng.normal(size=(Lk, Lq, H, 1))
+    drop = (rng.random((Lk, Lq, H, B)) > 0.3) / 0.7
+    wx, wa = rng.normal(size=(E, Lq, B)), rng.normal(size=(Lk, Lq, H, B))
+
+    def loss(q_, k_, v_):
+        x, a = O.dot_product_attention(q_, k_, v_, bias, H, None, drop=drop)
+        return (x * wx).sum() + (a * wa).sum()
+    grads = O.dot_product_attention_bwd(q, k, v, wx, bias, H, None, dalpha=wa, drop=drop)
+    for i, g in enumerate(grads):
+        fd_check(loss, (q, k, v), g, i, rtol=2e-5, atol=1e-6)
+
+
 # ---- bf16 / init: test/utils.jl:311, 53-59, 95-104 -----------------------------------------
 def test_bf16_exact_and_rounding():
     v = np.array([1, 1.5, -2.25, 96], dtype=np.float32)
