@@ -352,7 +352,8 @@ def run_ours(args):
     else:
         # the one-launch train step: forward, backward, bucketed all-reduce and Adam replayed from a CUDA graph
         k0 = lib.raw().fb_kernel_launches()
-        gstep = F.GraphedTrainStep(loss_fn, model, opt, (x_dev, y_dev), grad_sink=buckets, shard_optimizer=not args.no_shard)
+        gstep = F.GraphedTrainStep(loss_fn, model, opt, (x_dev, y_dev), grad_sink=buckets, shard_optimizer=not args.no_shard,
+                                   defer_gather=not args.no_defer)
         launches_per_step = (lib.raw().fb_kernel_launches() - k0) // 2      # warm-up pass + captured pass
         step_resident = lambda: gstep(x_dev, y_dev)                          # inputs already in HBM
         # end to end: every step copies one batch from pinned host memory (the batch of the FOLLOWING step, started
@@ -429,6 +430,9 @@ def run_ours(args):
                        "step": "eager launches" if args.eager else "CUDA graph replay (GraphedTrainStep)",
                        "optimizer": ("sharded Adam (reduce-scatter, 1/N update, all-gather per bucket)"
                                      if (not args.eager and getattr(gstep, "sharded", False)) else "Adam on every rank"),
+                       "exchange": ("n/a" if world == 1 else
+                                    ("copy engines over peer memory" if getattr(buckets, "peer", None) is not None else "NCCL collectives") +
+                                    (", parameter gather deferred to the next forward pass" if getattr(buckets, "defer_gather", False) else "")),
                        "batch": "one global draw (seed 100), contiguous column block per rank",
                        "nccl_env": {k: v for k, v in os.environ.items() if k.startswith("NCCL_")},
                        "l2": "inputs larger than L2 (553 MB parameters, >3 GB activations per step)"},
@@ -787,6 +791,8 @@ def main():
                     help="print, on stderr, device time marks of the last step (compute and communication streams)")
     ap.add_argument("--no-shard", dest="no_shard", action="store_true",
                     help="N > 1: all-reduce gradients and run Adam on every rank instead of reduce-scatter + sharded Adam + all-gather")
+    ap.add_argument("--no-defer", dest="no_defer", action="store_true",
+                    help="N > 1: gather the updated parameter blocks inside the step that made them instead of beside the next forward pass")
     ap.add_argument("--eager", action="store_true", help="launch every kernel from the host each step instead of replaying a CUDA graph")
     ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5],
                     help="5 (default): the data-parallel MLP the headline metric is quoted on (at 1 GPU its line carries "

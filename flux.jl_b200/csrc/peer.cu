@@ -1,16 +1,19 @@
-// Gradient exchange over peer memory: the copy-engine form of reduce-scatter and all-gather for the data-parallel
-// step with a sharded optimiser.
+// Gradient exchange over peer memory for the data-parallel step with a sharded optimiser (single node, NVLink /
+// NVSwitch): reduce-scatter and all-gather as kernels that READ the peers' buffers.
 //
-// Every rank owns 1/N of each gradient bucket.  Instead of NCCL's reduce-scatter and all-gather kernels - which hold
-// SMs while the reverse sweep's GEMMs want all of them - the blocks travel as plain device-to-device copies into
-// buffers the peers have mapped (CUDA IPC, NVLink / NVSwitch; the copies run on the copy engines):
-//   1. my block p of the bucket -> slot [me] of peer p's staging area, for every peer p   (fb_peer_scatter_blocks)
-//   2. a one-element NCCL all-reduce on the same stream as a barrier: when it completes here, every peer's copies
-//      (ordered before its barrier kernel in its stream) have landed in my staging area
-//   3. mean over the N slots in rank order, then Adam on my block                           (fb_reduce_slots)
-//   4. my updated parameter block -> its place in every peer's parameter buffer            (fb_peer_gather_block)
-// and one more barrier at the end of the step, before anybody reads the parameters again.  The sums run in a fixed
-// order, so every run and every rank count gives bitwise reproducible averages.
+// Every rank owns 1/N of each gradient bucket.  The gradient buffer and the parameter buffer of every rank are
+// allocated by fb_peer_alloc and mapped by all the others (CUDA IPC).  Per bucket:
+//   1. a one-element NCCL all-reduce on the communication stream as a barrier: when it completes here, every rank's
+//      gradients of the bucket are written (each rank enqueues the barrier behind its own reverse-sweep kernels)
+//   2. fb_reduce_slots: the mean of the N ranks' copies of MY block, read in place from the N gradient buffers in
+//      rank order (plain loads over NVLink, 16 bytes per load, every thread keeps up to 8 loads in flight), then Adam
+//      on my block
+//   3. fb_peer_gather_blocks: the other ranks' updated blocks, read from their parameter buffers into mine - behind
+//      a second barrier inside the step, or behind one barrier at the start of the next step, beside its forward pass
+// Remote memory is only read, never written: the only cross-rank hazard is "a rank overwrites what a peer still
+// reads", and every such write sits behind a barrier the reader joins after its reads (stream order).  The sums run
+// in rank order, so every run gives bitwise the same averages.  NCCL's reduce-scatter and all-gather remain the
+// path when the ranks cannot map each other's memory.
 #include "common.cuh"
 
 namespace {
@@ -22,66 +25,45 @@ __global__ void __launch_bounds__(256)
 reduce_slots_kernel(SlotTable t, int nslots, float* __restrict__ out, int64_t count4, int64_t count, float scale) {
   const int64_t stride = (int64_t)gridDim.x * 256;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < count4; i += stride) {
-    float4 a = __ldcs((const float4*)t.p[0] + i);
-    for (int s = 1; s < nslots; ++s) {
-      const float4 b = __ldcs((const float4*)t.p[s] + i);
-      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < nslots; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s)        // all loads of a group are issued before the first sum waits for one
+        if (s0 + s < nslots) v[s] = __ldcs((const float4*)t.p[s0 + s] + i);
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (s0 + s < nslots) { a.x += v[s].x; a.y += v[s].y; a.z += v[s].z; a.w += v[s].w; }
     }
     a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
     ((float4*)out)[i] = a;
   }
-  // tail (count not a multiple of 4)
+  // tail (count not a multiple of 4, or a pointer off the 16-byte grid)
   for (int64_t i = 4 * count4 + (int64_t)blockIdx.x * 256 + threadIdx.x; i < count; i += stride) {
-    float a = t.p[0][i];
-    for (int s = 1; s < nslots; ++s) a += t.p[s][i];
+    float a = 0.f;
+    for (int s = 0; s < nslots; ++s) a += t.p[s][i];
     out[i] = a * scale;
   }
 }
 
-// Copies to different peers are issued on different auxiliary streams so that several copy engines work at once
-// (one stream's copies run one after the other and reach less than half of the NVLink bandwidth).  The fork / join
-// events make the auxiliary work part of the caller's stream order, also under stream capture.  The pool is created
-// by fb_peer_alloc, outside any capture.
-constexpr int PEER_AUX = 8;
-constexpr int PEER_MAX_DEVICES = 64;
-struct PeerPool {
-  bool ready = false;
-  cudaStream_t aux[PEER_AUX];
-  cudaEvent_t fork, join[PEER_AUX];
-};
-PeerPool g_peer_pool[PEER_MAX_DEVICES];
-
-int32_t peer_pool_create(int device) {
-  if (device < 0 || device >= PEER_MAX_DEVICES) return fb_fail(FB_ERR_UNSUPPORTED, "peer exchange: device index %d not supported", device);
-  PeerPool& pp = g_peer_pool[device];
-  if (pp.ready) return FB_OK;
-  int lo = 0, hi = 0;
-  FB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-  for (int i = 0; i < PEER_AUX; ++i) {
-    FB_CUDA(cudaStreamCreateWithPriority(&pp.aux[i], cudaStreamNonBlocking, hi));
-    FB_CUDA(cudaEventCreateWithFlags(&pp.join[i], cudaEventDisableTiming));
+// blockIdx.y selects the peer (starting behind this rank, so that the ranks do not all read the same one first);
+// every thread moves four 16-byte words per round, loaded together before the first store.
+__global__ void __launch_bounds__(256)
+gather_blocks_kernel(SlotTable src, float* __restrict__ dst, int nranks, int rank, int64_t blk4, int64_t blk) {
+  const int r = (rank + 1 + (int)blockIdx.y) % nranks;
+  const float* s = src.p[r] + (int64_t)r * blk;
+  float* d = dst + (int64_t)r * blk;
+  const int64_t round = (int64_t)gridDim.x * 1024;
+  for (int64_t base = (int64_t)blockIdx.x * 1024 + threadIdx.x; base < blk4; base += round) {
+    float4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (base + k * 256 < blk4) v[k] = __ldcs((const float4*)s + base + k * 256);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (base + k * 256 < blk4) ((float4*)d)[base + k * 256] = v[k];
   }
-  FB_CUDA(cudaEventCreateWithFlags(&pp.fork, cudaEventDisableTiming));
-  pp.ready = true;
-  return FB_OK;
-}
-
-// copies[i] = (dst, src) for i < n, all of `bytes` bytes: spread over the auxiliary streams, joined back into `stream`
-int32_t peer_parallel_copies(fb_ctx* ctx, cudaStream_t stream, int n, float* const* dst, const float* const* src, size_t bytes) {
-  PeerPool& pp = g_peer_pool[ctx->device];
-  if (!pp.ready) {
-    for (int i = 0; i < n; ++i) FB_CUDA(cudaMemcpyAsync(dst[i], src[i], bytes, cudaMemcpyDeviceToDevice, stream));
-    return FB_OK;
-  }
-  FB_CUDA(cudaEventRecord(pp.fork, stream));
-  const int used = n < PEER_AUX ? n : PEER_AUX;
-  for (int a = 0; a < used; ++a) FB_CUDA(cudaStreamWaitEvent(pp.aux[a], pp.fork, 0));
-  for (int i = 0; i < n; ++i) FB_CUDA(cudaMemcpyAsync(dst[i], src[i], bytes, cudaMemcpyDeviceToDevice, pp.aux[i % PEER_AUX]));
-  for (int a = 0; a < used; ++a) {
-    FB_CUDA(cudaEventRecord(pp.join[a], pp.aux[a]));
-    FB_CUDA(cudaStreamWaitEvent(stream, pp.join[a], 0));
-  }
-  return FB_OK;
+  for (int64_t i = 4 * blk4 + (int64_t)blockIdx.x * 256 + threadIdx.x; i < blk; i += (int64_t)gridDim.x * 256) d[i] = s[i];
 }
 
 }  // namespace
@@ -91,8 +73,6 @@ FB_API int32_t fb_peer_alloc(fb_ctx* ctx, int64_t bytes, void** ptr_out, void* h
   FB_REQUIRE(ptr_out && handle_host && bytes >= 1, FB_ERR_INVALID_ARG, "fb_peer_alloc: bad arguments");
   *ptr_out = nullptr;
   FB_CUDA(cudaSetDevice(ctx->device));
-  const int32_t pst = peer_pool_create(ctx->device);
-  if (pst != FB_OK) return pst;
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, (size_t)bytes);
   if (e != cudaSuccess) {
@@ -144,36 +124,27 @@ FB_API int32_t fb_peer_free(fb_ctx* ctx, void* ptr) {
   return FB_OK;
 }
 
-FB_API int32_t fb_peer_scatter_blocks(fb_ctx* ctx, void* stream, const float* bucket, float* const* peer_stage_host, int32_t nranks,
-                                      int32_t rank, int64_t blk) {
+FB_API int32_t fb_peer_gather_blocks(fb_ctx* ctx, void* stream, const float* const* peer_src_host, float* dst, int32_t nranks,
+                                     int32_t rank, int64_t blk) {
   FB_CHECK_CTX(ctx);
-  FB_REQUIRE(bucket && peer_stage_host && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && blk >= 1,
-             FB_ERR_INVALID_ARG, "fb_peer_scatter_blocks: bad arguments (ranks %d, rank %d, block %lld)", nranks, rank, (long long)blk);
-  float* dst[PEER_MAX_RANKS];
-  const float* src[PEER_MAX_RANKS];
-  for (int i = 1; i < nranks; ++i) {
-    const int p = (rank + i) % nranks;     // every rank starts with a different peer
-    FB_REQUIRE(peer_stage_host[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_scatter_blocks: peer %d has no staging pointer", p);
-    dst[i - 1] = peer_stage_host[p] + (int64_t)rank * blk;
-    src[i - 1] = bucket + (int64_t)p * blk;
+  FB_REQUIRE(peer_src_host && dst && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && blk >= 1,
+             FB_ERR_INVALID_ARG, "fb_peer_gather_blocks: bad arguments (ranks %d, rank %d, block %lld)", nranks, rank, (long long)blk);
+  SlotTable t;
+  bool vec = fb_aligned16(dst) && blk % 4 == 0;
+  for (int p = 0; p < PEER_MAX_RANKS; ++p) {
+    t.p[p] = (p < nranks && p != rank) ? peer_src_host[p] : nullptr;
+    if (p < nranks && p != rank) {
+      FB_REQUIRE(peer_src_host[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_gather_blocks: peer %d has no source pointer", p);
+      vec = vec && fb_aligned16(peer_src_host[p]);
+    }
   }
-  return peer_parallel_copies(ctx, (cudaStream_t)stream, nranks - 1, dst, src, (size_t)blk * sizeof(float));
-}
-
-FB_API int32_t fb_peer_gather_block(fb_ctx* ctx, void* stream, const float* my_block, float* const* peer_dst_host, int32_t nranks,
-                                    int32_t rank, int64_t blk) {
-  FB_CHECK_CTX(ctx);
-  FB_REQUIRE(my_block && peer_dst_host && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && blk >= 1,
-             FB_ERR_INVALID_ARG, "fb_peer_gather_block: bad arguments (ranks %d, rank %d, block %lld)", nranks, rank, (long long)blk);
-  float* dst[PEER_MAX_RANKS];
-  const float* src[PEER_MAX_RANKS];
-  for (int i = 1; i < nranks; ++i) {
-    const int p = (rank + i) % nranks;
-    FB_REQUIRE(peer_dst_host[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_gather_block: peer %d has no destination pointer", p);
-    dst[i - 1] = peer_dst_host[p];
-    src[i - 1] = my_block;
-  }
-  return peer_parallel_copies(ctx, (cudaStream_t)stream, nranks - 1, dst, src, (size_t)blk * sizeof(float));
+  const int64_t blk4 = vec ? blk / 4 : 0;
+  int64_t per_peer = (blk / 4 + 1023) / 1024 + 1;
+  const int64_t cap = ((int64_t)ctx->sm_count * 2 + nranks - 2) / (nranks - 1);
+  if (per_peer > cap) per_peer = cap;
+  gather_blocks_kernel<<<dim3((unsigned)per_peer, (unsigned)(nranks - 1)), 256, 0, (cudaStream_t)stream>>>(t, dst, nranks, rank, blk4, blk);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
 }
 
 FB_API int32_t fb_reduce_slots(fb_ctx* ctx, void* stream, int32_t nslots, const float* const* slots_host, float* out, int64_t count,
@@ -192,7 +163,7 @@ FB_API int32_t fb_reduce_slots(fb_ctx* ctx, void* stream, int32_t nslots, const 
   }
   const int64_t count4 = vec ? count / 4 : 0;
   int64_t blocks = (count / 4 + 255) / 256 + 1;
-  if (blocks > (int64_t)ctx->sm_count * 8) blocks = (int64_t)ctx->sm_count * 8;
+  if (blocks > (int64_t)ctx->sm_count * 2) blocks = (int64_t)ctx->sm_count * 2;
   reduce_slots_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(t, nslots, out, count4, count, scale);
   FB_LAUNCH_CHECK();
   return FB_OK;

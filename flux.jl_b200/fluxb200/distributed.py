@@ -266,6 +266,8 @@ class GradBuckets:
     when a bucket's last gradient has landed, its mean all-reduce starts on the communication stream
     while the backward pass continues."""
 
+    SMALL_LEAF = 1 << 16   # leaves below this many elements share the last bucket
+
     def __init__(self, backend, params, bucket_mb: float = 64.0, reserved_sms: int | None = None):
         self.backend = backend
         # SMs the reverse sweep's persistent GEMMs leave free for the NCCL kernels that run beside them.  Measured at
@@ -287,6 +289,9 @@ class GradBuckets:
         self.adam = None
         self.armed = False
         self.peer = None             # peer-memory tables of the copy-based exchange (see _setup_peer_exchange)
+        self.defer_gather = False    # parameter gathers at the start of the next step (start_gathers) instead of per bucket
+        self.gather_events = None
+        self.gathering = False
         self.loss = None
         self.guard = None            # device scalar the update kernels test for finiteness (see set_loss)
         self._guard_buf = None
@@ -297,7 +302,19 @@ class GradBuckets:
         limit = int(bucket_mb * (1 << 20) / 4)
         off = 0
         cur_start, cur_ids = 0, []
-        for p in reversed(self.params):
+        # Weight matrices in the order the reverse sweep produces them, cut into buckets of ~bucket_mb; the small
+        # leaves (biases, normalisation scales) together in one last bucket.  A Dense pullback reports its weight
+        # gradient as soon as the dW product is enqueued, so a bucket of weights starts its exchange while the dX
+        # product and the normalisation layer's reverse pass still run; what is left after the sweep's last kernel is
+        # the small bucket only.
+        small = lambda q: q.numel() < self.SMALL_LEAF
+        order = [q for q in reversed(self.params) if not small(q)]
+        n_big = len(order)
+        order += [q for q in reversed(self.params) if small(q)]
+        for pi, p in enumerate(order):
+            if pi == n_big and cur_ids:       # the small leaves start a bucket of their own
+                self.buckets.append([cur_start, off, set(), list(cur_ids)])
+                cur_start, cur_ids = off, []
             n = p.numel()
             self.views[id(p)] = B200Array(self.flat[off:off + n], p.size)
             self.offsets[id(p)] = off
@@ -344,6 +361,10 @@ class GradBuckets:
         for b in self.buckets:
             b[2] = set(b[3])
         self.launched = [False] * len(self.buckets)
+        self.early = set()      # parameters a pullback reported itself and has not released yet
+        self.holds = {}         # bucket -> early-reported parameters some enqueued kernel may still read
+        self.update_pending = set()   # buckets whose gradients are exchanged but whose update waits for a release
+        self.gather_waited = set()   # buckets whose deferred parameter gather the forward pass already waits for
         self.handed = set()     # parameters whose slice a pullback of this step already writes
         self.uses = {}          # parameter id -> gradient contributions still to come (set by expect_uses)
         if self.marks is not None:
@@ -367,10 +388,27 @@ class GradBuckets:
         reverse sweep; `ready` starts a bucket only after the last contribution of each of its parameters."""
         self.uses = dict(counts)
 
-    def ready(self, param):
+    def ready(self, param, early=False):
+        """The gradient of `param` has been enqueued.  A pullback may call this itself with early=True as soon as the
+        kernel that writes the gradient is launched although its remaining kernels still READ the parameter; the
+        reverse sweep's own call for the same contribution, which comes when the pullback has returned, then only
+        releases the parameter.  Between the two calls the bucket's gradient exchange may run, its parameter update
+        may not (`_launch` holds it back).  Honoured with the peer-memory exchange only."""
         k = id(param)
         bi = self.bucket_of.get(k)
         if bi is None:
+            return
+        if early:
+            if not (self.armed and self.peer is not None):
+                return
+            self.early.add(k)
+            self.holds[bi] = self.holds.get(bi, 0) + 1
+        elif k in self.early:
+            self.early.discard(k)
+            self.holds[bi] -= 1
+            if self.holds[bi] == 0 and bi in self.update_pending:
+                self.update_pending.discard(bi)
+                self._peer_update(bi)
             return
         left = self.uses.get(k, 1) - 1
         self.uses[k] = left
@@ -397,10 +435,17 @@ class GradBuckets:
             return False
         if self.pflat is None:
             self.mflat, self.vflat = (torch.zeros_like(self.flat) for _ in range(2))
-            # parameters live in memory the peers can write when the copy-based exchange is available
-            self.pflat = self._setup_peer_exchange()
-            if self.pflat is None:
+            # gradients and parameters live in memory the peers have mapped when the peer-memory exchange is available
+            bufs = self._setup_peer_exchange()
+            if bufs is None:
                 self.pflat = torch.zeros_like(self.flat)
+            else:
+                gflat, self.pflat = bufs
+                gflat.copy_(self.flat)
+                self.flat = gflat
+                for p in self.params:
+                    off = self.offsets[id(p)]
+                    self.views[id(p)] = B200Array(self.flat[off:off + p.numel()], p.size)
             for p in self.params:
                 off, cnt = self.offsets[id(p)], p.numel()
                 st = opt_state.leaves[id(p)].state
@@ -412,10 +457,11 @@ class GradBuckets:
         return True
 
     def _setup_peer_exchange(self):
-        """Maps, on every rank, a staging area and the parameter buffer of every other rank (CUDA IPC), so that the
-        reduce-scatter and the all-gather of the sharded step can run as device-to-device copies on the copy engines
-        (no SM is taken from the reverse sweep's GEMMs).  Returns this rank's parameter buffer as a tensor, or None
-        when any rank cannot map its peers (or FLUXB200_EXCHANGE=nccl): then the NCCL collectives are used."""
+        """Allocates this rank's gradient buffer and parameter buffer in memory the other ranks map (CUDA IPC) and maps
+        theirs, so that the reduce-scatter and the all-gather of the sharded step run as kernels that read the peers'
+        buffers over NVLink (fb_reduce_slots, fb_peer_gather_blocks).  Returns (gradient buffer, parameter buffer) as
+        tensors, or None when any rank cannot map its peers (or FLUXB200_EXCHANGE=nccl): then the NCCL collectives
+        are used."""
         import torch.distributed as dist
         be = self.backend
         self.peer = None
@@ -426,7 +472,7 @@ class GradBuckets:
         mine, ptrs = [0] * (1 + 2 * HB), []
         if want:
             try:
-                for k in range(2):          # staging area, parameter buffer
+                for k in range(2):          # gradient buffer, parameter buffer
                     ptr, h = C.c_void_p(), (C.c_uint8 * HB)()
                     lib.call("fb_peer_alloc", ctx.handle, nbytes, C.byref(ptr), h)
                     ptrs.append(ptr.value)
@@ -462,15 +508,68 @@ class GradBuckets:
             def __init__(self, ptr, count):
                 self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3, "strides": None}
 
-        raw = _Raw(pbuf[be.rank], self.flat.numel())
-        ptensor = torch.as_tensor(raw, device=self.flat.device)
-        self.peer = {"stage": stage, "pflat": pbuf, "keep": raw,
-                     "token": torch.zeros(1, dtype=torch.float32, device=self.flat.device), "done": torch.cuda.Event()}
-        return ptensor
+        raws = [_Raw(table[be.rank], self.flat.numel()) for table in (stage, pbuf)]
+        tensors = tuple(torch.as_tensor(raw, device=self.flat.device) for raw in raws)
+        self.peer = {"grads": stage, "pflat": pbuf, "keep": raws,
+                     "token": torch.zeros(1, dtype=torch.float32, device=self.flat.device)}
+        return tensors
+
+    def start_gathers(self):
+        """Deferred all-gather (sharded optimiser over peer memory): the parameter blocks updated in the previous step
+        travel to the peers at the START of a step, in the order the forward pass needs them, beside the forward
+        pass - instead of beside the reverse sweep, whose exchange then carries the gradients only.  Every layer waits
+        for its bucket (`wait_param`) before it reads its parameters.  Between steps the parameters of a rank are
+        current only inside its own blocks; `sync_params` brings them together for a reader outside the step."""
+        peer = self.peer
+        if peer is None or self.adam is None:
+            return
+        be = self.backend
+        n = be.size
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        be.stream.wait_event(ev)
+        cs = C.c_void_p(be.stream.cuda_stream)
+        h = context().handle
+        tab = C.c_void_p * n
+        if self.gather_events is None:
+            self.gather_events = [torch.cuda.Event() for _ in self.buckets]
+            self.start_fence = torch.cuda.Event()
+        # one barrier: every rank has finished the previous step, its updates and its reads of my gradient buffer
+        self._peer_barrier(cs)
+        self.start_fence.record(be.stream)
+        nb = len(self.buckets)
+        order = [nb - 1] + list(range(nb - 2, -1, -1)) if nb > 1 else [0]   # small leaves, then weights first layer first
+        for bi in order:
+            start, blk, _ = self._peer_block(bi)
+            lib.call("fb_peer_gather_blocks", h, cs, tab(*[peer["pflat"][r] + 4 * start for r in range(n)]),
+                     C.c_void_p(self.pflat.data_ptr() + 4 * start), n, be.rank, blk)
+            self.gather_events[bi].record(be.stream)
+        self.gather_waited = set()
+        self.gathering = True
+
+    def wait_param(self, param):
+        """Called by a layer before it reads `param` in a step with deferred gathers."""
+        if not getattr(self, "gathering", False) or param is None:
+            return
+        bi = self.bucket_of.get(id(param))
+        if bi is None or bi in self.gather_waited:
+            return
+        self.gather_waited.add(bi)
+        torch.cuda.current_stream().wait_event(self.gather_events[bi])
+
+    def sync_params(self):
+        """Brings every rank's parameters up to date (outside a step): runs the deferred gathers now and waits."""
+        if self.peer is None or not self.defer_gather:
+            return
+        self.start_gathers()
+        for ev in self.gather_events:
+            torch.cuda.current_stream().wait_event(ev)
+        self.gathering = False
+        torch.cuda.current_stream().synchronize()
 
     def _peer_barrier(self, cs):
-        """A one-element all-reduce on the communication stream: when it completes on this rank, the copies every
-        rank enqueued before it have reached their destinations."""
+        """A one-element all-reduce on the communication stream: when it completes on this rank, every rank has
+        finished what it enqueued before its own call."""
         tok = C.c_void_p(self.peer["token"].data_ptr())
         lib.call("fb_allreduce", self.backend.comm, cs, tok, tok, 1, lib.OP["+"])
 
@@ -482,6 +581,10 @@ class GradBuckets:
         self.loss = loss
         self.guard = loss
         be = self.backend
+        if self.gathering and getattr(self, "start_fence", None) is not None:
+            # no gradient is written before every rank has left the previous step (a peer may still read this rank's
+            # gradient buffer until then); the layers' own waits normally come first
+            torch.cuda.current_stream().wait_event(self.start_fence)
         if be.size > 1 and be.comm is not None:
             if self._guard_buf is None:
                 self._guard_buf = B200Array(torch.zeros(1, dtype=torch.float32, device=loss.t.device), ())
@@ -515,24 +618,12 @@ class GradBuckets:
             lo = 4 * (start + be.rank * blk)
             g, pp = self.flat.data_ptr() + lo, self.pflat.data_ptr() + lo
             one = C.c_void_p * 1
-            peer = getattr(self, "peer", None)
-            if peer is not None:
-                # copy-based reduce-scatter: my block p goes to slot [me] of peer p's staging area; after the barrier
-                # the N slots of my block are summed in rank order (my own slot is read where it was produced)
-                h = context().handle
-                tab = C.c_void_p * n
-                lib.call("fb_peer_scatter_blocks", h, cs, ptr, tab(*[peer["stage"][r] + 4 * start for r in range(n)]), n, be.rank, blk)
-                self._peer_barrier(cs)
-                slots = tab(*[(peer["stage"][be.rank] + 4 * (start + r * blk)) if r != be.rank else g for r in range(n)])
-                lib.call("fb_reduce_slots", h, cs, n, slots, C.c_void_p(g), blk, 1.0 / n)
-                self._mark(f"bucket {bi} reduce-scatter end", be.stream)
-                lib.call("fb_adam_step_dev", h, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
-                         one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
-                         rule.epsilon, C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
-                self._mark(f"bucket {bi} adam end", be.stream)
-                lib.call("fb_peer_gather_block", h, cs, C.c_void_p(pp), tab(*[peer["pflat"][r] + lo for r in range(n)]), n, be.rank, blk)
-                self._mark(f"bucket {bi} comm end", be.stream)
-                self.events[bi].record(be.stream)
+            if self.peer is not None:
+                self._peer_exchange(bi)
+                if self.holds.get(bi, 0) > 0:
+                    self.update_pending.add(bi)
+                else:
+                    self._peer_update(bi, waited=True)
                 return
             lib.call("fb_reduce_scatter", be.comm, cs, ptr, C.c_void_p(g), blk, lib.OP["avg"])
             self._mark(f"bucket {bi} reduce-scatter end", be.stream)
@@ -546,6 +637,54 @@ class GradBuckets:
         self._mark(f"bucket {bi} comm end", be.stream)
         self.events[bi].record(be.stream)
 
+    def _peer_block(self, bi):
+        start, end = self.buckets[bi][0], self.buckets[bi][1]
+        blk = (end - start) // self.backend.size
+        return start, blk, 4 * (start + self.backend.rank * blk)
+
+    def _peer_exchange(self, bi):
+        """Reduce-scatter of one bucket over peer memory: behind a barrier (every rank's gradients of the bucket are
+        written), the mean of the N ranks' copies of my block, read in place in rank order."""
+        be, peer = self.backend, self.peer
+        n = be.size
+        start, blk, lo = self._peer_block(bi)
+        cs = C.c_void_p(be.stream.cuda_stream)
+        tab = C.c_void_p * n
+        g = self.flat.data_ptr() + lo
+        self._peer_barrier(cs)
+        slots = tab(*[(peer["grads"][r] + lo) if r != be.rank else g for r in range(n)])
+        lib.call("fb_reduce_slots", context().handle, cs, n, slots, C.c_void_p(g), blk, 1.0 / n)
+        self._mark(f"bucket {bi} reduce-scatter end", be.stream)
+
+    def _peer_update(self, bi, waited=False):
+        """Adam on my block of one bucket and, unless the gathers are deferred to the next step, a barrier (every
+        rank's block is updated) and the copies of the peers' blocks into my parameter buffer.  With waited=False the
+        call comes from a release: the communication stream first waits for the kernels enqueued so far, the last
+        readers of the parameter among them."""
+        be, peer = self.backend, self.peer
+        n = be.size
+        start, blk, lo = self._peer_block(bi)
+        cs = C.c_void_p(be.stream.cuda_stream)
+        h = context().handle
+        if not waited:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            be.stream.wait_event(ev)
+        rule, bt = self.adam
+        one = C.c_void_p * 1
+        g, pp = self.flat.data_ptr() + lo, self.pflat.data_ptr() + lo
+        lib.call("fb_adam_step_dev", h, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
+                 one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
+                 rule.epsilon, C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
+        self._mark(f"bucket {bi} adam end", be.stream)
+        if not self.defer_gather:
+            tab = C.c_void_p * n
+            self._peer_barrier(cs)
+            lib.call("fb_peer_gather_blocks", h, cs, tab(*[peer["pflat"][r] + 4 * start for r in range(n)]),
+                     C.c_void_p(self.pflat.data_ptr() + 4 * start), n, be.rank, blk)
+        self._mark(f"bucket {bi} comm end", be.stream)
+        self.events[bi].record(be.stream)
+
     def finish(self):
         """Launches whatever is still pending and makes the compute stream wait for every bucket."""
         for bi in range(len(self.buckets)):
@@ -553,10 +692,9 @@ class GradBuckets:
                 self._launch(bi)
         self._mark("backward end")
         if self.backend.size > 1:
-            if self.armed and getattr(self, "peer", None) is not None:
-                # the peers' parameter blocks must have landed here before anybody reads the parameters again
-                self._peer_barrier(C.c_void_p(self.backend.stream.cuda_stream))
-                self.events[-1].record(self.backend.stream)
+            for bi in sorted(self.update_pending):      # a pullback that never released: update after everything enqueued
+                self._peer_update(bi)
+            self.update_pending = set()
             for ev in self.events:
                 torch.cuda.current_stream().wait_event(ev)
             if self.guard_event is not None:

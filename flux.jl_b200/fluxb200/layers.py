@@ -38,6 +38,16 @@ def _ptr(a):
     return a.ptr if a is not None else None
 
 
+def _wait_params(*params):
+    """A gradient sink that defers the parameter all-gather to the next step's forward pass must have delivered a
+    layer's parameters before the layer reads them."""
+    sink = Tape.grad_sink
+    if sink is not None and getattr(sink, "gathering", False):
+        for p in params:
+            if isinstance(p, B200Array):
+                sink.wait_param(p)
+
+
 def _size_check(layer, x: B200Array, d: int, n: int):
     """basic.jl:217-223 (d is 1-based)."""
     if not (0 < d <= x.ndim):
@@ -186,6 +196,7 @@ class Dense(Layer):
         _size_check(self, x, 1, in_dim)
         n = x.numel() // in_dim
         ctx = context()
+        _wait_params(self.weight, self.bias)
         if is_bf16(self.weight):
             return self._call_bf16(to_bf16(x), out_dim, in_dim, n)
         x = to_f32(x)
@@ -207,8 +218,17 @@ class Dense(Layer):
                 db = ((sink.buffer_for(b) if sink else None) or empty(b.size)) if b is not None else None
                 dx = empty(x.size) if need_dx else None
                 delta = empty(y.size) if act != 0 else None
-                lib.call("fb_dense_bwd", ctx.handle, ctx.stream, act, prec, W.ptr, x.ptr, y.ptr, _ptr(z), dy.ptr,
-                         _ptr(delta), dW.ptr, _ptr(db), _ptr(dx), out_dim, in_dim, n)
+                if sink is not None and need_dx and hasattr(sink, "ready"):
+                    # dW (and db) first, reported to the gradient sink at once so that their exchange overlaps the dX product
+                    lib.call("fb_dense_bwd", ctx.handle, ctx.stream, act, prec, W.ptr, x.ptr, y.ptr, _ptr(z), dy.ptr,
+                             _ptr(delta), dW.ptr, _ptr(db), None, out_dim, in_dim, n)
+                    sink.ready(W, early=True)
+                    d = delta if act != 0 else dy
+                    lib.call("fb_gemm_f32", ctx.handle, ctx.stream, 1, 0, in_dim, n, out_dim, W.ptr, out_dim, d.ptr, out_dim, dx.ptr, in_dim,
+                             0, prec)
+                else:
+                    lib.call("fb_dense_bwd", ctx.handle, ctx.stream, act, prec, W.ptr, x.ptr, y.ptr, _ptr(z), dy.ptr,
+                             _ptr(delta), dW.ptr, _ptr(db), _ptr(dx), out_dim, in_dim, n)
                 res = [(W, dW)]
                 if b is not None:
                     res.append((b, db))
@@ -287,6 +307,7 @@ class LayerNorm(Layer):
     def __call__(self, x: B200Array) -> B200Array:
         x = to_f32(x)
         if self.affine:
+            _wait_params(self.diag.scale, self.diag.bias)
             for d, s in enumerate(self.size):
                 _size_check(self, x, d + 1, s)
         d = int(np.prod(self.size))

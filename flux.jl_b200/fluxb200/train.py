@@ -461,7 +461,7 @@ class GraphedTrainStep:
 
     error_poll_every = 16   # the device error word is read back every this many steps (one 4-byte copy)
 
-    def __init__(self, loss, model, opt_state, example_batch, grad_sink=None, shard_optimizer=False):
+    def __init__(self, loss, model, opt_state, example_batch, grad_sink=None, shard_optimizer=False, defer_gather=False):
         from .layers import BatchNorm, _walk
         if not isinstance(example_batch, tuple):
             example_batch = (example_batch,)
@@ -509,6 +509,10 @@ class GraphedTrainStep:
             if grad_sink is not None:
                 grad_sink.begin_step()
                 grad_sink.armed = self.sharded
+                # deferred gathers need every layer of the model to wait for its parameters: Dense and LayerNorm do
+                if self.sharded and defer_gather and getattr(grad_sink, "peer", None) is not None and self._only_waiting_layers(model):
+                    grad_sink.defer_gather = True
+                    grad_sink.start_gathers()
             try:
                 loss_arr, _, tree = _withgradient_device(fn, model, grad_sink)
                 gmap: dict = {}
@@ -541,6 +545,17 @@ class GraphedTrainStep:
         self.loss_arr = loss_arr
         self.guard_arr = guard
         self._updated = ps
+
+    @staticmethod
+    def _only_waiting_layers(model):
+        from .layers import Chain, Dense, LayerNorm, _walk
+        return all(isinstance(l, (Chain, Dense, LayerNorm, LayerNorm._Scale)) for l in _walk(model))
+
+    def sync_params(self):
+        """With deferred gathers a rank's parameters are complete only after the next step has started; call this
+        before reading them (checkpoint, evaluation) outside a step."""
+        if self.sink is not None and hasattr(self.sink, "sync_params"):
+            self.sink.sync_params()
 
     def prefetch(self, *batch):
         """Starts copying the NEXT step's inputs (pinned host tensors, or device arrays) into staging buffers on a copy

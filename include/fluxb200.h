@@ -444,28 +444,27 @@ int32_t fb_bcast(fb_comm* comm, void* stream, const float* send, float* recv, in
 /* DistributedUtils.reduce! (NCCL.Reduce!, FluxMPINCCLExt.jl:86-102). */
 int32_t fb_reduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op, int32_t root);
 
-/* Gradient exchange over peer memory (single node, NVLink / NVSwitch), for the sharded optimiser: the reduce-scatter
- * and the all-gather done as device-to-device copies into buffers the other ranks have mapped, so that they run on
- * the copy engines and leave every SM to the reverse sweep.  No counterpart in the reference (which calls
- * NCCL.Allreduce! per leaf, ext/FluxMPINCCLExt/FluxMPINCCLExt.jl:61-66); results equal a mean all-reduce followed by
- * the same update on every rank.
+/* Gradient exchange over peer memory (single node, NVLink / NVSwitch), for the sharded optimiser: reduce-scatter and
+ * all-gather as kernels that read buffers the other ranks have mapped into this process.  No counterpart in the
+ * reference (which calls NCCL.Allreduce! per leaf, ext/FluxMPINCCLExt/FluxMPINCCLExt.jl:61-66); results equal a mean
+ * all-reduce followed by the same update on every rank.
  *  - fb_peer_alloc allocates `bytes` of zeroed device memory and returns a FB_PEER_HANDLE_BYTES handle that the
  *    caller hands to the other processes (any host channel); fb_peer_open maps a peer's handle into this process.
- *  - fb_peer_scatter_blocks copies block p (blk floats) of this rank's bucket into peer_stage_host[p] + rank * blk
- *    for every peer p (peer_stage_host[p] = the bucket's staging area in peer p's memory, nranks slots of blk floats).
- *  - fb_reduce_slots: out = scale * (slots[0] + slots[1] + ... ) in that order.
- *  - fb_peer_gather_block copies this rank's updated block to peer_dst_host[p] for every peer p.
- * The caller orders the phases with a collective on the same stream (a one-element fb_allreduce is enough): copies are
- * complete at the destination once a collective enqueued after them on every rank has completed. */
+ *  - fb_reduce_slots: out = scale * (slots[0] + slots[1] + ... ) in that order; slots may lie in peers' memory, and
+ *    out may be one of them (reduce-scatter: slots[r] = my block inside rank r's gradient buffer).
+ *  - fb_peer_gather_blocks: for every peer p, block p (blk floats at offset p * blk) of peer_src_host[p] is copied to
+ *    the same offset of dst (all-gather: peer_src_host[p] = the bucket inside rank p's parameter buffer, dst = the
+ *    bucket inside mine; the entry of this rank is ignored).
+ * Remote memory is only read.  The caller orders the phases with a collective on the same stream (a one-element
+ * fb_allreduce is enough): what a rank wrote before it enqueued the collective is visible to a kernel another rank
+ * enqueues behind it. */
 #define FB_PEER_HANDLE_BYTES 64
 int32_t fb_peer_alloc(fb_ctx* ctx, int64_t bytes, void** ptr_out, void* handle_host);
 int32_t fb_peer_open(fb_ctx* ctx, const void* handle_host, void** ptr_out);
 int32_t fb_peer_close(fb_ctx* ctx, void* ptr);
 int32_t fb_peer_free(fb_ctx* ctx, void* ptr);
-int32_t fb_peer_scatter_blocks(fb_ctx* ctx, void* stream, const float* bucket, float* const* peer_stage_host,
-                               int32_t nranks, int32_t rank, int64_t blk);
-int32_t fb_peer_gather_block(fb_ctx* ctx, void* stream, const float* my_block, float* const* peer_dst_host,
-                             int32_t nranks, int32_t rank, int64_t blk);
+int32_t fb_peer_gather_blocks(fb_ctx* ctx, void* stream, const float* const* peer_src_host, float* dst,
+                              int32_t nranks, int32_t rank, int64_t blk);
 int32_t fb_reduce_slots(fb_ctx* ctx, void* stream, int32_t nslots, const float* const* slots_host, float* out,
                         int64_t count, float scale);
 

@@ -74,9 +74,15 @@ def main():
     lib.call("fb_bucket_destroy", bset)
 
     # data container: contiguous ceil(n/N) shards whose sizes add up
-    data = np.arange(10 * 7, dtype=np.float32).reshape(7, 10)
+    nobs = 5 * world - 1                       # a ragged split in which every worker still owns observations
+    data = np.arange(nobs * 7, dtype=np.float32).reshape(7, nobs)
     ddc = DU.DistributedDataContainer(backend, data)
-    assert len(ddc) == min(int(np.ceil(10 / world)), max(10 - rank * int(np.ceil(10 / world)), 0))
+    per = int(np.ceil(nobs / world))
+    assert len(ddc) == min(per, max(nobs - rank * per, 0)) and len(ddc) >= 1
+    cnt = torch.tensor([len(ddc)], dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(cnt)
+    assert int(cnt.item()) == nobs
 
     # data-parallel training == single-process training on the full batch
     rng = np.random.default_rng(7)             # same stream on every rank
@@ -170,19 +176,23 @@ def main():
         return F.Chain(*ls)
 
     runs = []
-    for shard in (False, True):
+    for shard, defer in ((False, False), (True, False), (True, True)):
         m = build()
         bk = DU.GradBuckets(backend, F.trainables(m), bucket_mb=0.2)
         o = F.setup(DU.DistributedOptimizer(backend, F.Adam(1e-3), bk), m)
         gs = F.GraphedTrainStep(lambda mm, xx, yy: F.logitcrossentropy(mm(xx), yy), m, o, (xg, yg), grad_sink=bk,
-                                shard_optimizer=shard)
+                                shard_optimizer=shard, defer_gather=defer)
         assert gs.sharded == (shard and world > 1)
-        runs.append((m, [gs(xg, yg) for _ in range(3)]))
-    (ma, la), (mb, lb) = runs
+        losses = [gs(xg, yg) for _ in range(3)]
+        gs.sync_params()          # deferred gathers: the peers' blocks of the last update arrive now
+        runs.append((m, losses))
+    (ma, la), (mb, lb), (mc, lc) = runs
     np.testing.assert_allclose(la, lb, rtol=1e-5)
+    np.testing.assert_allclose(la, lc, rtol=1e-5)
     assert la[2] < la[0]
-    for pa, pb in zip(F.trainables(ma), F.trainables(mb)):
+    for pa, pb, pc in zip(F.trainables(ma), F.trainables(mb), F.trainables(mc)):
         np.testing.assert_allclose(F.cpu(pb), F.cpu(pa), rtol=0, atol=3e-6)
+        np.testing.assert_allclose(F.cpu(pc), F.cpu(pa), rtol=0, atol=3e-6)
     wb = mb.layers[1].weight
     chk = torch.stack([wb.t.double().sum(), (wb.t.double() ** 2).sum()]).cpu()
     lo, hi = chk.clone(), chk.clone()
