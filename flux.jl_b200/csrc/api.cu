@@ -60,7 +60,9 @@ FB_API int32_t fb_ctx_create(int32_t device, fb_ctx** out) {
     return fb_fail(FB_ERR_ALLOC, "fb_ctx_create: cudaMalloc failed: %s", cudaGetErrorString(e));
   }
   cudaMemset(c->dev_error, 0, 256);
-  const int32_t ws_status = fb_gemm_workspace_create(c);
+  int32_t ws_status = fb_side_kernels_prepare_elementwise();
+  if (ws_status == FB_OK) ws_status = fb_side_kernels_prepare_peer();
+  if (ws_status == FB_OK) ws_status = fb_gemm_workspace_create(c);
   if (ws_status != FB_OK) {
     cudaFree(c->dev_error);
     delete c;

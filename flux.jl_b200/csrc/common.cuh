@@ -237,6 +237,11 @@ int32_t fb_attn_bwd_dkdv_tc(fb_ctx* ctx, cudaStream_t stream, const float* q, co
                             const float* lse, const float* dlt, const float* dout, float* dk, float* dv, int64_t e_dim,
                             int64_t ev_dim, int64_t lq, int64_t lk, int64_t batch, int nheads, int causal);
 int32_t fb_gemm_workspace_create(fb_ctx* ctx);
+// Kernels that run on a communication stream beside a resident GEMM CTA (update, peer exchange, time marks) ask for
+// the same shared-memory carve-out as the GEMM: an SM runs CTAs of different kernels together only when they agree
+// on how its L1 / shared memory is split.
+int32_t fb_side_kernels_prepare_elementwise();
+int32_t fb_side_kernels_prepare_peer();
 void fb_gemm_workspace_reset(fb_ctx* ctx, cudaStream_t stream);
 
 // delta = dy .* act'(.) and db[j] = sum_rows delta[row][j]   (rows x cols row-major; cols = out_dim)

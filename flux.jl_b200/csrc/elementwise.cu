@@ -157,7 +157,10 @@ struct AdamTable {
   int ntensors;
 };
 
-__global__ void __launch_bounds__(EW_THREADS)
+// 128 threads of at most 32 registers: such a CTA fits on an SM beside a resident GEMM CTA (one warp per register-file
+// partition), so an update enqueued on the communication stream does not wait for the reverse sweep's GEMM to end.
+constexpr int ADAM_THREADS = 128;
+__global__ void __launch_bounds__(ADAM_THREADS, 2048 / ADAM_THREADS)
 adam_kernel(const __grid_constant__ AdamTable tab, float eta, float beta1, float beta2, float eps, float inv_c1,
             float inv_c2, float grad_scale, const float* __restrict__ bt_dev, const float* __restrict__ guard) {
   // device-resident step state (used when the step is replayed from a CUDA graph): the running beta powers
@@ -182,7 +185,7 @@ adam_kernel(const __grid_constant__ AdamTable tab, float eta, float beta1, float
                      reinterpret_cast<uintptr_t>(v)) & 15u) == 0;
   if (vec) {
     const int64_t e4 = begin + ((end - begin) & ~int64_t(3));
-    for (int64_t i = begin + 4 * threadIdx.x; i < e4; i += 4 * EW_THREADS) {
+    for (int64_t i = begin + 4 * threadIdx.x; i < e4; i += 4 * ADAM_THREADS) {
       float4 gv = __ldcs((const float4*)(g + i));
       float4 mv = *(const float4*)(m + i), vv = *(const float4*)(v + i), wv = *(const float4*)(w + i);
       float* gp = &gv.x; float* mp = &mv.x; float* vp = &vv.x; float* wp = &wv.x;
@@ -197,14 +200,14 @@ adam_kernel(const __grid_constant__ AdamTable tab, float eta, float beta1, float
       *(float4*)(v + i) = vv;
       *(float4*)(w + i) = wv;
     }
-    for (int64_t i = e4 + threadIdx.x; i < end; i += EW_THREADS) {
+    for (int64_t i = e4 + threadIdx.x; i < end; i += ADAM_THREADS) {
       const float gk = g[i] * grad_scale;
       const float mk = beta1 * m[i] + omb1 * gk, vk = beta2 * v[i] + omb2 * gk * gk;
       m[i] = mk; v[i] = vk;
       w[i] -= mk * inv_c1 / (sqrtf(vk * inv_c2) + eps) * eta;
     }
   } else {
-    for (int64_t i = begin + threadIdx.x; i < end; i += EW_THREADS) {
+    for (int64_t i = begin + threadIdx.x; i < end; i += ADAM_THREADS) {
       const float gk = g[i] * grad_scale;
       const float mk = beta1 * m[i] + omb1 * gk, vk = beta2 * v[i] + omb2 * gk * gk;
       m[i] = mk; v[i] = vk;
@@ -346,6 +349,12 @@ __global__ void timestamp_kernel(uint64_t* out) {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   *out = t;
+}
+
+int32_t fb_side_kernels_prepare_elementwise() {
+  FB_CUDA(cudaFuncSetAttribute(adam_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  FB_CUDA(cudaFuncSetAttribute(timestamp_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  return FB_OK;
 }
 
 FB_API int32_t fb_timestamp(fb_ctx* ctx, void* stream, uint64_t* out_dev) {
@@ -536,7 +545,7 @@ static int32_t adam_common(fb_ctx* ctx, cudaStream_t stream, int32_t ntensors, f
     if (k == 0) continue;
     tab.block_start[k] = blocks;
     tab.ntensors = k;
-    adam_kernel<<<(unsigned)blocks, EW_THREADS, 0, stream>>>(tab, eta, beta1, beta2, eps, inv_c1, inv_c2, grad_scale, bt_dev, guard);
+    adam_kernel<<<(unsigned)blocks, ADAM_THREADS, 0, stream>>>(tab, eta, beta1, beta2, eps, inv_c1, inv_c2, grad_scale, bt_dev, guard);
     FB_LAUNCH_CHECK();
   }
   return FB_OK;

@@ -396,6 +396,9 @@ int32_t launch_bf16(fb_ctx* ctx, cudaStream_t stream, const fb_gemm_bf16_args& a
                           (long long)a.M, (long long)a.N, (long long)a.K, (long long)a.lda, (long long)a.ldb);
   auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, PAIR>;
   FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+  // the whole L1 / shared array as shared memory: the communication-stream kernels ask for the same split, and an SM
+  // takes CTAs of two kernels together only when their splits agree
+  FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   const int tiles_n = (int)((a.N + BN - 1) / BN);
   const int64_t tiles_m = PAIR ? (a.M + 255) / 256 : (a.M + HBM_ - 1) / HBM_;
   const int64_t num_tiles = tiles_m * tiles_n;

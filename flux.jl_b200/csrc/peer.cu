@@ -3,8 +3,10 @@
 //
 // Every rank owns 1/N of each gradient bucket.  The gradient buffer and the parameter buffer of every rank are
 // allocated by fb_peer_alloc and mapped by all the others (CUDA IPC).  Per bucket:
-//   1. a one-element NCCL all-reduce on the communication stream as a barrier: when it completes here, every rank's
-//      gradients of the bucket are written (each rank enqueues the barrier behind its own reverse-sweep kernels)
+//   1. fb_peer_barrier on the communication stream: one warp writes this rank's epoch into a flag word of every peer
+//      and waits (bounded) until every peer's epoch has arrived here; when it completes, every rank's gradients of
+//      the bucket are written (each rank enqueues the barrier behind its own reverse-sweep kernels).  One warp and
+//      a dozen registers: it finds room on an SM beside a resident GEMM CTA, which an NCCL kernel does not
 //   2. fb_reduce_slots: the mean of the N ranks' copies of MY block, read in place from the N gradient buffers in
 //      rank order (plain loads over NVLink, 16 bytes per load, every thread keeps up to 8 loads in flight), then Adam
 //      on my block
@@ -21,52 +23,101 @@ namespace {
 constexpr int PEER_MAX_RANKS = 16;
 struct SlotTable { const float* p[PEER_MAX_RANKS]; };
 
-__global__ void __launch_bounds__(256)
-reduce_slots_kernel(SlotTable t, int nslots, float* __restrict__ out, int64_t count4, int64_t count, float scale) {
-  const int64_t stride = (int64_t)gridDim.x * 256;
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < count4; i += stride) {
+// Side-kernel shape: 128 threads of at most 32 registers.  A resident 3xTF32 GEMM CTA (22 warps of 80 registers) leaves
+// about 1 K registers free in each of the SM's four register-file partitions: one warp of 32 registers per partition
+// still fits, a wider CTA or a fatter thread waits until the GEMM has ended.
+constexpr int SIDE_THREADS = 128;
+
+__global__ void __launch_bounds__(SIDE_THREADS, 2048 / SIDE_THREADS)
+reduce_slots_kernel(const __grid_constant__ SlotTable t, int nslots, float* __restrict__ out, int64_t count4, int64_t count, float scale) {
+  const int64_t stride = (int64_t)gridDim.x * SIDE_THREADS;
+  for (int64_t i = (int64_t)blockIdx.x * SIDE_THREADS + threadIdx.x; i < count4; i += stride) {
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < nslots; s0 += 8) {
-      float4 v[8];
+    for (int s0 = 0; s0 < nslots; s0 += 4) {
+      float4 v[4];
 #pragma unroll
-      for (int s = 0; s < 8; ++s)        // all loads of a group are issued before the first sum waits for one
+      for (int s = 0; s < 4; ++s)        // the loads of a group are issued before the first sum waits for one
         if (s0 + s < nslots) v[s] = __ldcs((const float4*)t.p[s0 + s] + i);
 #pragma unroll
-      for (int s = 0; s < 8; ++s)
+      for (int s = 0; s < 4; ++s)
         if (s0 + s < nslots) { a.x += v[s].x; a.y += v[s].y; a.z += v[s].z; a.w += v[s].w; }
     }
     a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
     ((float4*)out)[i] = a;
   }
   // tail (count not a multiple of 4, or a pointer off the 16-byte grid)
-  for (int64_t i = 4 * count4 + (int64_t)blockIdx.x * 256 + threadIdx.x; i < count; i += stride) {
+  for (int64_t i = 4 * count4 + (int64_t)blockIdx.x * SIDE_THREADS + threadIdx.x; i < count; i += stride) {
     float a = 0.f;
     for (int s = 0; s < nslots; ++s) a += t.p[s][i];
     out[i] = a * scale;
   }
 }
 
+// Barrier between the ranks of one node.  flags.p[r] = rank r's array of nranks epoch words (this rank's own array is
+// local memory, the others are mapped).  `epoch` is a device word owned by this rank that counts the barriers passed,
+// so that a captured launch works for every replay.  Lane r posts to peer r and waits for peer r.  A wait that runs
+// out (a peer that died or never reached the barrier) writes FB_DEV_ERR_PEER_BARRIER to the device error word and
+// lets the kernel end: the context stays usable and the host finds the code with fb_device_error.
+constexpr int32_t FB_DEV_ERR_PEER_BARRIER = 9101;
+
+struct FlagTable { uint32_t* p[PEER_MAX_RANKS]; };
+
+__global__ void __maxnreg__(32)
+peer_barrier_kernel(const __grid_constant__ FlagTable flags, int nranks, int rank, uint32_t* __restrict__ epoch, int32_t* __restrict__ dev_err, uint64_t limit_ns) {
+  const int lane = threadIdx.x;
+  const uint32_t e = *epoch + 1u;
+  __syncwarp();
+  if (lane < nranks && lane != rank) {
+    uint32_t* remote = flags.p[lane] + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(e) : "memory");
+    const uint32_t* mine = flags.p[rank] + lane;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    uint32_t polls = 0;
+    while (true) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if ((int32_t)(seen - e) >= 0) break;
+      if ((++polls & 63u) == 0) {
+        uint64_t t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > limit_ns) { atomicCAS(dev_err, 0, FB_DEV_ERR_PEER_BARRIER); break; }
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncwarp();
+  if (lane == 0) *epoch = e;
+}
+
 // blockIdx.y selects the peer (starting behind this rank, so that the ranks do not all read the same one first);
 // every thread moves four 16-byte words per round, loaded together before the first store.
-__global__ void __launch_bounds__(256)
-gather_blocks_kernel(SlotTable src, float* __restrict__ dst, int nranks, int rank, int64_t blk4, int64_t blk) {
+__global__ void __launch_bounds__(SIDE_THREADS, 2048 / SIDE_THREADS)
+gather_blocks_kernel(const __grid_constant__ SlotTable src, float* __restrict__ dst, int nranks, int rank, int64_t blk4, int64_t blk) {
   const int r = (rank + 1 + (int)blockIdx.y) % nranks;
   const float* s = src.p[r] + (int64_t)r * blk;
   float* d = dst + (int64_t)r * blk;
-  const int64_t round = (int64_t)gridDim.x * 1024;
-  for (int64_t base = (int64_t)blockIdx.x * 1024 + threadIdx.x; base < blk4; base += round) {
+  const int64_t round = (int64_t)gridDim.x * (4 * SIDE_THREADS);
+  for (int64_t base = (int64_t)blockIdx.x * (4 * SIDE_THREADS) + threadIdx.x; base < blk4; base += round) {
     float4 v[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      if (base + k * 256 < blk4) v[k] = __ldcs((const float4*)s + base + k * 256);
+      if (base + k * SIDE_THREADS < blk4) v[k] = __ldcs((const float4*)s + base + k * SIDE_THREADS);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      if (base + k * 256 < blk4) ((float4*)d)[base + k * 256] = v[k];
+      if (base + k * SIDE_THREADS < blk4) ((float4*)d)[base + k * SIDE_THREADS] = v[k];
   }
-  for (int64_t i = 4 * blk4 + (int64_t)blockIdx.x * 256 + threadIdx.x; i < blk; i += (int64_t)gridDim.x * 256) d[i] = s[i];
+  for (int64_t i = 4 * blk4 + (int64_t)blockIdx.x * SIDE_THREADS + threadIdx.x; i < blk; i += (int64_t)gridDim.x * SIDE_THREADS) d[i] = s[i];
 }
 
 }  // namespace
+
+int32_t fb_side_kernels_prepare_peer() {
+  FB_CUDA(cudaFuncSetAttribute(reduce_slots_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  FB_CUDA(cudaFuncSetAttribute(gather_blocks_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  FB_CUDA(cudaFuncSetAttribute(peer_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  return FB_OK;
+}
 
 FB_API int32_t fb_peer_alloc(fb_ctx* ctx, int64_t bytes, void** ptr_out, void* handle_host) {
   FB_CHECK_CTX(ctx);
@@ -124,6 +175,21 @@ FB_API int32_t fb_peer_free(fb_ctx* ctx, void* ptr) {
   return FB_OK;
 }
 
+FB_API int32_t fb_peer_barrier(fb_ctx* ctx, void* stream, uint32_t* const* peer_flags_host, int32_t nranks, int32_t rank,
+                               uint32_t* epoch_dev, int64_t timeout_ms) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(peer_flags_host && epoch_dev && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && timeout_ms >= 1,
+             FB_ERR_INVALID_ARG, "fb_peer_barrier: bad arguments (ranks %d, rank %d, timeout %lld ms)", nranks, rank, (long long)timeout_ms);
+  FlagTable t;
+  for (int p = 0; p < PEER_MAX_RANKS; ++p) {
+    t.p[p] = p < nranks ? peer_flags_host[p] : nullptr;
+    FB_REQUIRE(p >= nranks || t.p[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_barrier: rank %d has no flag array", p);
+  }
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(t, nranks, rank, epoch_dev, ctx->dev_error, (uint64_t)timeout_ms * 1000000ull);
+  FB_LAUNCH_CHECK();
+  return FB_OK;
+}
+
 FB_API int32_t fb_peer_gather_blocks(fb_ctx* ctx, void* stream, const float* const* peer_src_host, float* dst, int32_t nranks,
                                      int32_t rank, int64_t blk) {
   FB_CHECK_CTX(ctx);
@@ -139,10 +205,10 @@ FB_API int32_t fb_peer_gather_blocks(fb_ctx* ctx, void* stream, const float* con
     }
   }
   const int64_t blk4 = vec ? blk / 4 : 0;
-  int64_t per_peer = (blk / 4 + 1023) / 1024 + 1;
+  int64_t per_peer = (blk / 4 + 4 * SIDE_THREADS - 1) / (4 * SIDE_THREADS) + 1;
   const int64_t cap = ((int64_t)ctx->sm_count * 2 + nranks - 2) / (nranks - 1);
   if (per_peer > cap) per_peer = cap;
-  gather_blocks_kernel<<<dim3((unsigned)per_peer, (unsigned)(nranks - 1)), 256, 0, (cudaStream_t)stream>>>(t, dst, nranks, rank, blk4, blk);
+  gather_blocks_kernel<<<dim3((unsigned)per_peer, (unsigned)(nranks - 1)), SIDE_THREADS, 0, (cudaStream_t)stream>>>(t, dst, nranks, rank, blk4, blk);
   FB_LAUNCH_CHECK();
   return FB_OK;
 }
@@ -162,9 +228,9 @@ FB_API int32_t fb_reduce_slots(fb_ctx* ctx, void* stream, int32_t nslots, const 
     }
   }
   const int64_t count4 = vec ? count / 4 : 0;
-  int64_t blocks = (count / 4 + 255) / 256 + 1;
+  int64_t blocks = (count / 4 + SIDE_THREADS - 1) / SIDE_THREADS + 1;
   if (blocks > (int64_t)ctx->sm_count * 2) blocks = (int64_t)ctx->sm_count * 2;
-  reduce_slots_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(t, nslots, out, count4, count, scale);
+  reduce_slots_kernel<<<(unsigned)blocks, SIDE_THREADS, 0, (cudaStream_t)stream>>>(t, nslots, out, count4, count, scale);
   FB_LAUNCH_CHECK();
   return FB_OK;
 }

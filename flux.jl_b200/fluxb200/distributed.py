@@ -469,28 +469,32 @@ class GradBuckets:
         ctx = context()
         nbytes = 4 * self.flat.numel()
         HB = 64
-        mine, ptrs = [0] * (1 + 2 * HB), []
+        NB = 3                              # gradient buffer, parameter buffer, barrier epoch words
+        mine, ptrs = [0] * (1 + NB * HB + 16), []
+        mine[1 + NB * HB:] = list(torch.cuda.get_device_properties(self.flat.device).uuid.bytes)
         if want:
             try:
-                for k in range(2):          # gradient buffer, parameter buffer
+                for k in range(NB):
                     ptr, h = C.c_void_p(), (C.c_uint8 * HB)()
-                    lib.call("fb_peer_alloc", ctx.handle, nbytes, C.byref(ptr), h)
+                    lib.call("fb_peer_alloc", ctx.handle, nbytes if k < 2 else 4096, C.byref(ptr), h)
                     ptrs.append(ptr.value)
                     mine[1 + k * HB:1 + (k + 1) * HB] = list(bytes(h))
                 mine[0] = 1
             except lib.FluxB200Error:
                 mine[0] = 0
-        gathered = [torch.zeros(1 + 2 * HB, dtype=torch.uint8) for _ in range(be.size)]
+        gathered = [torch.zeros(1 + NB * HB + 16, dtype=torch.uint8) for _ in range(be.size)]
         dist.all_gather(gathered, torch.tensor(mine, dtype=torch.uint8))
         ok = all(int(g[0]) == 1 for g in gathered)
-        stage, pbuf = [None] * be.size, [None] * be.size
+        # the barrier kernels of the ranks wait for one another: every rank needs a GPU of its own
+        ok = ok and len({bytes(g[1 + NB * HB:].tolist()) for g in gathered}) == be.size
+        stage, pbuf, flags = [None] * be.size, [None] * be.size, [None] * be.size
         if ok:
             try:
                 for r, g in enumerate(gathered):
                     if r == be.rank:
-                        stage[r], pbuf[r] = ptrs
+                        stage[r], pbuf[r], flags[r] = ptrs
                         continue
-                    for k, table in ((0, stage), (1, pbuf)):
+                    for k, table in ((0, stage), (1, pbuf), (2, flags)):
                         h = (C.c_uint8 * HB)(*g[1 + k * HB:1 + (k + 1) * HB].tolist())
                         ptr = C.c_void_p()
                         lib.call("fb_peer_open", ctx.handle, h, C.byref(ptr))
@@ -510,8 +514,10 @@ class GradBuckets:
 
         raws = [_Raw(table[be.rank], self.flat.numel()) for table in (stage, pbuf)]
         tensors = tuple(torch.as_tensor(raw, device=self.flat.device) for raw in raws)
-        self.peer = {"grads": stage, "pflat": pbuf, "keep": raws,
-                     "token": torch.zeros(1, dtype=torch.float32, device=self.flat.device)}
+        self.peer = {"grads": stage, "pflat": pbuf, "flags": flags, "keep": raws,
+                     "epoch": torch.zeros(1, dtype=torch.int32, device=self.flat.device),
+                     "timeout_ms": int(os.environ.get("FLUXB200_BARRIER_TIMEOUT_MS", "10000"))}
+        dist.barrier()      # every rank has mapped every flag array before the first epoch is posted
         return tensors
 
     def start_gathers(self):
@@ -568,10 +574,14 @@ class GradBuckets:
         torch.cuda.current_stream().synchronize()
 
     def _peer_barrier(self, cs):
-        """A one-element all-reduce on the communication stream: when it completes on this rank, every rank has
-        finished what it enqueued before its own call."""
-        tok = C.c_void_p(self.peer["token"].data_ptr())
-        lib.call("fb_allreduce", self.backend.comm, cs, tok, tok, 1, lib.OP["+"])
+        """A barrier between the ranks on the communication stream (fb_peer_barrier: one warp posting and polling epoch
+        words in peer memory): when it completes on this rank, every rank has finished what it enqueued before its own
+        call.  A peer that does not arrive within FLUXB200_BARRIER_TIMEOUT_MS (default 10 s) leaves code 9101 in the
+        device error word, which the step's error poll raises on the host."""
+        peer = self.peer
+        n = self.backend.size
+        lib.call("fb_peer_barrier", context().handle, cs, (C.c_void_p * n)(*peer["flags"]), n, self.backend.rank,
+                 C.c_void_p(peer["epoch"].data_ptr()), peer["timeout_ms"])
 
     def set_loss(self, loss):
         """The step's loss (device scalar): the captured update kernels skip themselves when it is not finite.  With

@@ -455,14 +455,20 @@ int32_t fb_reduce(fb_comm* comm, void* stream, const float* send, float* recv, i
  *  - fb_peer_gather_blocks: for every peer p, block p (blk floats at offset p * blk) of peer_src_host[p] is copied to
  *    the same offset of dst (all-gather: peer_src_host[p] = the bucket inside rank p's parameter buffer, dst = the
  *    bucket inside mine; the entry of this rank is ignored).
- * Remote memory is only read.  The caller orders the phases with a collective on the same stream (a one-element
- * fb_allreduce is enough): what a rank wrote before it enqueued the collective is visible to a kernel another rank
- * enqueues behind it. */
+ *  - fb_peer_barrier: a barrier between the ranks as one warp on `stream`.  peer_flags_host[r] = rank r's array of
+ *    nranks 32-bit epoch words (zero at the start, allocated with fb_peer_alloc and mapped by the others); epoch_dev =
+ *    a zeroed device word of this rank that counts the barriers passed (the launch is therefore replayable from a
+ *    CUDA graph).  Every rank must enqueue the same sequence of barriers.  What a rank wrote before its barrier is
+ *    visible to a kernel another rank enqueues behind its own.  A rank that waits longer than timeout_ms for a peer
+ *    stores 9101 in the device error word (fb_device_error) and lets its stream continue: nothing hangs.
+ * Apart from the epoch words, remote memory is only read. */
 #define FB_PEER_HANDLE_BYTES 64
 int32_t fb_peer_alloc(fb_ctx* ctx, int64_t bytes, void** ptr_out, void* handle_host);
 int32_t fb_peer_open(fb_ctx* ctx, const void* handle_host, void** ptr_out);
 int32_t fb_peer_close(fb_ctx* ctx, void* ptr);
 int32_t fb_peer_free(fb_ctx* ctx, void* ptr);
+int32_t fb_peer_barrier(fb_ctx* ctx, void* stream, uint32_t* const* peer_flags_host, int32_t nranks, int32_t rank,
+                        uint32_t* epoch_dev, int64_t timeout_ms);
 int32_t fb_peer_gather_blocks(fb_ctx* ctx, void* stream, const float* const* peer_src_host, float* dst,
                               int32_t nranks, int32_t rank, int64_t blk);
 int32_t fb_reduce_slots(fb_ctx* ctx, void* stream, int32_t nslots, const float* const* slots_host, float* out,
