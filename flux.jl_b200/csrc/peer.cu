@@ -1,21 +1,20 @@
 // Gradient exchange over peer memory for the data-parallel step with a sharded optimiser (single node, NVLink /
-// NVSwitch): reduce-scatter and all-gather as kernels that READ the peers' buffers.
+// NVSwitch): reduce-scatter and all-gather as small kernels that STORE into buffers the peers have mapped.
 //
-// Every rank owns 1/N of each gradient bucket.  The gradient buffer and the parameter buffer of every rank are
-// allocated by fb_peer_alloc and mapped by all the others (CUDA IPC).  Per bucket:
-//   1. fb_peer_barrier on the communication stream: one warp writes this rank's epoch into a flag word of every peer
-//      and waits (bounded) until every peer's epoch has arrived here; when it completes, every rank's gradients of
-//      the bucket are written (each rank enqueues the barrier behind its own reverse-sweep kernels).  One warp and
-//      a dozen registers: it finds room on an SM beside a resident GEMM CTA, which an NCCL kernel does not
-//   2. fb_reduce_slots: the mean of the N ranks' copies of MY block, read in place from the N gradient buffers in
-//      rank order (plain loads over NVLink, 16 bytes per load, every thread keeps up to 8 loads in flight), then Adam
-//      on my block
-//   3. fb_peer_gather_blocks: the other ranks' updated blocks, read from their parameter buffers into mine - behind
-//      a second barrier inside the step, or behind one barrier at the start of the next step, beside its forward pass
-// Remote memory is only read, never written: the only cross-rank hazard is "a rank overwrites what a peer still
-// reads", and every such write sits behind a barrier the reader joins after its reads (stream order).  The sums run
-// in rank order, so every run gives bitwise the same averages.  NCCL's reduce-scatter and all-gather remain the
-// path when the ranks cannot map each other's memory.
+// Every rank owns 1/N of each gradient bucket.  A staging area, the parameter buffer and a page of barrier words of
+// every rank are allocated by fb_peer_alloc and mapped by all the others (CUDA IPC).  Per bucket:
+//   1. fb_peer_push_blocks: block p of my gradients -> slot [me] of peer p's staging area, for every peer p
+//   2. fb_peer_barrier: one warp writes this rank's epoch into a flag word of every peer and waits (bounded) until
+//      every peer's epoch has arrived here: the peers' blocks have landed in my staging area
+//   3. fb_reduce_slots: mean over the N slots of my block in rank order (local reads), then Adam on my block
+//   4. fb_peer_push_blocks: my updated block -> its place in every peer's parameter buffer, behind a barrier that
+//      says every rank has stopped reading the old values; one more barrier before anybody reads the new ones.
+//      With deferred gathers step 4 runs at the start of the next step, beside its forward pass.
+// Stores over NVLink are posted, so a few warps per SM keep the links busy; loads from a peer would need far more
+// bytes in flight than the registers beside a resident GEMM CTA allow (measured: 150 GB/s pulling, 8 ranks).
+// All kernels here are "side kernels": 128 threads of at most 32 registers, see SIDE_THREADS.  NCCL's kernels do
+// not fit beside the GEMM and wait for it to end; they remain the path when the ranks cannot map each other's memory.
+// The sums run in rank order, so every run gives bitwise the same averages.
 #include "common.cuh"
 
 namespace {
@@ -90,13 +89,14 @@ peer_barrier_kernel(const __grid_constant__ FlagTable flags, int nranks, int ran
   if (lane == 0) *epoch = e;
 }
 
-// blockIdx.y selects the peer (starting behind this rank, so that the ranks do not all read the same one first);
-// every thread moves four 16-byte words per round, loaded together before the first store.
+// blockIdx.y selects the peer (starting behind this rank, so that the ranks do not all write to the same one first);
+// every thread moves four 16-byte words per round, loaded (locally) together before the first (remote) store.
 __global__ void __launch_bounds__(SIDE_THREADS, 2048 / SIDE_THREADS)
-gather_blocks_kernel(const __grid_constant__ SlotTable src, float* __restrict__ dst, int nranks, int rank, int64_t blk4, int64_t blk) {
+push_blocks_kernel(const __grid_constant__ SlotTable dst, const float* __restrict__ src, int64_t src_stride, int nranks, int rank,
+                   int64_t blk4, int64_t blk) {
   const int r = (rank + 1 + (int)blockIdx.y) % nranks;
-  const float* s = src.p[r] + (int64_t)r * blk;
-  float* d = dst + (int64_t)r * blk;
+  const float* s = src + (int64_t)r * src_stride;
+  float* d = const_cast<float*>(dst.p[r]);
   const int64_t round = (int64_t)gridDim.x * (4 * SIDE_THREADS);
   for (int64_t base = (int64_t)blockIdx.x * (4 * SIDE_THREADS) + threadIdx.x; base < blk4; base += round) {
     float4 v[4];
@@ -114,7 +114,7 @@ gather_blocks_kernel(const __grid_constant__ SlotTable src, float* __restrict__ 
 
 int32_t fb_side_kernels_prepare_peer() {
   FB_CUDA(cudaFuncSetAttribute(reduce_slots_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-  FB_CUDA(cudaFuncSetAttribute(gather_blocks_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  FB_CUDA(cudaFuncSetAttribute(push_blocks_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   FB_CUDA(cudaFuncSetAttribute(peer_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   return FB_OK;
 }
@@ -190,25 +190,26 @@ FB_API int32_t fb_peer_barrier(fb_ctx* ctx, void* stream, uint32_t* const* peer_
   return FB_OK;
 }
 
-FB_API int32_t fb_peer_gather_blocks(fb_ctx* ctx, void* stream, const float* const* peer_src_host, float* dst, int32_t nranks,
-                                     int32_t rank, int64_t blk) {
+FB_API int32_t fb_peer_push_blocks(fb_ctx* ctx, void* stream, const float* src, int64_t src_stride, float* const* peer_dst_host,
+                                   int32_t nranks, int32_t rank, int64_t blk) {
   FB_CHECK_CTX(ctx);
-  FB_REQUIRE(peer_src_host && dst && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && blk >= 1,
-             FB_ERR_INVALID_ARG, "fb_peer_gather_blocks: bad arguments (ranks %d, rank %d, block %lld)", nranks, rank, (long long)blk);
+  FB_REQUIRE(src && peer_dst_host && nranks >= 2 && nranks <= PEER_MAX_RANKS && rank >= 0 && rank < nranks && blk >= 1 && src_stride >= 0,
+             FB_ERR_INVALID_ARG, "fb_peer_push_blocks: bad arguments (ranks %d, rank %d, block %lld)", nranks, rank, (long long)blk);
   SlotTable t;
-  bool vec = fb_aligned16(dst) && blk % 4 == 0;
+  bool vec = fb_aligned16(src) && blk % 4 == 0 && src_stride % 4 == 0;
   for (int p = 0; p < PEER_MAX_RANKS; ++p) {
-    t.p[p] = (p < nranks && p != rank) ? peer_src_host[p] : nullptr;
+    t.p[p] = (p < nranks && p != rank) ? peer_dst_host[p] : nullptr;
     if (p < nranks && p != rank) {
-      FB_REQUIRE(peer_src_host[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_gather_blocks: peer %d has no source pointer", p);
-      vec = vec && fb_aligned16(peer_src_host[p]);
+      FB_REQUIRE(peer_dst_host[p] != nullptr, FB_ERR_INVALID_ARG, "fb_peer_push_blocks: peer %d has no destination pointer", p);
+      vec = vec && fb_aligned16(peer_dst_host[p]);
     }
   }
   const int64_t blk4 = vec ? blk / 4 : 0;
   int64_t per_peer = (blk / 4 + 4 * SIDE_THREADS - 1) / (4 * SIDE_THREADS) + 1;
   const int64_t cap = ((int64_t)ctx->sm_count * 2 + nranks - 2) / (nranks - 1);
   if (per_peer > cap) per_peer = cap;
-  gather_blocks_kernel<<<dim3((unsigned)per_peer, (unsigned)(nranks - 1)), SIDE_THREADS, 0, (cudaStream_t)stream>>>(t, dst, nranks, rank, blk4, blk);
+  push_blocks_kernel<<<dim3((unsigned)per_peer, (unsigned)(nranks - 1)), SIDE_THREADS, 0, (cudaStream_t)stream>>>(t, src, src_stride, nranks,
+                                                                                                                 rank, blk4, blk);
   FB_LAUNCH_CHECK();
   return FB_OK;
 }

@@ -435,17 +435,10 @@ class GradBuckets:
             return False
         if self.pflat is None:
             self.mflat, self.vflat = (torch.zeros_like(self.flat) for _ in range(2))
-            # gradients and parameters live in memory the peers have mapped when the peer-memory exchange is available
-            bufs = self._setup_peer_exchange()
-            if bufs is None:
+            # parameters live in memory the peers can write when the peer-memory exchange is available
+            self.pflat = self._setup_peer_exchange()
+            if self.pflat is None:
                 self.pflat = torch.zeros_like(self.flat)
-            else:
-                gflat, self.pflat = bufs
-                gflat.copy_(self.flat)
-                self.flat = gflat
-                for p in self.params:
-                    off = self.offsets[id(p)]
-                    self.views[id(p)] = B200Array(self.flat[off:off + p.numel()], p.size)
             for p in self.params:
                 off, cnt = self.offsets[id(p)], p.numel()
                 st = opt_state.leaves[id(p)].state
@@ -457,11 +450,11 @@ class GradBuckets:
         return True
 
     def _setup_peer_exchange(self):
-        """Allocates this rank's gradient buffer and parameter buffer in memory the other ranks map (CUDA IPC) and maps
-        theirs, so that the reduce-scatter and the all-gather of the sharded step run as kernels that read the peers'
-        buffers over NVLink (fb_reduce_slots, fb_peer_gather_blocks).  Returns (gradient buffer, parameter buffer) as
-        tensors, or None when any rank cannot map its peers (or FLUXB200_EXCHANGE=nccl): then the NCCL collectives
-        are used."""
+        """Allocates a staging area, this rank's parameter buffer and a page of barrier words in memory the other ranks
+        map (CUDA IPC) and maps theirs, so that the reduce-scatter and the all-gather of the sharded step run as small
+        kernels that store over NVLink (fb_peer_push_blocks, fb_peer_barrier, fb_reduce_slots).  Returns the parameter
+        buffer as a tensor, or None when any rank cannot map its peers (or FLUXB200_EXCHANGE=nccl): then the NCCL
+        collectives are used."""
         import torch.distributed as dist
         be = self.backend
         self.peer = None
@@ -469,7 +462,7 @@ class GradBuckets:
         ctx = context()
         nbytes = 4 * self.flat.numel()
         HB = 64
-        NB = 3                              # gradient buffer, parameter buffer, barrier epoch words
+        NB = 3                              # staging area, parameter buffer, barrier epoch words
         mine, ptrs = [0] * (1 + NB * HB + 16), []
         mine[1 + NB * HB:] = list(torch.cuda.get_device_properties(self.flat.device).uuid.bytes)
         if want:
@@ -512,13 +505,13 @@ class GradBuckets:
             def __init__(self, ptr, count):
                 self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3, "strides": None}
 
-        raws = [_Raw(table[be.rank], self.flat.numel()) for table in (stage, pbuf)]
-        tensors = tuple(torch.as_tensor(raw, device=self.flat.device) for raw in raws)
-        self.peer = {"grads": stage, "pflat": pbuf, "flags": flags, "keep": raws,
+        raw = _Raw(pbuf[be.rank], self.flat.numel())
+        ptensor = torch.as_tensor(raw, device=self.flat.device)
+        self.peer = {"stage": stage, "pflat": pbuf, "flags": flags, "keep": raw,
                      "epoch": torch.zeros(1, dtype=torch.int32, device=self.flat.device),
                      "timeout_ms": int(os.environ.get("FLUXB200_BARRIER_TIMEOUT_MS", "10000"))}
         dist.barrier()      # every rank has mapped every flag array before the first epoch is posted
-        return tensors
+        return ptensor
 
     def start_gathers(self):
         """Deferred all-gather (sharded optimiser over peer memory): the parameter blocks updated in the previous step
@@ -540,15 +533,15 @@ class GradBuckets:
         if self.gather_events is None:
             self.gather_events = [torch.cuda.Event() for _ in self.buckets]
             self.start_fence = torch.cuda.Event()
-        # one barrier: every rank has finished the previous step, its updates and its reads of my gradient buffer
+        # one barrier first: every rank has finished the previous step - nobody reads the old parameter values any
+        # more (the dX products of a slower rank) and the staging areas are free again
         self._peer_barrier(cs)
         self.start_fence.record(be.stream)
         nb = len(self.buckets)
         order = [nb - 1] + list(range(nb - 2, -1, -1)) if nb > 1 else [0]   # small leaves, then weights first layer first
         for bi in order:
-            start, blk, _ = self._peer_block(bi)
-            lib.call("fb_peer_gather_blocks", h, cs, tab(*[peer["pflat"][r] + 4 * start for r in range(n)]),
-                     C.c_void_p(self.pflat.data_ptr() + 4 * start), n, be.rank, blk)
+            self._peer_gather(bi)
+            self._peer_barrier(cs)      # the peers' blocks of this bucket have landed here
             self.gather_events[bi].record(be.stream)
         self.gather_waited = set()
         self.gathering = True
@@ -652,30 +645,40 @@ class GradBuckets:
         blk = (end - start) // self.backend.size
         return start, blk, 4 * (start + self.backend.rank * blk)
 
-    def _peer_exchange(self, bi):
-        """Reduce-scatter of one bucket over peer memory: behind a barrier (every rank's gradients of the bucket are
-        written), the mean of the N ranks' copies of my block, read in place in rank order."""
+    def _peer_gather(self, bi):
+        """My updated block of one bucket -> its place in every peer's parameter buffer."""
         be, peer = self.backend, self.peer
         n = be.size
-        start, blk, lo = self._peer_block(bi)
-        cs = C.c_void_p(be.stream.cuda_stream)
-        tab = C.c_void_p * n
-        g = self.flat.data_ptr() + lo
-        self._peer_barrier(cs)
-        slots = tab(*[(peer["grads"][r] + lo) if r != be.rank else g for r in range(n)])
-        lib.call("fb_reduce_slots", context().handle, cs, n, slots, C.c_void_p(g), blk, 1.0 / n)
-        self._mark(f"bucket {bi} reduce-scatter end", be.stream)
+        _, blk, lo = self._peer_block(bi)
+        lib.call("fb_peer_push_blocks", context().handle, C.c_void_p(be.stream.cuda_stream), C.c_void_p(self.pflat.data_ptr() + lo), 0,
+                 (C.c_void_p * n)(*[peer["pflat"][r] + lo for r in range(n)]), n, be.rank, blk)
 
-    def _peer_update(self, bi, waited=False):
-        """Adam on my block of one bucket and, unless the gathers are deferred to the next step, a barrier (every
-        rank's block is updated) and the copies of the peers' blocks into my parameter buffer.  With waited=False the
-        call comes from a release: the communication stream first waits for the kernels enqueued so far, the last
-        readers of the parameter among them."""
+    def _peer_exchange(self, bi):
+        """Reduce-scatter of one bucket over peer memory: block p of my gradients goes to slot [me] of peer p's staging
+        area; behind a barrier (the peers' blocks have landed here) the N slots of my block are averaged in rank
+        order (my own slot is read where it was produced)."""
         be, peer = self.backend, self.peer
         n = be.size
         start, blk, lo = self._peer_block(bi)
         cs = C.c_void_p(be.stream.cuda_stream)
         h = context().handle
+        tab = C.c_void_p * n
+        g = self.flat.data_ptr() + lo
+        lib.call("fb_peer_push_blocks", h, cs, C.c_void_p(self.flat.data_ptr() + 4 * start), blk,
+                 tab(*[peer["stage"][r] + 4 * (start + be.rank * blk) for r in range(n)]), n, be.rank, blk)
+        self._peer_barrier(cs)
+        slots = tab(*[(peer["stage"][be.rank] + 4 * (start + r * blk)) if r != be.rank else g for r in range(n)])
+        lib.call("fb_reduce_slots", h, cs, n, slots, C.c_void_p(g), blk, 1.0 / n)
+        self._mark(f"bucket {bi} reduce-scatter end", be.stream)
+
+    def _peer_update(self, bi, waited=False):
+        """Adam on my block of one bucket and, unless the gathers are deferred to the next step, a barrier (every
+        rank has released the bucket's parameters: nobody reads the old values any more) and the copies of my block
+        into the peers' parameter buffers.  With waited=False the call comes from a release: the communication stream
+        first waits for the kernels enqueued so far, the last readers of the parameter among them."""
+        be = self.backend
+        _, blk, lo = self._peer_block(bi)
+        cs = C.c_void_p(be.stream.cuda_stream)
         if not waited:
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream())
@@ -683,15 +686,13 @@ class GradBuckets:
         rule, bt = self.adam
         one = C.c_void_p * 1
         g, pp = self.flat.data_ptr() + lo, self.pflat.data_ptr() + lo
-        lib.call("fb_adam_step_dev", h, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
+        lib.call("fb_adam_step_dev", context().handle, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
                  one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
                  rule.epsilon, C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
         self._mark(f"bucket {bi} adam end", be.stream)
         if not self.defer_gather:
-            tab = C.c_void_p * n
             self._peer_barrier(cs)
-            lib.call("fb_peer_gather_blocks", h, cs, tab(*[peer["pflat"][r] + 4 * start for r in range(n)]),
-                     C.c_void_p(self.pflat.data_ptr() + 4 * start), n, be.rank, blk)
+            self._peer_gather(bi)
         self._mark(f"bucket {bi} comm end", be.stream)
         self.events[bi].record(be.stream)
 
@@ -705,6 +706,10 @@ class GradBuckets:
             for bi in sorted(self.update_pending):      # a pullback that never released: update after everything enqueued
                 self._peer_update(bi)
             self.update_pending = set()
+            if self.armed and self.peer is not None and not self.defer_gather:
+                # the peers' parameter blocks must have landed here before anybody reads the parameters again
+                self._peer_barrier(C.c_void_p(self.backend.stream.cuda_stream))
+                self.events[-1].record(self.backend.stream)
             for ev in self.events:
                 torch.cuda.current_stream().wait_event(ev)
             if self.guard_event is not None:

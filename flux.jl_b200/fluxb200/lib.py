@@ -124,7 +124,7 @@ PROTOTYPES = {
     "fb_peer_close": (_i32, [_p, _p]),
     "fb_peer_free": (_i32, [_p, _p]),
     "fb_peer_barrier": (_i32, [_p, _p, C.POINTER(_p), _i32, _i32, _p, _i64]),
-    "fb_peer_gather_blocks": (_i32, [_p, _p, C.POINTER(_p), _p, _i32, _i32, _i64]),
+    "fb_peer_push_blocks": (_i32, [_p, _p, _p, _i64, C.POINTER(_p), _i32, _i32, _i64]),
     "fb_reduce_slots": (_i32, [_p, _p, _i32, C.POINTER(_p), _p, _i64, _f]),
     "fb_bucket_create": (_i32, [_p, _p, _p, _i64, _i32, C.POINTER(_i64), _p, C.POINTER(_p)]),
     "fb_bucket_destroy": (_i32, [_p]),

@@ -445,23 +445,24 @@ int32_t fb_bcast(fb_comm* comm, void* stream, const float* send, float* recv, in
 int32_t fb_reduce(fb_comm* comm, void* stream, const float* send, float* recv, int64_t count, int32_t op, int32_t root);
 
 /* Gradient exchange over peer memory (single node, NVLink / NVSwitch), for the sharded optimiser: reduce-scatter and
- * all-gather as kernels that read buffers the other ranks have mapped into this process.  No counterpart in the
- * reference (which calls NCCL.Allreduce! per leaf, ext/FluxMPINCCLExt/FluxMPINCCLExt.jl:61-66); results equal a mean
- * all-reduce followed by the same update on every rank.
+ * all-gather as small kernels that store into buffers the other ranks have mapped into this process; they are shaped
+ * to run on an SM beside a resident GEMM CTA, which NCCL's kernels are not.  No counterpart in the reference (which
+ * calls NCCL.Allreduce! per leaf, ext/FluxMPINCCLExt/FluxMPINCCLExt.jl:61-66); results equal a mean all-reduce
+ * followed by the same update on every rank.
  *  - fb_peer_alloc allocates `bytes` of zeroed device memory and returns a FB_PEER_HANDLE_BYTES handle that the
  *    caller hands to the other processes (any host channel); fb_peer_open maps a peer's handle into this process.
- *  - fb_reduce_slots: out = scale * (slots[0] + slots[1] + ... ) in that order; slots may lie in peers' memory, and
- *    out may be one of them (reduce-scatter: slots[r] = my block inside rank r's gradient buffer).
- *  - fb_peer_gather_blocks: for every peer p, block p (blk floats at offset p * blk) of peer_src_host[p] is copied to
- *    the same offset of dst (all-gather: peer_src_host[p] = the bucket inside rank p's parameter buffer, dst = the
- *    bucket inside mine; the entry of this rank is ignored).
+ *  - fb_peer_push_blocks: for every peer p, blk floats at src + p * src_stride are copied to peer_dst_host[p] (the
+ *    entry of this rank is ignored).  Reduce-scatter: src = my bucket, src_stride = blk, peer_dst_host[p] = slot
+ *    [me] of the bucket's staging area in peer p's memory.  All-gather: src = my updated block, src_stride = 0,
+ *    peer_dst_host[p] = the block's place in peer p's parameter buffer.
+ *  - fb_reduce_slots: out = scale * (slots[0] + slots[1] + ... ) in that order; out may be one of the slots.
  *  - fb_peer_barrier: a barrier between the ranks as one warp on `stream`.  peer_flags_host[r] = rank r's array of
  *    nranks 32-bit epoch words (zero at the start, allocated with fb_peer_alloc and mapped by the others); epoch_dev =
  *    a zeroed device word of this rank that counts the barriers passed (the launch is therefore replayable from a
- *    CUDA graph).  Every rank must enqueue the same sequence of barriers.  What a rank wrote before its barrier is
- *    visible to a kernel another rank enqueues behind its own.  A rank that waits longer than timeout_ms for a peer
- *    stores 9101 in the device error word (fb_device_error) and lets its stream continue: nothing hangs.
- * Apart from the epoch words, remote memory is only read. */
+ *    CUDA graph).  Every rank must enqueue the same sequence of barriers.  What a rank stored before its barrier
+ *    (into its own or a peer's memory) is visible to a kernel another rank enqueues behind its own.  A rank that waits
+ *    longer than timeout_ms for a peer stores 9101 in the device error word (fb_device_error) and lets its stream
+ *    continue: nothing hangs. */
 #define FB_PEER_HANDLE_BYTES 64
 int32_t fb_peer_alloc(fb_ctx* ctx, int64_t bytes, void** ptr_out, void* handle_host);
 int32_t fb_peer_open(fb_ctx* ctx, const void* handle_host, void** ptr_out);
@@ -469,8 +470,8 @@ int32_t fb_peer_close(fb_ctx* ctx, void* ptr);
 int32_t fb_peer_free(fb_ctx* ctx, void* ptr);
 int32_t fb_peer_barrier(fb_ctx* ctx, void* stream, uint32_t* const* peer_flags_host, int32_t nranks, int32_t rank,
                         uint32_t* epoch_dev, int64_t timeout_ms);
-int32_t fb_peer_gather_blocks(fb_ctx* ctx, void* stream, const float* const* peer_src_host, float* dst,
-                              int32_t nranks, int32_t rank, int64_t blk);
+int32_t fb_peer_push_blocks(fb_ctx* ctx, void* stream, const float* src, int64_t src_stride, float* const* peer_dst_host,
+                            int32_t nranks, int32_t rank, int64_t blk);
 int32_t fb_reduce_slots(fb_ctx* ctx, void* stream, int32_t nslots, const float* const* slots_host, float* out,
                         int64_t count, float scale);
 
