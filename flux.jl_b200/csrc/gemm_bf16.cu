@@ -12,9 +12,8 @@
 // overlaps the main loop of the next.
 //
 // Warp roles: warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the
-// epilogue (one TMEM lane quadrant each).  In a pair, warp 6 of each CTA relays "my half of stage s has landed" to
-// the leader's ready barrier, because the leader's MMA reads both CTAs' shared memory while a TMA load can only
-// signal a barrier of its own CTA.
+// epilogue (one TMEM lane quadrant each).  In a pair the leader's MMA reads both CTAs' shared memory, so both CTAs'
+// loads (cta_group::2 form) complete on the LEADER's full barrier, which expects the bytes of both halves.
 //
 // Operand layouts in shared memory are the canonical 128-byte-swizzle layouts the MMA descriptors name: K-major
 // tiles are rows of 128 bytes in 8-row atoms (SBO = 1024); MN-major tiles are chunks of 64 MN-values x BK k-rows of
@@ -43,7 +42,7 @@ struct HCfg {
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int SMEM_BYTES = BAR_OFFSET + 512 + 1024;  // barriers + alignment slack
   static constexpr int TMEM_COLS = 2 * BN;                    // two accumulator buffers
-  static constexpr int NUM_THREADS = 32 * (PAIR ? 7 : 6);
+  static constexpr int NUM_THREADS = 32 * 6;
   static constexpr uint32_t ARRIVALS = PAIR ? 8 : 4;          // epilogue warps arriving on tmem_empty
 };
 
@@ -84,10 +83,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t smem_base = smem_u32(smem);
   uint64_t* bars = (uint64_t*)(smem + cfg::BAR_OFFSET);
   const uint32_t bar_base = smem_base + cfg::BAR_OFFSET;
-  // barrier slots: full[S], empty[S], ready[S], tmem_full[2], tmem_empty[2]
+  // barrier slots: full[S], empty[S], (unused)[S], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(STAGES + s); };
-  auto ready_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * STAGES + s); };
   auto tmem_full_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * STAGES + b); };
   auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * STAGES + 2 + b); };
   volatile uint32_t* s_tmem = (volatile uint32_t*)(bars + 3 * STAGES + 4);
@@ -107,7 +105,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(ready_bar(s), 2);   // one relay arrival per CTA of the pair
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tmem_full_bar(b), 1);
@@ -165,29 +162,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
           ok = mbar_wait_cluster(empty_bar(s), ph ^ 1u, s_abort);
           if (!ok) break;
-          mbar_arrive_expect_tx(full_bar(s), (uint32_t)(cfg::A_BYTES + cfg::B_BYTES));
+          // pairs: the leader's barrier counts the bytes of both CTAs' halves; the peer only issues its loads
+          const uint32_t fb = PAIR ? map_to_cta(full_bar(s), 0u) : full_bar(s);
+          if (!PAIR || leader) mbar_arrive_expect_tx(full_bar(s), (uint32_t)((PAIR ? 2 : 1) * (cfg::A_BYTES + cfg::B_BYTES)));
           const uint32_t a_dst = smem_base + (uint32_t)(s * cfg::STAGE_BYTES);
           const uint32_t b_dst = a_dst + (uint32_t)cfg::A_BYTES;
           const int k0 = kb * HBK;
+          auto load2 = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
+            if (PAIR) tma_load_2d_pair(dst, map, x, y, fb);
+            else tma_load_2d(dst, map, x, y, fb);
+          };
+          auto load3 = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z) {
+            if (PAIR) tma_load_3d_pair(dst, map, x, y, z, fb);
+            else tma_load_3d(dst, map, x, y, z, fb);
+          };
           if (A_MN) {
             if (a3d) {
-              tma_load_3d(a_dst, &tmA, 0, k0, m0 >> 6, full_bar(s));
+              load3(a_dst, &tmA, 0, k0, m0 >> 6);
             } else {
 #pragma unroll
-              for (int c = 0; c < HBM_ / 64; ++c) tma_load_2d(a_dst + (uint32_t)(c * HBK * 128), &tmA, m0 + 64 * c, k0, full_bar(s));
+              for (int c = 0; c < HBM_ / 64; ++c) load2(a_dst + (uint32_t)(c * HBK * 128), &tmA, m0 + 64 * c, k0);
             }
           } else {
-            tma_load_2d(a_dst, &tmA, k0, m0, full_bar(s));
+            load2(a_dst, &tmA, k0, m0);
           }
           if (B_MN) {
             if (b3d) {
-              tma_load_3d(b_dst, &tmB, 0, k0, nb0 >> 6, full_bar(s));
+              load3(b_dst, &tmB, 0, k0, nb0 >> 6);
             } else {
 #pragma unroll
-              for (int c = 0; c < cfg::BNC / 64; ++c) tma_load_2d(b_dst + (uint32_t)(c * HBK * 128), &tmB, nb0 + 64 * c, k0, full_bar(s));
+              for (int c = 0; c < cfg::BNC / 64; ++c) load2(b_dst + (uint32_t)(c * HBK * 128), &tmB, nb0 + 64 * c, k0);
             }
           } else {
-            tma_load_2d(b_dst, &tmB, k0, nb0, full_bar(s));
+            load2(b_dst, &tmB, k0, nb0);
           }
         }
       }
@@ -211,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-          ok = mbar_wait_cluster(PAIR ? ready_bar(s) : full_bar(s), ph, s_abort);
+          ok = mbar_wait_cluster(full_bar(s), ph, s_abort);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_s = smem_base + (uint32_t)(s * cfg::STAGE_BYTES);
@@ -238,20 +245,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (last) tc_commit(tmem_full_bar(buf));
           }
         }
-      }
-    }
-  } else if (warp == 6) {
-    // ------------------------------- relay (pairs only): this CTA's half of a stage has landed ---
-    if (lane == 0) {
-      int total_kb = 0;
-      for (int t = cid; t < num_tiles; t += G) total_kb += num_kb;
-      bool ok = true;
-      for (int it = 0; it < total_kb && ok; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-        ok = mbar_wait(full_bar(s), ph, s_abort);
-        if (!ok) break;
-        mbar_arrive_cluster(map_to_cta(ready_bar(s), 0u));
       }
     }
   } else {
