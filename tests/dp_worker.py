@@ -201,6 +201,36 @@ def main():
         torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
     assert torch.equal(lo, hi), "replicas diverged under the sharded optimiser"
     assert F.context().device_error() == 0
+
+    # a non-finite loss on ONE worker: every worker skips the update (the reference decides per process, train.jl:377,
+    # which would leave the other workers' collectives without a partner and let the replicas diverge)
+    if world > 1:
+        bad = rank == world - 1
+        xbad = F.gpu(np.full(F.cpu(xg).shape, np.inf, np.float32)) if bad else xg
+        for shard in (False, True):
+            m = build()
+            bk = DU.GradBuckets(backend, F.trainables(m), bucket_mb=0.2)
+            o = F.setup(DU.DistributedOptimizer(backend, F.Adam(1e-3), bk), m)
+            gs = F.GraphedTrainStep(lambda mm, xx, yy: F.logitcrossentropy(mm(xx), yy), m, o, (xg, yg), grad_sink=bk,
+                                    shard_optimizer=shard, defer_gather=shard)
+            gs.sync_params()
+            before = [F.cpu(q).copy() for q in F.trainables(m)]
+            loss = gs(xbad, yg)
+            gs.sync_params()
+            assert np.isfinite(loss) != bad
+            for q, b in zip(F.trainables(m), before):
+                assert np.array_equal(F.cpu(q), b), "a worker updated although another worker's loss was not finite"
+            gs(xg, yg)             # the next finite step updates again, on every worker
+            gs.sync_params()
+            assert not np.array_equal(F.cpu(F.trainables(m)[0]), before[0])
+        m = build()
+        bk = DU.GradBuckets(backend, F.trainables(m), bucket_mb=0.2)
+        o = F.setup(DU.DistributedOptimizer(backend, F.Adam(1e-3), bk), m)
+        before = [F.cpu(q).copy() for q in F.trainables(m)]
+        F.trainstep(lambda mm, xx, yy: F.logitcrossentropy(mm(xx), yy), m, (xbad, yg), o)
+        for q, b in zip(F.trainables(m), before):
+            assert np.array_equal(F.cpu(q), b)
+    assert F.context().device_error() == 0
     if rank == 0:
         print("dp_worker ok", world)
 
