@@ -993,6 +993,133 @@ bool persistent_enabled() {
 
 // A cooperative launch cannot be recorded into a CUDA graph: under stream capture the time loop stays one launch per
 // step (which a graph replays at no host cost anyway).
+// GRU counterpart of lstm_bwd_persist_kernel: the whole reverse time loop in one cooperative launch.  Phase 1 of step t
+// forms the gate derivatives (dgx_t, dgh_t) from dh = dout_t + dh_direct + the partial sums of the step after it;
+// phase 2 lets block (ub, rb, bz) multiply its resident 64 x 128 tile of Wh with the 64 x 128 tile of dgh_t into
+// partial sums of dh_{t-1}.  dh_direct (dh * z) is carried by the thread that wrote it.  R = 3H need not be a multiple
+// of 128: columns past R are zero in both tiles.
+__global__ void __launch_bounds__(RT, 1)
+gru_bwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ cch, const float* __restrict__ out,
+                       const float* __restrict__ h0, const float* __restrict__ dout, const float* __restrict__ dhT, float* dgx,
+                       float* dgh, float* dh_direct, float* parts, int H, int B, int T, int UB, int NP, unsigned* counter,
+                       int32_t* dev_err) {
+  extern __shared__ __align__(16) float sm[];
+  float* Ws = sm;                   // [64 u][PB_LD]
+  float* Ds = Ws + DH_U * PB_LD;    // [64 b][PB_LD]
+  const int R = 3 * H;
+  const int ub = blockIdx.x % UB, rb = (blockIdx.x / UB) % NP, bz = blockIdx.x / (UB * NP);
+  const int u0 = ub * DH_U, r0 = rb * PB_R, b0 = bz * BC;
+  const int64_t ldrow = (int64_t)T * H, ldc = (int64_t)T * 4 * H, ldd = (int64_t)T * 3 * H, total = (int64_t)B * H;
+  for (int e = threadIdx.x; e < DH_U * (PB_R / 4); e += RT) {
+    const int row = e / (PB_R / 4), c4 = e % (PB_R / 4);
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (u0 + row < H && r0 + 4 * c4 < R) w = __ldg((const float4*)(Wh + (int64_t)(u0 + row) * R + r0 + 4 * c4));
+    *(float4*)(Ws + row * PB_LD + 4 * c4) = w;
+    *(float4*)(Ds + row * PB_LD + 4 * c4) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __syncthreads();
+  const int nrows = (B - b0) < BC ? (B - b0) : BC;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  unsigned gen = 0;      // grid barriers passed
+  for (int t = T - 1; t >= 0; --t) {
+    // ---- phase 1: gate derivatives of step t
+    {
+      const float* c_t = cch + (int64_t)t * 4 * H;
+      const float* dout_t = dout + (int64_t)t * H;
+      float* dgx_t = dgx + (int64_t)t * 3 * H;
+      float* dgh_t = dgh + (int64_t)t * 3 * H;
+      const bool lastt = (t == T - 1);
+      for (int64_t e = (int64_t)blockIdx.x * RT + threadIdx.x; e < total; e += (int64_t)gridDim.x * RT) {
+        const int b = (int)(e / H), u = (int)(e % H);
+        const float* cr = c_t + (int64_t)b * ldc;
+        const float r = cr[u], z = cr[H + u], hc = cr[2 * H + u], gh3 = cr[3 * H + u];
+        const float hp = t == 0 ? (h0 ? h0[e] : 0.0f) : out[(int64_t)(t - 1) * H + (int64_t)b * ldrow + u];
+        float dh = dout_t[(int64_t)b * ldrow + u];
+        if (lastt) {
+          if (dhT) dh += dhT[e];
+        } else {
+          dh += dh_direct[e];   // written by this same thread one step earlier
+          // partials written by other blocks: four loads in flight at a time, added in a fixed order
+          const float* pe = parts + e;
+          int p = 0;
+          for (; p + 4 <= NP; p += 4) {
+            const float q0 = __ldcg(pe + (int64_t)p * total), q1 = __ldcg(pe + (int64_t)(p + 1) * total);
+            const float q2 = __ldcg(pe + (int64_t)(p + 2) * total), q3 = __ldcg(pe + (int64_t)(p + 3) * total);
+            dh += (q0 + q1) + (q2 + q3);
+          }
+          for (; p < NP; ++p) dh += __ldcg(pe + (int64_t)p * total);
+        }
+        const float da3 = dh * (1.0f - z) * (1.0f - hc * hc);
+        const float da2 = dh * (hp - hc) * z * (1.0f - z);
+        const float da1 = da3 * gh3 * r * (1.0f - r);
+        float* x_ = dgx_t + (int64_t)b * ldd;
+        float* h_ = dgh_t + (int64_t)b * ldd;
+        x_[u] = da1; x_[H + u] = da2; x_[2 * H + u] = da3;
+        h_[u] = da1; h_[H + u] = da2; h_[2 * H + u] = da3 * r;
+        dh_direct[e] = dh * z;
+      }
+    }
+    if (t == 0) break;
+    ++gen;
+    if (!grid_barrier(counter, gen * gridDim.x, dev_err, 3004)) break;
+    // ---- phase 2: partial sums of Wh' * dgh_t (the recurrent part of dh_{t-1})
+    {
+      constexpr int PER = DH_U * (PB_R / 4) / RT;   // 8
+      float4 v[PER];
+      const float* base = dgh + (int64_t)t * 3 * H + r0;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int e = threadIdx.x + i * RT;
+        const int row = e / (PB_R / 4), c4 = e % (PB_R / 4);
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < nrows && r0 + 4 * c4 < R) v[i] = __ldcg((const float4*)(base + (int64_t)(b0 + row) * ldd + 4 * c4));
+      }
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int e = threadIdx.x + i * RT;
+        const int row = e / (PB_R / 4), c4 = e % (PB_R / 4);
+        *(float4*)(Ds + row * PB_LD + 4 * c4) = v[i];
+      }
+      __syncthreads();
+    }
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+#pragma unroll 4
+    for (int c = 0; c < PB_R; c += 4) {
+      float4 a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = *(const float4*)(Ds + (ty + 16 * i) * PB_LD + c);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = *(const float4*)(Ws + (tx + 16 * j) * PB_LD + c);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i].x, w[j].x, acc[i][j]);
+          acc[i][j] = fmaf(a[i].y, w[j].y, acc[i][j]);
+          acc[i][j] = fmaf(a[i].z, w[j].z, acc[i][j]);
+          acc[i][j] = fmaf(a[i].w, w[j].w, acc[i][j]);
+        }
+    }
+    float* pp = parts + (int64_t)rb * total;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int gb = b0 + ty + 16 * i;
+      if (gb >= B) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int gu = u0 + tx + 16 * j;
+        if (gu < H) pp[(int64_t)gb * H + gu] = acc[i][j];
+      }
+    }
+    ++gen;
+    if (!grid_barrier(counter, gen * gridDim.x, dev_err, 3004)) break;
+  }
+}
+
 bool persistent_allowed(cudaStream_t stream) {
   if (!persistent_enabled()) return false;
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -1318,16 +1445,38 @@ FB_API int32_t fb_gru_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
   float* dgx = (float*)cache + rows * 4 * H;       // [rows][3H], over the input projection
   float* dgh = dgx + rows * 3 * H;                 // [rows][3H]
   const int R = 3 * H;
-  const int nparts = (R + DH_R - 1) / DH_R;
+  // one cooperative launch for the whole reverse time loop when its grid can be resident at once
+  const int UBp = (H + DH_U - 1) / DH_U, NPp = (R + PB_R - 1) / PB_R, BZp = (B + BC - 1) / BC;
+  const int64_t pgrid = (int64_t)UBp * NPp * BZp;
+  bool persist = T > 1 && (H % 32 == 0) && fb_aligned16(Wh) && fb_aligned16(cache) && pgrid >= 1 && pgrid <= 4096 &&
+                 2 * T * pgrid < 0x7fffffff && persistent_allowed(stream);
+  if (persist) {
+    int per_sm = 0;
+    FB_CUDA(cudaFuncSetAttribute(gru_bwd_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PB_SMEM));
+    FB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gru_bwd_persist_kernel, RT, PB_SMEM));
+    persist = (int64_t)per_sm * ctx->sm_count >= pgrid;
+  }
+  const int nparts = persist ? NPp : (R + DH_R - 1) / DH_R;
   float* ws = (float*)fb_scratch(ctx, stream, (size_t)((1 + nparts) * (int64_t)B * H) * sizeof(float));
   if (!ws) return FB_ERR_ALLOC;
   float* dh_direct = ws;                     // dh * z, the part of dh_{t-1} that bypasses Wh
   float* parts = ws + (int64_t)B * H;        // [nparts][B][H] partial sums of Wh' * dgh
+  if (persist) {
+    unsigned* counter = (unsigned*)(ctx->dev_error + 16);
+    FB_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned), stream));
+    int Hi = H, Bi = B, Ti = (int)T, ubi = UBp, npi = NPp;
+    int32_t* dev_err = ctx->dev_error;
+    void* args[] = {(void*)&Wh, (void*)&cch, (void*)&out, (void*)&h0, (void*)&dout, (void*)&dhT, (void*)&dgx, (void*)&dgh,
+                    (void*)&dh_direct, (void*)&parts, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&ubi, (void*)&npi, (void*)&counter,
+                    (void*)&dev_err};
+    FB_CUDA(cudaLaunchCooperativeKernel((const void*)gru_bwd_persist_kernel, dim3((unsigned)pgrid), dim3(RT), args, PB_SMEM, stream));
+    FB_LAUNCH_CHECK();
+  }
   FB_CUDA(cudaFuncSetAttribute(rnn_bwd_dh2d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DH2D_SMEM));
   const dim3 grid_dh((unsigned)((H + DH_U - 1) / DH_U), (unsigned)nparts, (unsigned)((B + BC - 1) / BC));
   int64_t eb = ((int64_t)B * H + RT - 1) / RT;
   if (eb > ctx->sm_count * 8) eb = ctx->sm_count * 8;
-  for (int64_t t = T - 1; t >= 0; --t) {
+  for (int64_t t = persist ? -1 : T - 1; t >= 0; --t) {
     const float* hprev = t == 0 ? h0 : out + (t - 1) * H;
     const bool last = (t == T - 1);
     gru_bwd_gates_kernel<<<(unsigned)eb, RT, 0, stream>>>(cch + t * 4 * H, T * 4 * H, hprev, t == 0 ? (int64_t)H : ldrow,

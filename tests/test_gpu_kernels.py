@@ -401,7 +401,8 @@ def test_adam_matches_oracle_over_ten_steps(fb):
 
 
 # --------------------------------------------------------------------------------- recurrent ---
-@pytest.mark.parametrize("I,H,T,B", [(3, 4, 5, 2), (16, 32, 7, 3), (64, 128, 12, 70), (20, 130, 4, 5)])
+# (24, 64, 6, 32) and (40, 144, 5, 16): H and B multiples of 16, the register-tiled persistent forward kernel
+@pytest.mark.parametrize("I,H,T,B", [(3, 4, 5, 2), (16, 32, 7, 3), (64, 128, 12, 70), (20, 130, 4, 5), (24, 64, 6, 32), (40, 144, 5, 16)])
 @pytest.mark.parametrize("bias,state", [(True, False), (False, True)])
 def test_lstm_fwd_bwd(fb, I, H, T, B, bias, state):
     rng = np.random.default_rng(I + H + T + B)
@@ -440,7 +441,7 @@ def test_lstm_fwd_bwd(fb, I, H, T, B, bias, state):
         close(host(db, (4 * H,)), rb, name="db", rtol=2e-4, atol_scale=2e-4)
 
 
-@pytest.mark.parametrize("I,H,T,B", [(3, 4, 5, 2), (16, 32, 7, 3), (64, 128, 12, 70), (20, 130, 4, 5)])
+@pytest.mark.parametrize("I,H,T,B", [(3, 4, 5, 2), (16, 32, 7, 3), (64, 128, 12, 70), (20, 130, 4, 5), (24, 96, 6, 16)])
 @pytest.mark.parametrize("bias", [True, False])
 def test_gru_fwd_bwd(fb, I, H, T, B, bias):
     rng = np.random.default_rng(I + H + T + B + 1)
