@@ -655,6 +655,7 @@ batchnorm   BatchNorm(256, relu) training forward + backward on 32 x 32 x 256 x 
 adam        Adam step over 32 Mi parameters in 4 leaves
 attention   causal attention forward + backward, E = 1024, 16 heads, S = 1024, B = 2
 lstm        LSTM(512=>512) forward + backward, T = 32, B = 64
+gru         GRU(512=>512) forward + backward, T = 32, B = 64
 xent        logitcrossentropy forward + backward, 1000 x 8192"""
 
 
@@ -749,6 +750,17 @@ def run_case(args):
             call("fb_lstm_fwd", P(Wi), P(Wh), P(b), P(x), None, None, P(out), P(hT), P(cT), P(cache), I, Hd, T, B)
             call("fb_lstm_bwd", P(Wi), P(Wh), P(x), None, None, P(out), P(cache), P(dout), None, None, P(dWi), P(dWh), P(db), P(dx), I, Hd, T, B)
         work = (6.0 * 2 * 4 * Hd * (I + Hd) * T * B / 2, "TFLOP/s")
+    elif case == "gru":
+        I, Hd, T, B = 512, 512, 32, 64
+        Wi, Wh, b, x = rn(3 * Hd * I) * 0.05, rn(3 * Hd * Hd) * 0.05, rn(3 * Hd) * 0.1, rn(I * T * B)
+        out, hT, dout = em(Hd * T * B), em(Hd * B), rn(Hd * T * B)
+        cache = em(lib.raw().fb_gru_cache_bytes(I, Hd, T, B) // 4)
+        dWi, dWh, db, dx = torch.empty_like(Wi), torch.empty_like(Wh), torch.empty_like(b), torch.empty_like(x)
+
+        def fn():
+            call("fb_gru_fwd", P(Wi), P(Wh), P(b), P(x), None, P(out), P(hT), P(cache), I, Hd, T, B)
+            call("fb_gru_bwd", P(Wi), P(Wh), P(x), None, P(out), P(cache), P(dout), None, P(dWi), P(dWh), P(db), P(dx), I, Hd, T, B)
+        work = (6.0 * 2 * 3 * Hd * (I + Hd) * T * B / 2, "TFLOP/s")
     elif case == "xent":
         c, n = 1000, 8192
         yh, lab = rn(c * n), torch.randint(1, c + 1, (n,), device="cuda", dtype=torch.int32)

@@ -530,65 +530,63 @@ lstm_fwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ 
   }
 }
 
-// Register-tiled persistent LSTM forward (H and B multiples of 16): block (unit group, batch group) owns 16 hidden
-// units - their 64 gate rows of Wh, resident in shared memory as Ws[k][64] for all T steps - and 16 batch columns.
-// A step stages only the 16 rows of h_{t-1} the block needs (32 KB at H = 512 instead of all 64 rows), and every
-// thread accumulates a 4-row x 4-column tile over a quarter of k: per four k-values 8 shared-memory loads of 16 bytes
-// feed 64 FMAs (the row-per-thread scheme of lstm_fwd_persist_kernel issues 17 loads per 64 FMAs and is bound by
-// them).  The four k-quarters are summed through shared memory by the thread that owns (unit, column) in the gate
-// stage, which also kept c of that pair in the previous step.
-//   shared memory: Ws [H][64], hs [16][H + 4], red [4][64][17]
+// Register-tiled persistent forward time loop (H and B multiples of 16) for LSTM (NG = 4 gates) and GRU (NG = 3):
+// block (unit group, batch group) owns 16 hidden units - their NG * 16 gate rows of Wh, resident in shared memory as
+// Ws[k][NG * 16] for all T steps - and 16 batch columns.  A step stages only the 16 rows of h_{t-1} the block needs
+// (32 KB at H = 512 instead of all 64 rows), and every thread accumulates a 4-row x 4-column tile over a quarter of k:
+// per four k-values 8 shared-memory loads of 16 bytes feed 64 FMAs (the row-per-thread scheme of the *_persist
+// kernels issues 17 loads per 64 FMAs and is bound by them).  The four k-quarters are summed through shared memory
+// by the thread that owns (unit, column) in the gate stage; for the LSTM that thread also keeps c of the pair in a
+// register.  Only the blocks of one batch group exchange h rows, so each group has its own barrier counter.
+//   shared memory: Ws [H][NG * 16], hs [16][H + 4], red [4][NG * 16][17]
+//   LSTM: cache = gates [rows][4H] (or NULL), cst = cell states, gx [rows][4H].  GRU: cache = (r, z, hc, gh3)
+//   [rows][4H] (or NULL), gx [rows][3H]; c0 / cst / cT unused.
 constexpr int TU = 16, TB = 16;
-inline size_t tile_fwd_smem(int H) { return ((size_t)H * 64 + (size_t)TB * (H + 4) + 4 * 64 * 17) * sizeof(float); }
+inline size_t tile_fwd_smem(int ng, int H) {
+  return ((size_t)H * ng * 16 + (size_t)TB * (H + 4) + (size_t)4 * ng * 16 * 17) * sizeof(float);
+}
 
+template <int NG>
 __global__ void __launch_bounds__(RT, 1)
-lstm_fwd_tile_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, const float* __restrict__ h0,
-                     const float* __restrict__ c0, float* out, float* gates, float* cst, int cached, float* __restrict__ hT,
-                     float* __restrict__ cT, int H, int B, int T, unsigned* counter, int32_t* dev_err) {
+rnn_fwd_tile_kernel(const float* __restrict__ Wh, const float* __restrict__ gx, const float* __restrict__ h0,
+                    const float* __restrict__ c0, float* out, float* cache, float* cst, int cached, float* __restrict__ hT,
+                    float* __restrict__ cT, int H, int B, int T, unsigned* counter, int32_t* dev_err) {
+  constexpr int NR = NG * 16;
   extern __shared__ __align__(16) float sm[];
   const int hs_ld = H + 4;
   float* Ws = sm;
-  float* hs = Ws + (size_t)H * 64;
+  float* hs = Ws + (size_t)H * NR;
   float* red = hs + TB * hs_ld;
   const int ugroups = H / TU;
   const int u0 = ((int)blockIdx.x % ugroups) * TU, b0 = ((int)blockIdx.x / ugroups) * TB;
-  const int64_t ldrow = (int64_t)T * H, ldg = (int64_t)T * 4 * H;
+  const int64_t ldrow = (int64_t)T * H, ldgx = (int64_t)T * NG * H, ldc = (int64_t)T * 4 * H;
   __shared__ __align__(8) uint64_t h_bar;
   const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&h_bar);
   if (threadIdx.x == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1u) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // Ws[k][g * 16 + u] = Wh[g * H + u0 + u][k]: 16 consecutive floats of the [H][4H] weight memory per (k, g)
-  for (int e = threadIdx.x; e < H * 16; e += RT) {
-    const int k = e >> 4, q = e & 15, g = q >> 2, part = q & 3;
-    const float4 w = __ldg((const float4*)(Wh + (int64_t)k * (4 * H) + g * H + u0 + part * 4));
-    *(float4*)(Ws + (size_t)k * 64 + g * 16 + part * 4) = w;
+  // Ws[k][g * 16 + u] = Wh[g * H + u0 + u][k]: 16 consecutive floats of the [H][NG * H] weight memory per (k, g)
+  for (int e = threadIdx.x; e < H * (NG * 4); e += RT) {
+    const int k = e / (NG * 4), q = e % (NG * 4), g = q >> 2, part = q & 3;
+    const float4 w = __ldg((const float4*)(Wh + (int64_t)k * (NG * H) + g * H + u0 + part * 4));
+    *(float4*)(Ws + (size_t)k * NR + g * 16 + part * 4) = w;
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
   const int kq = threadIdx.x >> 6, rg = (threadIdx.x & 63) >> 2, bgi = threadIdx.x & 3;   // tile roles
   const int gu = threadIdx.x & 15, gb = threadIdx.x >> 4;                                 // gate-stage roles
+  const int b = b0 + gb, u = u0 + gu;
   const int per = H >> 2;   // k-values per quarter (a multiple of 4)
   uint32_t loads = 0;       // bulk loads waited for so far: names the barrier phase
-  float gxv[4] = {0.f, 0.f, 0.f, 0.f};
+  float gxv[NG];
   bool have_gx = false;
-  // the cell state of (column, unit) stays in a register of the thread that owns the pair in the gate stage
-  float c_reg = c0 ? c0[(int64_t)(b0 + gb) * H + u0 + gu] : 0.0f;
-  // only the blocks of the same batch group exchange h rows: one barrier counter per group
+  // LSTM: the cell state of (column, unit) stays in a register of the thread that owns the pair in the gate stage
+  float c_reg = (NG == 4 && c0) ? c0[(int64_t)b * H + u] : 0.0f;
   unsigned* my_counter = counter + (int)blockIdx.x / ugroups;
   for (int t = 0; t < T; ++t) {
     const float* hprev = t == 0 ? h0 : out + (int64_t)(t - 1) * H;
     const int64_t ldh = t == 0 ? H : ldrow;
-    float* c_t;
-    int64_t ldct;
-    if (cached) {
-      c_t = cst + (int64_t)t * H;
-      ldct = ldrow;
-    } else {
-      c_t = cst + (int64_t)(t & 1) * B * H;
-      ldct = H;
-    }
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -614,63 +612,84 @@ lstm_fwd_tile_kernel(const float* __restrict__ Wh, const float* __restrict__ gx,
         if (threadIdx.x == 0) atomicCAS(dev_err, 0, 3002);
         return;
       }
-      const float* hbase = hs + bgi * hs_ld;
-      const float* wbase = Ws + rg * 4;
-      for (int k = kq * per; k < (kq + 1) * per; k += 4) {
-        float4 hv[4];
+      if (rg < NG * 4) {
+        const float* hbase = hs + bgi * hs_ld;
+        const float* wbase = Ws + rg * 4;
+        for (int k = kq * per; k < (kq + 1) * per; k += 4) {
+          float4 hv[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) hv[j] = *(const float4*)(hbase + (4 * j) * hs_ld + k);   // columns bgi, bgi+4, bgi+8, bgi+12
+          for (int j = 0; j < 4; ++j) hv[j] = *(const float4*)(hbase + (4 * j) * hs_ld + k);   // columns bgi, bgi+4, bgi+8, bgi+12
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const float4 w = *(const float4*)(wbase + (size_t)(k + kk) * 64);
+          for (int kk = 0; kk < 4; ++kk) {
+            const float4 w = *(const float4*)(wbase + (size_t)(k + kk) * NR);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float hk = kk == 0 ? hv[j].x : kk == 1 ? hv[j].y : kk == 2 ? hv[j].z : hv[j].w;
-            acc[0][j] = fmaf(w.x, hk, acc[0][j]);
-            acc[1][j] = fmaf(w.y, hk, acc[1][j]);
-            acc[2][j] = fmaf(w.z, hk, acc[2][j]);
-            acc[3][j] = fmaf(w.w, hk, acc[3][j]);
+            for (int j = 0; j < 4; ++j) {
+              const float hk = kk == 0 ? hv[j].x : kk == 1 ? hv[j].y : kk == 2 ? hv[j].z : hv[j].w;
+              acc[0][j] = fmaf(w.x, hk, acc[0][j]);
+              acc[1][j] = fmaf(w.y, hk, acc[1][j]);
+              acc[2][j] = fmaf(w.z, hk, acc[2][j]);
+              acc[3][j] = fmaf(w.w, hk, acc[3][j]);
+            }
           }
         }
       }
     }
+    if (rg < NG * 4) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) red[(kq * 64 + rg * 4 + i) * 17 + bgi + 4 * j] = acc[i][j];
+        for (int j = 0; j < 4; ++j) red[(kq * NR + rg * 4 + i) * 17 + bgi + 4 * j] = acc[i][j];
+    }
     __syncthreads();
     {
-      const int b = b0 + gb, u = u0 + gu;
-      float pre[4];
+      float pre[NG];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
+      for (int g = 0; g < NG; ++g) {
         float sum = 0.0f;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) sum += red[(q * 64 + g * 16 + gu) * 17 + gb];
+        for (int q = 0; q < 4; ++q) sum += red[(q * NR + g * 16 + gu) * 17 + gb];
         pre[g] = sum;
       }
       if (!have_gx) {
-        const float* gxr = gx + (int64_t)t * 4 * H + (int64_t)b * ldg;
-        gxv[0] = gxr[u]; gxv[1] = gxr[H + u]; gxv[2] = gxr[2 * H + u]; gxv[3] = gxr[3 * H + u];
+        const float* gxr = gx + (int64_t)t * NG * H + (int64_t)b * ldgx;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) gxv[g] = gxr[g * H + u];
       }
-      const float zi = pre[0] + gxv[0], zf = pre[1] + gxv[1], zg = pre[2] + gxv[2], zo = pre[3] + gxv[3];
-      const float ig = 1.0f / (1.0f + expf(-zi)), fg = 1.0f / (1.0f + expf(-zf));
-      const float gg = tanhf(zg), og = 1.0f / (1.0f + expf(-zo));
-      const float cn = fg * c_reg + ig * gg;
-      c_reg = cn;
-      const float hn = og * tanhf(cn);
+      float hn;
+      if (NG == 4) {
+        const float zi = pre[0] + gxv[0], zf = pre[1] + gxv[1], zg = pre[2] + gxv[2], zo = pre[NG - 1] + gxv[NG - 1];
+        const float ig = 1.0f / (1.0f + expf(-zi)), fg = 1.0f / (1.0f + expf(-zf));
+        const float gg = tanhf(zg), og = 1.0f / (1.0f + expf(-zo));
+        const float cn = fg * c_reg + ig * gg;
+        c_reg = cn;
+        hn = og * tanhf(cn);
+        if (cache) {
+          float* gr = cache + (int64_t)t * 4 * H + (int64_t)b * ldc;
+          gr[u] = ig; gr[H + u] = fg; gr[2 * H + u] = gg; gr[3 * H + u] = og;
+        }
+        float* c_t = cached ? cst + (int64_t)t * H + (int64_t)b * ldrow : cst + (int64_t)(t & 1) * B * H + (int64_t)b * H;
+        c_t[u] = cn;
+        if (t == T - 1 && hT) cT[(int64_t)b * H + u] = cn;
+      } else {
+        const float gh3 = pre[2];
+        const float r = 1.0f / (1.0f + expf(-(gxv[0] + pre[0])));
+        const float z = 1.0f / (1.0f + expf(-(gxv[1] + pre[1])));
+        const float hc = tanhf(gxv[2] + r * gh3);
+        const float hp = hprev ? hs[gb * hs_ld + u] : 0.0f;   // the staged row of h_{t-1}
+        hn = (1.0f - z) * hc + z * hp;
+        if (cache) {
+          float* cr = cache + (int64_t)t * 4 * H + (int64_t)b * ldc;
+          cr[u] = r; cr[H + u] = z; cr[2 * H + u] = hc; cr[3 * H + u] = gh3;
+        }
+      }
       out[(int64_t)t * H + (int64_t)b * ldrow + u] = hn;
-      if (gates) {
-        float* gr = gates + (int64_t)t * 4 * H + (int64_t)b * ldg;
-        gr[u] = ig; gr[H + u] = fg; gr[2 * H + u] = gg; gr[3 * H + u] = og;
-      }
-      c_t[(int64_t)b * ldct + u] = cn;
-      if (t == T - 1 && hT) { hT[(int64_t)b * H + u] = hn; cT[(int64_t)b * H + u] = cn; }
+      if (t == T - 1 && hT) hT[(int64_t)b * H + u] = hn;
       // the input projection of the next step does not depend on the recurrence: fetch it before the barrier
       have_gx = false;
       if (t + 1 < T) {
-        const float* gxr = gx + (int64_t)(t + 1) * 4 * H + (int64_t)b * ldg;
-        gxv[0] = gxr[u]; gxv[1] = gxr[H + u]; gxv[2] = gxr[2 * H + u]; gxv[3] = gxr[3 * H + u];
+        const float* gxr = gx + (int64_t)(t + 1) * NG * H + (int64_t)b * ldgx;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) gxv[g] = gxr[g * H + u];
         have_gx = true;
       }
     }
@@ -1195,13 +1214,13 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
   else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
   const int64_t ldrow = T * H;       // stride between batch rows of out / cached c at a fixed t
-  if (fast && T > 1 && H % TU == 0 && B % TB == 0 && tile_fwd_smem(H) <= ctx->smem_optin && persistent_allowed(stream)) {
+  if (fast && T > 1 && H % TU == 0 && B % TB == 0 && tile_fwd_smem(4, H) <= ctx->smem_optin && persistent_allowed(stream)) {
     // register-tiled persistent kernel: (H / 16) x (B / 16) blocks, all resident, one cooperative launch
     const int64_t tgrid = (int64_t)(H / TU) * (B / TB);
-    const size_t tsmem = tile_fwd_smem(H);
+    const size_t tsmem = tile_fwd_smem(4, H);
     int per_sm = 0;
-    FB_CUDA(cudaFuncSetAttribute(lstm_fwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem));
-    FB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lstm_fwd_tile_kernel, RT, tsmem));
+    FB_CUDA(cudaFuncSetAttribute(rnn_fwd_tile_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem));
+    FB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rnn_fwd_tile_kernel<4>, RT, tsmem));
     if ((int64_t)per_sm * ctx->sm_count >= tgrid && T * tgrid < 0x7fffffff && B / TB <= 32) {
       unsigned* counter = (unsigned*)(ctx->dev_error + 16);      // one counter per batch group (at most 32)
       FB_CUDA(cudaMemsetAsync(counter, 0, (size_t)(B / TB) * sizeof(unsigned), stream));
@@ -1209,7 +1228,7 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
       int32_t* dev_err = ctx->dev_error;
       void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&c0, (void*)&out, (void*)&gates, (void*)&cst, (void*)&cached,
                       (void*)&hT, (void*)&cT, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&counter, (void*)&dev_err};
-      FB_CUDA(cudaLaunchCooperativeKernel((const void*)lstm_fwd_tile_kernel, dim3((unsigned)tgrid), dim3(RT), args, tsmem, stream));
+      FB_CUDA(cudaLaunchCooperativeKernel((const void*)rnn_fwd_tile_kernel<4>, dim3((unsigned)tgrid), dim3(RT), args, tsmem, stream));
       FB_LAUNCH_CHECK();
       return FB_OK;
     }
@@ -1398,6 +1417,27 @@ FB_API int32_t fb_gru_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
   if (fast) FB_CUDA(cudaFuncSetAttribute(gru_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   else FB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const unsigned grid = (unsigned)((H + hu - 1) / hu);
+  if (fast && T > 1 && H % TU == 0 && B % TB == 0 && tile_fwd_smem(3, H) <= ctx->smem_optin && persistent_allowed(stream)) {
+    // register-tiled persistent kernel: (H / 16) x (B / 16) blocks, all resident, one cooperative launch
+    const int64_t tgrid = (int64_t)(H / TU) * (B / TB);
+    const size_t tsmem = tile_fwd_smem(3, H);
+    int per_sm = 0;
+    FB_CUDA(cudaFuncSetAttribute(rnn_fwd_tile_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem));
+    FB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rnn_fwd_tile_kernel<3>, RT, tsmem));
+    if ((int64_t)per_sm * ctx->sm_count >= tgrid && T * tgrid < 0x7fffffff && B / TB <= 32) {
+      unsigned* counter = (unsigned*)(ctx->dev_error + 16);      // one counter per batch group (at most 32)
+      FB_CUDA(cudaMemsetAsync(counter, 0, (size_t)(B / TB) * sizeof(unsigned), stream));
+      int cached = 0, Hi = H, Bi = B, Ti = (int)T;
+      int32_t* dev_err = ctx->dev_error;
+      const float* c0 = nullptr;
+      float *cst = nullptr, *cT = nullptr;
+      void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&c0, (void*)&out, (void*)&cch, (void*)&cst, (void*)&cached,
+                      (void*)&hT, (void*)&cT, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&counter, (void*)&dev_err};
+      FB_CUDA(cudaLaunchCooperativeKernel((const void*)rnn_fwd_tile_kernel<3>, dim3((unsigned)tgrid), dim3(RT), args, tsmem, stream));
+      FB_LAUNCH_CHECK();
+      return FB_OK;
+    }
+  }
   if (fast && T > 1 && T * (int64_t)grid < 0x7fffffff && persistent_allowed(stream)) {
     // one cooperative launch for the whole sequence when every block can be resident at once
     int per_sm = 0;

@@ -441,7 +441,7 @@ def test_lstm_fwd_bwd(fb, I, H, T, B, bias, state):
         close(host(db, (4 * H,)), rb, name="db", rtol=2e-4, atol_scale=2e-4)
 
 
-@pytest.mark.parametrize("I,H,T,B", [(3, 4, 5, 2), (16, 32, 7, 3), (64, 128, 12, 70), (20, 130, 4, 5), (24, 96, 6, 16)])
+@pytest.mark.parametrize("I,H,T,B", [(3, 4, 5, 2), (16, 32, 7, 3), (64, 128, 12, 70), (20, 130, 4, 5), (24, 96, 6, 16), (40, 144, 5, 32)])
 @pytest.mark.parametrize("bias", [True, False])
 def test_gru_fwd_bwd(fb, I, H, T, B, bias):
     rng = np.random.default_rng(I + H + T + B + 1)
