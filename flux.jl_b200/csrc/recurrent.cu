@@ -1010,8 +1010,12 @@ bool persistent_enabled() {
   return on != 0;
 }
 
-// A cooperative launch cannot be recorded into a CUDA graph: under stream capture the time loop stays one launch per
-// step (which a graph replays at no host cost anyway).
+// The persistent kernels synchronise their blocks with a bounded barrier of their own, which needs every block
+// resident at once.  Outside a stream capture they are launched cooperatively (the runtime then guarantees it, or
+// refuses).  A cooperative launch cannot be recorded into a CUDA graph, so under capture the same kernel is launched
+// plainly: its grid was sized by the occupancy query to fit the GPU, and a replayed graph starts it when the stream's
+// previous kernel has ended; should another stream hold SMs at that moment, the barrier's limit ends the launch with
+// code 3001-3004 in the device error word instead of waiting for ever.
 // GRU counterpart of lstm_bwd_persist_kernel: the whole reverse time loop in one cooperative launch.  Phase 1 of step t
 // forms the gate derivatives (dgx_t, dgh_t) from dh = dout_t + dh_direct + the partial sums of the step after it;
 // phase 2 lets block (ub, rb, bz) multiply its resident 64 x 128 tile of Wh with the 64 x 128 tile of dgh_t into
@@ -1139,14 +1143,16 @@ gru_bwd_persist_kernel(const float* __restrict__ Wh, const float* __restrict__ c
   }
 }
 
-bool persistent_allowed(cudaStream_t stream) {
-  if (!persistent_enabled()) return false;
+bool persistent_allowed(cudaStream_t) { return persistent_enabled(); }
+
+cudaError_t launch_persistent(const void* kern, dim3 grid, dim3 block, void** args, size_t smem, cudaStream_t stream) {
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) {
     cudaGetLastError();
-    return false;
+    cs = cudaStreamCaptureStatusNone;
   }
-  return cs == cudaStreamCaptureStatusNone;
+  if (cs == cudaStreamCaptureStatusNone) return cudaLaunchCooperativeKernel(kern, grid, block, args, smem, stream);
+  return cudaLaunchKernel(kern, grid, block, args, smem, stream);
 }
 
 int32_t check_dims(const char* fn, int64_t in_dim, int64_t H, int64_t T, int64_t B) {
@@ -1228,7 +1234,7 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
       int32_t* dev_err = ctx->dev_error;
       void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&c0, (void*)&out, (void*)&gates, (void*)&cst, (void*)&cached,
                       (void*)&hT, (void*)&cT, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&counter, (void*)&dev_err};
-      FB_CUDA(cudaLaunchCooperativeKernel((const void*)rnn_fwd_tile_kernel<4>, dim3((unsigned)tgrid), dim3(RT), args, tsmem, stream));
+      FB_CUDA(launch_persistent((const void*)rnn_fwd_tile_kernel<4>, dim3((unsigned)tgrid), dim3(RT), args, tsmem, stream));
       FB_LAUNCH_CHECK();
       return FB_OK;
     }
@@ -1245,7 +1251,7 @@ FB_API int32_t fb_lstm_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
       int32_t* dev_err = ctx->dev_error;
       void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&c0, (void*)&out, (void*)&gates, (void*)&cst, (void*)&cached,
                       (void*)&hT, (void*)&cT, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&counter, (void*)&dev_err};
-      FB_CUDA(cudaLaunchCooperativeKernel((const void*)lstm_fwd_persist_kernel, dim3(grid), dim3(RT), args, smem, stream));
+      FB_CUDA(launch_persistent((const void*)lstm_fwd_persist_kernel, dim3(grid), dim3(RT), args, smem, stream));
       FB_LAUNCH_CHECK();
       return FB_OK;
     }
@@ -1323,7 +1329,7 @@ FB_API int32_t fb_lstm_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const fl
     int32_t* dev_err = ctx->dev_error;
     void* args[] = {(void*)&Wh, (void*)&gates, (void*)&cst, (void*)&c0, (void*)&dout, (void*)&dhT, (void*)&dc, (void*)&parts,
                     (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&ubi, (void*)&npi, (void*)&counter, (void*)&dev_err};
-    FB_CUDA(cudaLaunchCooperativeKernel((const void*)lstm_bwd_persist_kernel, dim3((unsigned)pgrid), dim3(RT), args, PB_SMEM, stream));
+    FB_CUDA(launch_persistent((const void*)lstm_bwd_persist_kernel, dim3((unsigned)pgrid), dim3(RT), args, PB_SMEM, stream));
     FB_LAUNCH_CHECK();
   }
   FB_CUDA(cudaFuncSetAttribute(rnn_bwd_dh2d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DH2D_SMEM));
@@ -1433,7 +1439,7 @@ FB_API int32_t fb_gru_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
       float *cst = nullptr, *cT = nullptr;
       void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&c0, (void*)&out, (void*)&cch, (void*)&cst, (void*)&cached,
                       (void*)&hT, (void*)&cT, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&counter, (void*)&dev_err};
-      FB_CUDA(cudaLaunchCooperativeKernel((const void*)rnn_fwd_tile_kernel<3>, dim3((unsigned)tgrid), dim3(RT), args, tsmem, stream));
+      FB_CUDA(launch_persistent((const void*)rnn_fwd_tile_kernel<3>, dim3((unsigned)tgrid), dim3(RT), args, tsmem, stream));
       FB_LAUNCH_CHECK();
       return FB_OK;
     }
@@ -1450,7 +1456,7 @@ FB_API int32_t fb_gru_fwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
       int32_t* dev_err = ctx->dev_error;
       void* args[] = {(void*)&Wh, (void*)&gx, (void*)&h0, (void*)&out, (void*)&cch, (void*)&hT, (void*)&Hi, (void*)&Bi, (void*)&Ti,
                       (void*)&counter, (void*)&dev_err};
-      FB_CUDA(cudaLaunchCooperativeKernel((const void*)gru_fwd_persist_kernel, dim3(grid), dim3(RT), args, smem, stream));
+      FB_CUDA(launch_persistent((const void*)gru_fwd_persist_kernel, dim3(grid), dim3(RT), args, smem, stream));
       FB_LAUNCH_CHECK();
       return FB_OK;
     }
@@ -1509,7 +1515,7 @@ FB_API int32_t fb_gru_bwd(fb_ctx* ctx, void* stream_, const float* Wi, const flo
     void* args[] = {(void*)&Wh, (void*)&cch, (void*)&out, (void*)&h0, (void*)&dout, (void*)&dhT, (void*)&dgx, (void*)&dgh,
                     (void*)&dh_direct, (void*)&parts, (void*)&Hi, (void*)&Bi, (void*)&Ti, (void*)&ubi, (void*)&npi, (void*)&counter,
                     (void*)&dev_err};
-    FB_CUDA(cudaLaunchCooperativeKernel((const void*)gru_bwd_persist_kernel, dim3((unsigned)pgrid), dim3(RT), args, PB_SMEM, stream));
+    FB_CUDA(launch_persistent((const void*)gru_bwd_persist_kernel, dim3((unsigned)pgrid), dim3(RT), args, PB_SMEM, stream));
     FB_LAUNCH_CHECK();
   }
   FB_CUDA(cudaFuncSetAttribute(rnn_bwd_dh2d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DH2D_SMEM));
