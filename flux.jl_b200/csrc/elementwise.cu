@@ -157,10 +157,13 @@ struct AdamTable {
   int ntensors;
 };
 
-// 128 threads of at most 32 registers: such a CTA fits on an SM beside a resident GEMM CTA (one warp per register-file
-// partition), so an update enqueued on the communication stream does not wait for the reverse sweep's GEMM to end.
-constexpr int ADAM_THREADS = 128;
-__global__ void __launch_bounds__(ADAM_THREADS, 2048 / ADAM_THREADS)
+// Two shapes of one kernel.  The plain one (256 threads) streams at the HBM roofline when it has the GPU to itself.
+// The side one (128 threads of at most 32 registers) fits on an SM beside a resident GEMM CTA - one warp per
+// register-file partition - so an update enqueued on the communication stream does not wait for the reverse sweep's
+// GEMM to end; alone it reaches about 70 % of the plain one's bandwidth.
+constexpr int ADAM_SIDE_THREADS = 128;
+template <int ADAM_THREADS, int MIN_BLOCKS>
+__global__ void __launch_bounds__(ADAM_THREADS, MIN_BLOCKS)
 adam_kernel(const __grid_constant__ AdamTable tab, float eta, float beta1, float beta2, float eps, float inv_c1,
             float inv_c2, float grad_scale, const float* __restrict__ bt_dev, const float* __restrict__ guard) {
   // device-resident step state (used when the step is replayed from a CUDA graph): the running beta powers
@@ -352,7 +355,8 @@ __global__ void timestamp_kernel(uint64_t* out) {
 }
 
 int32_t fb_side_kernels_prepare_elementwise() {
-  FB_CUDA(cudaFuncSetAttribute(adam_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  FB_CUDA(cudaFuncSetAttribute(adam_kernel<ADAM_SIDE_THREADS, 2048 / ADAM_SIDE_THREADS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared));
   FB_CUDA(cudaFuncSetAttribute(timestamp_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   return FB_OK;
 }
@@ -477,7 +481,7 @@ FB_API int32_t fb_logitcrossentropy_dense(fb_ctx* ctx, void* stream, const float
 static int32_t adam_common(fb_ctx* ctx, cudaStream_t stream, int32_t ntensors, float* const* w_host,
                            const float* const* g_host, float* const* m_host, float* const* v_host,
                            const int64_t* counts_host, float eta, float beta1, float beta2, float eps, float b1t,
-                           float b2t, float grad_scale, const float* bt_dev, const float* guard);
+                           float b2t, float grad_scale, const float* bt_dev, const float* guard, bool side = false);
 
 FB_API int32_t fb_adam_step(fb_ctx* ctx, void* stream_, int32_t ntensors, float* const* w_host,
                             const float* const* g_host, float* const* m_host, float* const* v_host,
@@ -498,6 +502,14 @@ FB_API int32_t fb_adam_step_dev(fb_ctx* ctx, void* stream_, int32_t ntensors, fl
                      0.0f, 0.0f, grad_scale, bt_dev, guard_dev);
 }
 
+FB_API int32_t fb_adam_block_dev(fb_ctx* ctx, void* stream_, float* w, const float* g, float* m, float* v, int64_t count, float eta,
+                                 float beta1, float beta2, float eps, const float* bt_dev, const float* guard_dev, float grad_scale) {
+  FB_CHECK_CTX(ctx);
+  FB_REQUIRE(bt_dev != nullptr, FB_ERR_INVALID_ARG, "fb_adam_block_dev: bt_dev is NULL");
+  return adam_common(ctx, (cudaStream_t)stream_, 1, &w, &g, &m, &v, &count, eta, beta1, beta2, eps, 0.0f, 0.0f, grad_scale, bt_dev,
+                     guard_dev, true);
+}
+
 __global__ void adam_advance_kernel(float* __restrict__ bt, float beta1, float beta2, const float* __restrict__ guard) {
   if (guard != nullptr && !isfinite(*guard)) return;
   bt[0] *= beta1;
@@ -515,7 +527,7 @@ FB_API int32_t fb_adam_advance(fb_ctx* ctx, void* stream_, float* bt_dev, float 
 static int32_t adam_common(fb_ctx* ctx, cudaStream_t stream, int32_t ntensors, float* const* w_host,
                            const float* const* g_host, float* const* m_host, float* const* v_host,
                            const int64_t* counts_host, float eta, float beta1, float beta2, float eps, float b1t,
-                           float b2t, float grad_scale, const float* bt_dev, const float* guard) {
+                           float b2t, float grad_scale, const float* bt_dev, const float* guard, bool side) {
   FB_REQUIRE(ntensors >= 0, FB_ERR_INVALID_ARG, "fb_adam_step: negative tensor count");
   if (ntensors == 0) return FB_OK;
   FB_REQUIRE(w_host && g_host && m_host && v_host && counts_host, FB_ERR_INVALID_ARG, "fb_adam_step: NULL table");
@@ -545,7 +557,12 @@ static int32_t adam_common(fb_ctx* ctx, cudaStream_t stream, int32_t ntensors, f
     if (k == 0) continue;
     tab.block_start[k] = blocks;
     tab.ntensors = k;
-    adam_kernel<<<(unsigned)blocks, ADAM_THREADS, 0, stream>>>(tab, eta, beta1, beta2, eps, inv_c1, inv_c2, grad_scale, bt_dev, guard);
+    if (side)
+      adam_kernel<ADAM_SIDE_THREADS, 2048 / ADAM_SIDE_THREADS><<<(unsigned)blocks, ADAM_SIDE_THREADS, 0, stream>>>(
+          tab, eta, beta1, beta2, eps, inv_c1, inv_c2, grad_scale, bt_dev, guard);
+    else
+      adam_kernel<EW_THREADS, 1><<<(unsigned)blocks, EW_THREADS, 0, stream>>>(tab, eta, beta1, beta2, eps, inv_c1, inv_c2, grad_scale,
+                                                                              bt_dev, guard);
     FB_LAUNCH_CHECK();
   }
   return FB_OK;

@@ -684,11 +684,10 @@ class GradBuckets:
             ev.record(torch.cuda.current_stream())
             be.stream.wait_event(ev)
         rule, bt = self.adam
-        one = C.c_void_p * 1
         g, pp = self.flat.data_ptr() + lo, self.pflat.data_ptr() + lo
-        lib.call("fb_adam_step_dev", context().handle, cs, 1, one(pp), one(g), one(self.mflat.data_ptr() + lo),
-                 one(self.vflat.data_ptr() + lo), (C.c_int64 * 1)(blk), rule.eta, rule.beta[0], rule.beta[1],
-                 rule.epsilon, C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
+        lib.call("fb_adam_block_dev", context().handle, cs, C.c_void_p(pp), C.c_void_p(g), C.c_void_p(self.mflat.data_ptr() + lo),
+                 C.c_void_p(self.vflat.data_ptr() + lo), blk, rule.eta, rule.beta[0], rule.beta[1], rule.epsilon,
+                 C.c_void_p(bt.data_ptr()), self.guard.ptr, 1.0)
         self._mark(f"bucket {bi} adam end", be.stream)
         if not self.defer_gather:
             self._peer_barrier(cs)

@@ -89,6 +89,7 @@ PROTOTYPES = {
                             C.POINTER(_i64), _f, _f, _f, _f, _f, _f, _f]),
     "fb_adam_step_dev": (_i32, [_p, _p, _i32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_p),
                                 C.POINTER(_i64), _f, _f, _f, _f, _p, _p, _f]),
+    "fb_adam_block_dev": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _f, _f, _f, _f, _p, _p, _f]),
     "fb_adam_advance": (_i32, [_p, _p, _p, _f, _f, _p]),
     "fb_lstm_cache_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "fb_gru_cache_bytes": (_i64, [_i64, _i64, _i64, _i64]),

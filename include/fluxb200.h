@@ -306,6 +306,11 @@ int32_t fb_adam_step_dev(fb_ctx* ctx, void* stream, int32_t ntensors, float* con
                          const float* const* g_host, float* const* m_host, float* const* v_host,
                          const int64_t* counts_host, float eta, float beta1, float beta2, float eps,
                          const float* bt_dev, const float* guard_dev, float grad_scale);
+/* The same update for ONE contiguous block, as a kernel shaped to run on an SM beside a resident GEMM CTA (128 threads
+ * of at most 32 registers): the sharded optimiser's update on the communication stream (no counterpart in the
+ * reference; public_api.jl:291-294 updates every leaf on every rank). */
+int32_t fb_adam_block_dev(fb_ctx* ctx, void* stream, float* w, const float* g, float* m, float* v, int64_t count, float eta,
+                          float beta1, float beta2, float eps, const float* bt_dev, const float* guard_dev, float grad_scale);
 int32_t fb_adam_advance(fb_ctx* ctx, void* stream, float* bt_dev, float beta1, float beta2,
                         const float* guard_dev);
 
