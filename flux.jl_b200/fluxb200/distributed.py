@@ -262,17 +262,20 @@ class DistributedDataContainer:
 
 class GradBuckets:
     """Flat gradient buffer split into buckets of ~bucket_mb MiB in reverse parameter order (the order
-    the backward pass produces gradients).  Layer pullbacks write gradients straight into their slice;
-    when a bucket's last gradient has landed, its mean all-reduce starts on the communication stream
-    while the backward pass continues."""
+    the backward pass produces gradients), the small leaves together in one last bucket.  Layer pullbacks write
+    gradients straight into their slice; when a bucket's last gradient has landed, its exchange starts on the
+    communication stream while the backward pass continues: a mean all-reduce, or - in a step captured with the
+    sharded optimiser (`shard_optimizer`) - reduce-scatter, Adam on this rank's block and all-gather, over peer memory
+    on one node (`_setup_peer_exchange`) or with NCCL."""
 
     SMALL_LEAF = 1 << 16   # leaves below this many elements share the last bucket
 
     def __init__(self, backend, params, bucket_mb: float = 64.0, reserved_sms: int | None = None):
         self.backend = backend
-        # SMs the reverse sweep's persistent GEMMs leave free for the NCCL kernels that run beside them.  Measured at
-        # 8 GPUs, per-GPU batch 1024: 0, 16 and 32 reserved SMs give 6.43-6.51, 6.52-6.56 and 6.85 ms per step, so the
-        # default reserves none (FLUXB200_SM_RESERVE or the argument overrides).
+        # SMs the persistent GEMMs leave free for the exchange kernels.  Measured at 8 GPUs, per-GPU batch 1024: with
+        # the NCCL exchange 0, 16 and 32 reserved SMs give 6.43-6.51, 6.52-6.56 and 6.85 ms per step; with the
+        # peer-memory exchange 12 reserved SMs gave 5.95 against 6.12 ms in one run and the default 5.91 in another,
+        # so the default reserves none (FLUXB200_SM_RESERVE or the argument overrides).
         if reserved_sms is None:
             reserved_sms = int(os.environ.get("FLUXB200_SM_RESERVE", "0"))
         self.reserved_sms = reserved_sms if backend.size > 1 else 0
@@ -288,7 +291,7 @@ class GradBuckets:
         self.pflat = self.mflat = self.vflat = None
         self.adam = None
         self.armed = False
-        self.peer = None             # peer-memory tables of the copy-based exchange (see _setup_peer_exchange)
+        self.peer = None             # peer-memory tables of the exchange over NVLink (see _setup_peer_exchange)
         self.defer_gather = False    # parameter gathers at the start of the next step (start_gathers) instead of per bucket
         self.gather_events = None
         self.gathering = False
