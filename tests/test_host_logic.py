@@ -45,3 +45,98 @@ def test_create_bias():
     assert F.create_bias(w, np.arange(3.0), 3).dtype == np.float32
     with pytest.raises(F.DimensionMismatch):
         F.create_bias(w, np.zeros(4), 3)
+
+
+# ------------------------------------------------------------------ the exchange's order of launches, simulated ---
+class _FakeStream:
+    cuda_stream = 0
+
+    def wait_event(self, ev):
+        pass
+
+    def synchronize(self):
+        pass
+
+
+class _FakeEvent:
+    def record(self, stream=None):
+        pass
+
+
+class _FakeArr:
+    def __init__(self, t, size):
+        self.t, self.size, self.ptr = t, tuple(size), None
+
+    def numel(self):
+        return self.t.numel()
+
+
+def _simulated_rank(monkeypatch, rank, world, defer, log):
+    """A GradBuckets of one rank with the library, CUDA events and streams replaced by recorders: what is checked is
+    the ORDER in which the exchange's kernels are enqueued, which must be the same on every rank (each rank has to
+    enqueue the same sequence of barriers) and must hold an update back until the parameter's last reader is
+    enqueued."""
+    import types
+
+    import torch
+
+    from fluxb200 import distributed as D
+    monkeypatch.setattr(D, "B200Array", _FakeArr)
+    monkeypatch.setattr(D, "context", lambda: types.SimpleNamespace(handle=None, stream=None))
+    monkeypatch.setattr(D.torch.cuda, "Event", _FakeEvent)
+    monkeypatch.setattr(D.torch.cuda, "current_stream", lambda: _FakeStream())
+    monkeypatch.setattr(D.lib, "call", lambda name, *a: log.append(name))
+    backend = types.SimpleNamespace(size=world, rank=rank, comm=None, stream=_FakeStream())
+    # three Dense layers (weight + bias) with a LayerNorm (scale, bias) in front of each, parameter order of the model
+    mk = lambda *size: _FakeArr(torch.zeros(int(np.prod(size))), size)
+    params = []
+    for _ in range(3):
+        params += [mk(256), mk(256), mk(256, 256), mk(256)]
+    gb = D.GradBuckets(backend, params, bucket_mb=0.25)
+    assert len(gb.buckets) == 4 and all((b[1] - b[0]) % world == 0 for b in gb.buckets)   # 3 weights + the small leaves
+    n = gb.flat.numel()
+    gb.pflat, gb.mflat, gb.vflat = (torch.zeros(n) for _ in range(3))
+    gb.adam = (types.SimpleNamespace(eta=1e-3, beta=(0.9, 0.999), epsilon=1e-8), torch.zeros(2))
+    gb.peer = {"stage": [0] * world, "pflat": [0] * world, "flags": [0] * world, "epoch": torch.zeros(1, dtype=torch.int32),
+               "timeout_ms": 10}
+    gb.armed, gb.loss, gb.guard, gb.defer_gather = True, object(), types.SimpleNamespace(ptr=None), defer
+    return gb, params
+
+
+@pytest.mark.parametrize("defer", [False, True])
+def test_exchange_enqueues_the_same_barriers_on_every_rank_and_holds_updates_back(monkeypatch, defer):
+    world = 2
+    logs = []
+    for rank in range(world):
+        log = []
+        gb, params = _simulated_rank(monkeypatch, rank, world, defer, log)
+        for step in range(2):
+            gb.begin_step()
+            if defer:
+                gb.start_gathers()
+            at_step_start = len(log)
+            # reverse sweep: Dense pullback reports its weight early (dW enqueued, dX still reads W), then the sweep
+            # reports weight and bias; the LayerNorm in front reports scale and bias
+            for layer in reversed(range(3)):
+                scale, lbias, W, b = params[4 * layer:4 * layer + 4]
+                before = len(log)
+                gb.ready(W, early=True)
+                during = log[before:]
+                assert "fb_reduce_slots" in during and "fb_adam_block_dev" not in during, during   # exchange yes, update no
+                gb.ready(W)
+                assert log[before + len(during):] [:1] == ["fb_adam_block_dev"]                   # released: the update follows
+                gb.ready(b)
+                gb.ready(lbias)
+                gb.ready(scale)
+            gb.finish()
+            per_step = log[at_step_start:]
+            assert per_step.count("fb_adam_block_dev") == 4 and per_step.count("fb_reduce_slots") == 4
+            # reduce-scatter push + barrier per bucket; gathers inside the step add a barrier and a push per bucket
+            # plus one closing barrier, deferred gathers add one opening barrier and a push + barrier per bucket
+            assert per_step.count("fb_peer_push_blocks") == (4 if defer else 8)
+            assert per_step.count("fb_peer_barrier") == (4 if defer else 9)
+            if defer:
+                start = log[at_step_start - 9:at_step_start]
+                assert start == ["fb_peer_barrier"] + ["fb_peer_push_blocks", "fb_peer_barrier"] * 4
+        logs.append(log)
+    assert logs[0] == logs[1]
