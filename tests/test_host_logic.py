@@ -140,3 +140,25 @@ def test_exchange_enqueues_the_same_barriers_on_every_rank_and_holds_updates_bac
                 assert start == ["fb_peer_barrier"] + ["fb_peer_push_blocks", "fb_peer_barrier"] * 4
         logs.append(log)
     assert logs[0] == logs[1]
+
+
+def test_nccl_fallback_keeps_its_order_and_ignores_early_reports(monkeypatch):
+    """Without mapped peer memory the sharded step uses NCCL per bucket (reduce-scatter, Adam, all-gather) and an early
+    report of a weight gradient changes nothing; an unarmed sink averages with one all-reduce per bucket."""
+    for armed in (True, False):
+        log = []
+        gb, params = _simulated_rank(monkeypatch, 0, 2, False, log)
+        gb.peer, gb.armed = None, armed
+        gb.begin_step()
+        for layer in reversed(range(3)):
+            scale, lbias, W, b = params[4 * layer:4 * layer + 4]
+            before = len(log)
+            gb.ready(W, early=True)
+            assert len(log) == before            # ignored: nothing may start while the dX product still reads W
+            for q in (W, b, lbias, scale):
+                gb.ready(q)
+        gb.finish()
+        if armed:
+            assert log == ["fb_reduce_scatter", "fb_adam_step_dev", "fb_allgather"] * 4
+        else:
+            assert log == ["fb_allreduce"] * 4
