@@ -348,7 +348,6 @@ class GradBuckets:
     def _mark(self, name, stream=None):
         if self.marks is None or len(self.mark_names) >= self.marks.numel():
             return
-        from .core import context
         st = C.c_void_p(stream.cuda_stream) if stream is not None else context().stream
         lib.call("fb_timestamp", context().handle, st, C.c_void_p(self.marks.data_ptr() + 8 * len(self.mark_names)))
         self.mark_names.append(name)
@@ -617,7 +616,6 @@ class GradBuckets:
         cs = C.c_void_p(be.stream.cuda_stream)
         ptr = C.c_void_p(self.flat.data_ptr() + 4 * start)
         if self.armed and self.adam is not None and self.loss is not None:
-            from .core import context
             rule, bt = self.adam
             n = be.size
             blk = (end - start) // n
